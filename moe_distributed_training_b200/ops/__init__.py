@@ -1,0 +1,99 @@
+"""Operator front end.
+
+Every op has exactly two implementations: the hand-written sm_100a kernels in
+the in-tree extension (`ops.cuda_ops`, taken for CUDA tensors; it raises if the
+extension is not built) and the plain PyTorch statement in `ops.reference`
+(taken for CPU tensors; also the numerical oracle in the tests).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import reference
+from .reference import BLOCK_ROWS, RoutingPlan, plan_capacity
+
+
+def _cuda():
+    from . import cuda_ops  # raises a clear error if the extension is missing
+    return cuda_ops
+
+
+def router(x, w_router, top_k, normalize=True, jitter_eps=None, training=False):
+    if x.is_cuda and jitter_eps is None:
+        return _cuda().router(x, w_router, top_k, normalize)
+    return reference.router(x, w_router, top_k, normalize, jitter_eps, training)
+
+
+def make_plan(top_experts, num_experts, block=BLOCK_ROWS, capacity=None) -> RoutingPlan:
+    if top_experts.is_cuda:
+        return _cuda().make_plan(top_experts, num_experts, block, capacity)
+    return reference.make_plan(top_experts, num_experts, block, capacity)
+
+
+def gather_rows(x, plan: RoutingPlan):
+    if x.is_cuda:
+        return _cuda().gather_rows(x, plan)
+    return reference.gather_rows(x, plan.src_slot, plan.top_k)
+
+
+def combine_rows(y, plan: RoutingPlan, weights: Optional[torch.Tensor]):
+    if y.is_cuda:
+        return _cuda().combine_rows(y, plan, weights)
+    return reference.combine_rows(y, plan.dest_row, weights, plan.top_k)
+
+
+def grouped_swiglu_mlp(xg, w1, w2, w3, plan: RoutingPlan, lora=None, wgrad_scale: float = 1.0):
+    """Expert MLP over block-padded groups; w1, w2, w3 are [E_local, F, H]."""
+    if xg.is_cuda:
+        return _cuda().grouped_swiglu_mlp(xg, w1, w2, w3, plan, lora, wgrad_scale)
+    return reference.grouped_swiglu_mlp(xg, w1, w2, w3, plan.padded_offsets, plan.tokens_per_expert, lora, wgrad_scale)
+
+
+def grouped_linear(x, w, plan: RoutingPlan, trans_b: bool, lora=None):
+    if x.is_cuda:
+        return _cuda().grouped_linear(x, w, plan, trans_b, lora)
+    return reference.grouped_linear(x, w, plan.padded_offsets, trans_b, plan.tokens_per_expert, lora)
+
+
+def linear(x, w, lora=None):
+    if x.is_cuda:
+        return _cuda().linear(x, w, lora)
+    return reference.linear(x, w, lora)
+
+
+def rmsnorm(x, weight, eps):
+    if x.is_cuda:
+        return _cuda().rmsnorm(x, weight, eps)
+    return reference.rmsnorm(x, weight, eps)
+
+
+def rope(x, positions, theta):
+    if x.is_cuda:
+        return _cuda().rope(x, positions, theta)
+    return reference.rope(x, positions, theta)
+
+
+def attention(q, k, v, cu_seqlens, max_seqlen=None):
+    if q.is_cuda:
+        return _cuda().attention(q, k, v, cu_seqlens, max_seqlen)
+    return reference.attention(q, k, v, cu_seqlens)
+
+
+def cross_entropy_sum(hidden, w_head, labels, ignore_index=-100):
+    if hidden.is_cuda:
+        return _cuda().cross_entropy_sum(hidden, w_head, labels, ignore_index)
+    return reference.cross_entropy_sum(hidden, w_head, labels, ignore_index)
+
+
+def embedding(ids, weight):
+    if weight.is_cuda:
+        return _cuda().embedding(ids, weight)
+    return torch.nn.functional.embedding(ids, weight)
+
+
+def swiglu(g, u):
+    if g.is_cuda:
+        return _cuda().swiglu(g, u)
+    return reference.swiglu(g, u)

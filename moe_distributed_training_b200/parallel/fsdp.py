@@ -1,0 +1,424 @@
+"""Parameter sharding (ZeRO-3 / FSDP2 semantics) with block-wise recomputation.
+
+The reference applies torch's `fully_shard` to every decoder block and to the
+root module, wraps each block in an activation-checkpoint wrapper, and excludes
+the MoE modules from sharding when they are expert-parallel
+(train_accelerate_fsdp2.py:163-238).  This module provides the same behaviour
+with explicit control over buffers and streams:
+
+  * each unit (one decoder block; the root = embeddings + final norm + lm_head)
+    keeps its dense parameters as one flat buffer, split evenly over the shard
+    group; the flat shard is the `nn.Parameter` the optimizer sees
+  * before a block runs, its full flat buffer is gathered (prefetched one block
+    ahead on a side stream) and the modules' weights become views into it
+  * a block's forward runs without a graph; its backward gathers again,
+    recomputes the block, back-propagates, and reduce-scatters the flat gradient
+    (scaled by 1/shard-group size, reduced over the replicate group for HSDP)
+  * MoE parameters that are expert-parallel stay ordinary local parameters;
+    their gradients get the data-parallel reductions the reference omits
+    (router: mean over all ranks; experts: mean over expert replicas)
+
+On a 2-D `(data_parallel, expert_parallel)` mesh the dense parameters are
+sharded over the expert_parallel dim and replicated over data_parallel, which is
+what passing that mesh to `fully_shard` does in the reference
+(train_accelerate_fsdp2.py:141-160,187).
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import ops
+from ..models.mixtral import CausalLMOutput, MixtralForCausalLM, PackedBatch
+from . import collectives as coll
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class FlatParamGroup:
+    """Parameters of one unit flattened into a single buffer sharded over `group`."""
+
+    ALIGN = 128  # elements; keeps every rank's shard 256-byte aligned for bf16
+
+    def __init__(self, entries, group, trainable: bool):
+        # entries: list of (module, attribute name, parameter)
+        self.group = group
+        self.ws, self.rank = coll.group_size(group), coll.group_rank(group)
+        self.trainable = trainable
+        self.specs = []
+        off = 0
+        p0 = entries[0][2]
+        self.dtype, self.device = p0.dtype, p0.device
+        self.qualnames = []
+        for mod, name, p, qual in entries:
+            self.specs.append((mod, name, tuple(p.shape), p.numel(), off))
+            self.qualnames.append(qual)
+            off += _round_up(p.numel(), 8)  # 16-byte aligned starts (bulk-copy friendly)
+        self.numel = off
+        self.padded = _round_up(off, self.ws * self.ALIGN)
+        self.shard_numel = self.padded // self.ws
+        lo, hi = self.rank * self.shard_numel, (self.rank + 1) * self.shard_numel
+        shard = torch.zeros(self.shard_numel, dtype=self.dtype, device=self.device)
+        with torch.no_grad():
+            for (mod, name, shape, n, o), (_, _, p, _q) in zip(self.specs, entries):
+                a, b = max(o, lo), min(o + n, hi)
+                if a < b:
+                    shard[a - lo:b - lo].copy_(p.detach().reshape(-1)[a - o:b - o])
+                del mod._parameters[name]
+                setattr(mod, name, None)
+        self.shard = nn.Parameter(shard, requires_grad=trainable)
+        self.full: Optional[torch.Tensor] = None
+        self.acc: Optional[torch.Tensor] = None  # fp32 full-size local accumulation (sync_each_batch=False)
+
+    def install(self, full: torch.Tensor, as_leaves: bool) -> List[torch.Tensor]:
+        """Point the modules' weights at views of `full`; optionally as autograd leaves."""
+        self.full = full
+        leaves = []
+        for mod, name, shape, n, o in self.specs:
+            v = full[o:o + n].view(shape)
+            if as_leaves and self.trainable:
+                v = v.detach().requires_grad_(True)
+                leaves.append(v)
+            setattr(mod, name, v)
+        return leaves
+
+    def flat_grad(self, grads: List[Optional[torch.Tensor]], out: torch.Tensor) -> torch.Tensor:
+        """Write per-parameter grads into the flat layout (zeros where a grad is missing)."""
+        for (mod, name, shape, n, o), g in zip(self.specs, grads):
+            if g is None:
+                out[o:o + n].zero_()
+            else:
+                out[o:o + n].copy_(g.reshape(-1))
+        return out
+
+
+class FsdpUnit:
+    def __init__(self, name: str, roots, group, exclude=()):
+        # roots: list of (qualified prefix, module) whose parameters belong to this unit
+        self.name = name
+        excluded = set()
+        for m in exclude:
+            excluded.update(id(p) for p in m.parameters())
+        train, frozen = [], []
+        for prefix, root in roots:
+            for mname, mod in root.named_modules():
+                for pname, p in list(mod._parameters.items()):
+                    if p is None or id(p) in excluded:
+                        continue
+                    qual = ".".join(x for x in (prefix, mname, pname) if x)
+                    (train if p.requires_grad else frozen).append((mod, pname, p, qual))
+        self.groups: List[FlatParamGroup] = []
+        if train:
+            self.groups.append(FlatParamGroup(train, group, True))
+        if frozen:
+            self.groups.append(FlatParamGroup(frozen, group, False))
+        self.local_params = [p for m in exclude for p in m.parameters()]
+        self.buffers: Optional[List[torch.Tensor]] = None   # gathered flat buffers currently held
+        self.ready_event = None
+
+    @property
+    def trainable_group(self) -> Optional[FlatParamGroup]:
+        for g in self.groups:
+            if g.trainable:
+                return g
+        return None
+
+
+class _BufferPool:
+    """Round-robin pool of full-size flat buffers shared by the decoder-block units."""
+
+    def __init__(self, sizes, dtype, device, slots: int):
+        self.slots = [[torch.empty(s, dtype=dtype, device=device) for s in sizes] for _ in range(slots)]
+        self.free_events = [None] * slots
+        self.owner = [None] * slots
+        self.next = 0
+
+    def acquire(self, owner):
+        for _ in range(len(self.slots)):
+            i = self.next
+            self.next = (self.next + 1) % len(self.slots)
+            if self.owner[i] is None:
+                self.owner[i] = owner
+                return i
+        raise RuntimeError("parameter buffer pool exhausted (a unit was not released)")
+
+    def release(self, i, event):
+        self.owner[i] = None
+        self.free_events[i] = event
+
+
+class _LayerFn(torch.autograd.Function):
+    """One decoder block: graph-free forward, recompute + backward + gradient reduction."""
+
+    @staticmethod
+    def forward(ctx, runner, idx, batch, x, *shards):
+        ctx.runner, ctx.idx, ctx.batch = runner, idx, batch
+        ctx.save_for_backward(x)
+        layer = runner.model.model.layers[idx]
+        with torch.no_grad():
+            return layer(x, batch)
+
+    @staticmethod
+    def backward(ctx, gout):
+        runner: "ShardedMixtral" = ctx.runner
+        idx, batch = ctx.idx, ctx.batch
+        (x,) = ctx.saved_tensors
+        unit = runner.units[idx]
+        runner._acquire(idx, backward=True)
+        runner._prefetch(idx - 1, backward=True)
+        leaves = []
+        for g, buf in zip(unit.groups, unit.buffers):
+            leaves += g.install(buf, as_leaves=True)
+        local = [p for p in unit.local_params if p.requires_grad]
+        xin = x.detach().requires_grad_(True)
+        layer = runner.model.model.layers[idx]
+        with torch.enable_grad():
+            y = layer(xin, batch)
+        grads = torch.autograd.grad(y, [xin] + leaves + local, gout, allow_unused=True)
+        dx = grads[0]
+        runner._reduce_unit_grads(unit, list(grads[1:1 + len(leaves)]))
+        for p, g in zip(local, grads[1 + len(leaves):]):
+            if g is not None:
+                p.grad = g if p.grad is None else p.grad.add_(g)
+        runner._release(idx)
+        return (None, None, None, dx) + (None,) * (len(ctx.needs_input_grad) - 4)
+
+
+class ShardedMixtral:
+    """Runs a `MixtralForCausalLM` with sharded dense parameters and block recomputation.
+
+    Installed as `model.layer_runner`; `model(input_ids, labels=...)` then goes
+    through `embed` / `run_layer` / `head` below.
+    """
+
+    def __init__(self, model: MixtralForCausalLM, shard_group=None, replicate_group=None,
+                 expert_dp_group=None, world_group=None, shard_experts: bool = False,
+                 sync_each_batch: bool = False, pool_slots: int = 3):
+        self.model = model
+        self.shard_group, self.replicate_group = shard_group, replicate_group
+        self.expert_dp_group, self.world_group = expert_dp_group, world_group
+        self.sync_each_batch = sync_each_batch
+        self.ws = coll.group_size(shard_group)
+        self.rep = coll.group_size(replicate_group)
+        layers = model.model.layers
+        self.units: List[FsdpUnit] = []
+        for i, layer in enumerate(layers):
+            exclude = () if shard_experts else (layer.block_sparse_moe,)
+            self.units.append(FsdpUnit(f"layers.{i}", [(f"model.layers.{i}", layer)], shard_group, exclude))
+        self.root = FsdpUnit("root", [("model.embed_tokens", model.model.embed_tokens),
+                                      ("model.norm", model.model.norm), ("lm_head", model.lm_head)], shard_group)
+        # register the flat shards so that model.parameters() / the optimizer see them
+        shards = nn.ParameterList()
+        for u in self.units + [self.root]:
+            for g in u.groups:
+                shards.append(g.shard)
+        model._flat_shards = shards
+        dev = next(model.parameters()).device
+        self.device = dev
+        self.is_cuda = dev.type == "cuda"
+        self.comm_stream = torch.cuda.Stream(device=dev) if (self.is_cuda and self.ws > 1) else None
+        self.pool = None
+        if self.ws > 1:
+            n_groups = max(len(u.groups) for u in self.units)
+            sizes = [max((u.groups[j].padded for u in self.units if len(u.groups) > j), default=0) for j in range(n_groups)]
+            dts = self.units[0].groups[0].dtype
+            self.pool = _BufferPool(sizes, dts, dev, pool_slots)
+            self.root_buffers = [torch.empty(g.padded, dtype=g.dtype, device=dev) for g in self.root.groups]
+        self._slot = {}
+        self._root_leaves: List[torch.Tensor] = []
+        self._grad_tmp = {}
+        model.layer_runner = self
+
+    # ------------------------------------------------------------------ buffers
+    def _gather_into(self, unit: FsdpUnit, buffers):
+        for g, buf in zip(unit.groups, buffers):
+            coll.all_gather_flat(buf[:g.padded], g.shard.data, g.group)
+
+    def _start_gather(self, idx: int):
+        """Issue the all-gather of unit idx (on the side stream when there is one)."""
+        unit = self.units[idx]
+        if unit.buffers is not None or idx in self._slot:
+            return
+        if self.ws == 1:
+            unit.buffers = [g.shard.data for g in unit.groups]
+            return
+        slot = self.pool.acquire(idx)
+        self._slot[idx] = slot
+        bufs = self.pool.slots[slot][:len(unit.groups)]
+        if self.comm_stream is not None:
+            ev = self.pool.free_events[slot]
+            # the shards may have just been written by the optimizer on the compute stream
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.comm_stream):
+                if ev is not None:
+                    self.comm_stream.wait_event(ev)
+                self._gather_into(unit, bufs)
+                unit.ready_event = torch.cuda.Event()
+                unit.ready_event.record(self.comm_stream)
+        else:
+            self._gather_into(unit, bufs)
+        unit.buffers = bufs
+
+    def _acquire(self, idx: int, backward: bool = False):
+        unit = self.units[idx]
+        self._start_gather(idx)
+        if unit.ready_event is not None:
+            torch.cuda.current_stream().wait_event(unit.ready_event)
+            unit.ready_event = None
+        if not backward:
+            for g, buf in zip(unit.groups, unit.buffers):
+                g.install(buf, as_leaves=False)
+
+    def _prefetch(self, idx: int, backward: bool = False):
+        if 0 <= idx < len(self.units):
+            self._start_gather(idx)
+
+    def _release(self, idx: int):
+        unit = self.units[idx]
+        if self.ws == 1 or unit.buffers is None:
+            unit.buffers = None if self.ws > 1 else unit.buffers
+            return
+        ev = None
+        if self.is_cuda:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+        self.pool.release(self._slot.pop(idx), ev)
+        unit.buffers = None
+
+    # ------------------------------------------------------------------ gradients
+    def _reduce_unit_grads(self, unit: FsdpUnit, grads):
+        g = unit.trainable_group
+        if g is None:
+            return
+        scale = 1.0 / (self.ws * self.rep)
+        if self.sync_each_batch or self.ws == 1:
+            key = (g.padded, g.dtype)
+            tmp = self._grad_tmp.get(key)
+            if tmp is None:
+                tmp = self._grad_tmp[key] = torch.zeros(g.padded, dtype=g.dtype, device=self.device)
+            g.flat_grad(grads, tmp)
+            if g.shard.grad is None:
+                g.shard.grad = torch.zeros_like(g.shard.data)
+            coll.reduce_scatter_flat(g.shard.grad, tmp, g.group, scale=scale, accumulate=True)
+        else:
+            if g.acc is None:
+                g.acc = torch.zeros(g.padded, dtype=torch.float32, device=self.device)
+                g._acc_dirty = False
+            for (mod, name, shape, n, o), gr in zip(g.specs, grads):
+                if gr is not None:
+                    g.acc[o:o + n].add_(gr.reshape(-1))
+            g._acc_dirty = True
+
+    def reduce_gradients(self):
+        """Finish the gradient reductions of one optimizer step (call after the last backward)."""
+        scale = 1.0 / (self.ws * self.rep)
+        for u in self.units + [self.root]:
+            g = u.trainable_group
+            if g is None:
+                continue
+            if g.acc is not None and getattr(g, "_acc_dirty", False):
+                if g.shard.grad is None:
+                    g.shard.grad = torch.zeros_like(g.shard.data)
+                coll.reduce_scatter_flat(g.shard.grad, g.acc, g.group, scale=scale, accumulate=True)
+                g.acc.zero_()
+                g._acc_dirty = False
+            if self.rep > 1 and g.shard.grad is not None:
+                coll.all_reduce_flat(g.shard.grad, self.replicate_group)
+        # router: mean over all ranks; experts (and their LoRA factors): mean over expert replicas
+        router_grads, expert_grads = [], []
+        for u in self.units:
+            for p in u.local_params:
+                if p.grad is None:
+                    continue
+                (expert_grads if getattr(p, "_is_expert_param", False) else router_grads).append(p.grad)
+        wg = self.world_group
+        if router_grads and coll.group_size(wg) > 1:
+            _all_reduce_list(router_grads, wg, 1.0 / coll.group_size(wg))
+        if expert_grads and coll.group_size(self.expert_dp_group) > 1:
+            _all_reduce_list(expert_grads, self.expert_dp_group, 1.0 / coll.group_size(self.expert_dp_group))
+
+    # ------------------------------------------------------------------ model hooks
+    def _install_root(self):
+        root = self.root
+        if self.ws == 1:
+            bufs = [g.shard.data for g in root.groups]
+        else:
+            bufs = self.root_buffers
+            self._gather_into(root, bufs)
+        need_grad = torch.is_grad_enabled()
+        self._root_leaves = []
+        for g, buf in zip(root.groups, bufs):
+            self._root_leaves += g.install(buf, as_leaves=need_grad)
+
+    def embed(self, ids):
+        self._install_root()
+        self._prefetch(0)
+        return ops.embedding(ids, self.model.model.embed_tokens.weight)
+
+    def run_layer(self, idx, layer, x, batch: PackedBatch):
+        self._acquire(idx)
+        self._prefetch(idx + 1)
+        if torch.is_grad_enabled():
+            shards = [g.shard for g in self.units[idx].groups if g.trainable]
+            local = [p for p in self.units[idx].local_params if p.requires_grad]
+            y = _LayerFn.apply(self, idx, batch, x, *shards, *local)
+        else:
+            y = layer(x, batch)
+        last = idx == len(self.units) - 1
+        if not (last and torch.is_grad_enabled()):
+            self._release(idx)
+        return y
+
+    def head(self, x, lab, batch, return_logits=False) -> CausalLMOutput:
+        return self.model.head(x, lab, batch, return_logits)
+
+    def finish_microbatch(self):
+        """Collect the root unit's gradients after `loss.backward()`."""
+        g = self.root.trainable_group
+        if g is not None and self._root_leaves:
+            grads = [leaf.grad for leaf in self._root_leaves]
+            self._reduce_unit_grads(self.root, grads)
+            for leaf in self._root_leaves:
+                leaf.grad = None
+        self._root_leaves = []
+        for idx in list(self._slot):
+            self._release(idx)
+
+    def zero_grad(self):
+        for p in self.model.parameters():
+            p.grad = None
+
+    # ------------------------------------------------------------------ unsharded views (checkpoint export)
+    def full_state(self, unit: FsdpUnit, grads: bool = False):
+        """Gathered {qualified name: tensor} of one unit's dense parameters (or their grads), on every rank."""
+        out = {}
+        for g in unit.groups:
+            src = g.shard.data
+            if grads:
+                if not g.trainable:
+                    continue
+                src = g.shard.grad if g.shard.grad is not None else torch.zeros_like(g.shard.data)
+            full = torch.empty(g.padded, dtype=src.dtype, device=g.device)
+            coll.all_gather_flat(full, src.contiguous(), g.group)
+            for (mod, name, shape, n, o), qual in zip(g.specs, g.qualnames):
+                out[qual] = full[o:o + n].view(shape).clone()
+        return out
+
+    def all_units(self):
+        return self.units + [self.root]
+
+
+def _all_reduce_list(tensors, group, scale: float):
+    flat = torch.cat([t.reshape(-1).float() for t in tensors])
+    dist.all_reduce(flat, group=group)
+    flat.mul_(scale)
+    off = 0
+    for t in tensors:
+        n = t.numel()
+        t.copy_(flat[off:off + n].view_as(t))
+        off += n

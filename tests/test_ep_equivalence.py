@@ -1,0 +1,133 @@
+"""Expert-parallel / sharded runs reproduce the gradients of the unsharded model.
+
+Tiny Mixtral (2 layers, hidden 256, 4 heads / 2 KV heads, 4 experts of FFN 512,
+top-2, vocab 1024), fp32, two gloo ranks on CPU, 2 sequences of 128 tokens per
+rank with the first 40% of every sequence label-masked.  The reference for every
+mode is a single process that owns all experts and averages the two ranks' losses.
+"""
+import pytest
+import torch
+
+from dist_utils import run_distributed
+from moe_distributed_training_b200 import MixtralConfig
+from moe_distributed_training_b200.data.synthetic import SyntheticInstructionDataset, collate_packed
+
+
+def _rank_batch(cfg, rank):
+    ds = SyntheticInstructionDataset(cfg.vocab_size, 2, fixed_len=128, seed=0, rank=rank)
+    return collate_packed([ds[0], ds[1]])
+
+
+def _collect(engine):
+    """{qualified name: full gradient} for dense params; local MoE grads keyed by module path."""
+    out = {}
+    for u in engine.runner.all_units():
+        out.update(engine.runner.full_state(u, grads=True))
+    for name, p in engine.model.named_parameters():
+        if ".block_sparse_moe." in name and p.grad is not None:
+            out[name] = p.grad.clone()
+    return {k: v.double() for k, v in out.items()}
+
+
+def _run(rank, world, mode, steps):
+    from moe_distributed_training_b200.train.engine import build_engine
+    torch.manual_seed(0)
+    cfg = MixtralConfig.tiny()
+    kw = dict(dtype=torch.float32, device_type="cpu", learning_rate=1e-3, max_grad_norm=None, seed=0,
+              lr_scheduler_type="constant")
+    if mode == "ep":
+        eng = build_engine(cfg, ep_size=world, **kw)
+    elif mode == "tp":
+        eng = build_engine(cfg, ep_size=2, use_tp_sharding=True, **kw)
+    elif mode == "fsdp":
+        eng = build_engine(cfg, ep_size=1, **kw)
+    elif mode == "ep-lora":
+        eng = build_engine(cfg, ep_size=world, use_lora="all", **kw)
+    else:
+        raise ValueError(mode)
+    if mode == "tp":
+        # tensor-parallel peers see the same batch (train_accelerate_fsdp2.py:346-382)
+        dp_rank = rank // 2
+        mbs = [_rank_batch(cfg, dp_rank)]
+    else:
+        mbs = [_rank_batch(cfg, rank)]
+    losses = []
+    for s in range(steps):
+        loss = eng.forward_backward(mbs[0], 1.0)
+        eng.runner.reduce_gradients()
+        losses.append(float(loss))
+        if s < steps - 1:
+            eng.optimizer.step(); eng.optimizer.zero_grad(set_to_none=True)
+    grads = _collect(eng)
+    ep_rank = rank if mode != "tp" else rank % 2
+    return losses, grads, ep_rank
+
+
+def _reference(n_batches, use_lora="none"):
+    from moe_distributed_training_b200.train.engine import build_engine
+    torch.manual_seed(0)
+    cfg = MixtralConfig.tiny()
+    eng = build_engine(cfg, dtype=torch.float32, device_type="cpu", max_grad_norm=None, seed=0, use_lora=use_lora)
+    losses = [float(eng.forward_backward(_rank_batch(cfg, r), 1.0 / n_batches)) for r in range(n_batches)]
+    eng.runner.reduce_gradients()
+    return losses, _collect(eng), cfg
+
+
+def _expert_slice(ref, name, cfg, ep_rank, ep, tp=False):
+    g = ref[name]
+    E, F, H = cfg.num_local_experts, cfg.intermediate_size, cfg.hidden_size
+    if "lora_A" in name or "lora_B" in name:
+        El = E // ep
+        return g[ep_rank * El:(ep_rank + 1) * El]
+    if tp:
+        Fl = F // ep
+        return g.view(E, F, H)[:, ep_rank * Fl:(ep_rank + 1) * Fl].reshape(-1, H)
+    El = E // ep
+    return g.view(E, F, H)[ep_rank * El:(ep_rank + 1) * El].reshape(-1, H)
+
+
+def _compare(ref_grads, grads, cfg, ep_rank, ep, tp=False, atol=2e-6):
+    assert set(grads) == set(ref_grads), set(grads) ^ set(ref_grads)
+    for name, g in grads.items():
+        r = ref_grads[name]
+        if ".experts." in name:
+            r = _expert_slice(ref_grads, name, cfg, ep_rank, ep, tp)
+        assert g.shape == r.shape, (name, g.shape, r.shape)
+        err = (g - r).abs().max().item()
+        assert err <= atol + 1e-4 * r.abs().max().item(), f"{name}: max abs err {err}"
+
+
+def test_ep2_matches_unsharded():
+    ref_losses, ref_grads, cfg = _reference(2)
+    res = run_distributed(_run, 2, "ep", 1)
+    for rank, (losses, grads, ep_rank) in enumerate(res):
+        assert abs(losses[0] - ref_losses[rank]) < 1e-5
+        _compare(ref_grads, grads, cfg, ep_rank, 2)
+
+
+def test_fsdp2_no_ep_matches_unsharded():
+    ref_losses, ref_grads, cfg = _reference(2)
+    res = run_distributed(_run, 2, "fsdp", 1)
+    for rank, (losses, grads, _) in enumerate(res):
+        assert abs(losses[0] - ref_losses[rank]) < 1e-5
+        # experts were sharded like dense parameters: full_state returned whole tensors
+        for name, g in grads.items():
+            err = (g - ref_grads[name]).abs().max().item()
+            assert err < 2e-6 + 1e-4 * ref_grads[name].abs().max().item(), name
+
+
+def test_ep2_lora_all_matches_unsharded():
+    ref_losses, ref_grads, cfg = _reference(2, use_lora="all")
+    res = run_distributed(_run, 2, "ep-lora", 1)
+    for rank, (losses, grads, ep_rank) in enumerate(res):
+        assert abs(losses[0] - ref_losses[rank]) < 1e-5
+        _compare(ref_grads, grads, cfg, ep_rank, 2)
+
+
+@pytest.mark.slow
+def test_tp2_dp2_matches_unsharded():
+    ref_losses, ref_grads, cfg = _reference(2)
+    res = run_distributed(_run, 4, "tp", 1)
+    for rank, (losses, grads, ep_rank) in enumerate(res):
+        assert abs(losses[0] - ref_losses[rank // 2]) < 1e-5
+        _compare(ref_grads, grads, cfg, ep_rank, 2, tp=True)
