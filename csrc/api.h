@@ -1,0 +1,86 @@
+// C launch interface of the sm_100a kernels.  Every function enqueues work on `stream` and returns
+// 0 on success (negative: rejected arguments or a CUDA launch error).  Pointers are device pointers.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- GEMM family (gemm_sm100.cu) -------------------------------------------------------------
+typedef struct MdtGemmDesc {
+  int mode;            // 0 dense, 1 grouped rows, 2 grouped depth (weight gradient)
+  int M, N, K;         // mode 0/1: C is [M(or capacity), N], depth K.  mode 2: C_g is [M, N], depth = rows of g (K if offsets == NULL)
+  int G;               // number of groups (1 for dense)
+  const int* offsets;  // [G+1] device: first row of every group (multiples of 128); mode 0: NULL
+  long long capacity_rows;  // mode 1: host-known upper bound of offsets[G]
+  // A operand: bf16 [a_rows, a_cols], row stride lda.  a_mn = 0: rows are M, cols are depth.  a_mn = 1: rows are depth, cols are M.
+  const void* A; long long a_rows, a_cols, lda; int a_mn;
+  // B operand: bf16 [G, b_rows, b_cols].  b_mn = 0: rows are N, cols are depth.  b_mn = 1: rows are depth, cols are N.
+  const void* B; const void* B2; long long b_rows, b_cols, ldb, b_group_stride; int b_mn;
+  int dual;            // 1: B and B2 are gate / up matrices, the epilogue writes silu(A*B) * (A*B2)
+  // optional second depth segment (LoRA): C += A_l * B_l with depth K_l
+  int K_l;
+  const void* A_l; long long al_rows, al_cols, lda_l; int a_mn_l;
+  const void* B_l; const void* B2_l; long long bl_rows, bl_cols, ldb_l, bl_group_stride; int b_mn_l;
+  // output
+  void* C; void* C2; void* C3;   // dual mode: C = h, optional C2 = gate, C3 = up (all bf16)
+  long long ldc, c_group_stride;
+  int c_fp32;          // C is fp32 instead of bf16
+  int accumulate;      // C += alpha * (A*B) instead of C = alpha * (A*B)
+  float alpha;
+  int* status;         // optional device word: set to a non-zero code if a wait inside the kernel gave up
+} MdtGemmDesc;
+
+int mdt_gemm(const MdtGemmDesc* desc, cudaStream_t stream);
+long long mdt_gemm_launch_count(void);
+
+// ---- element-wise / normalisation / loss / optimizer (elementwise.cu) --------------------------
+int mdt_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps, cudaStream_t s);
+int mdt_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx, float* dw_partial,
+                    int rows, int cols, int n_partial, cudaStream_t s);
+int mdt_rope(const void* x, void* y, const int* positions, int tokens, int heads, int head_dim, float theta,
+             int inverse, cudaStream_t s);
+int mdt_swiglu_bwd(const void* g, const void* u, const void* dh, void* dg, void* du, long long n, cudaStream_t s);
+int mdt_swiglu_fwd(const void* g, const void* u, void* h, long long n, cudaStream_t s);
+int mdt_embedding(const void* table, const long long* ids, void* out, int tokens, int cols, cudaStream_t s);
+int mdt_embedding_bwd(const void* dout, const long long* ids, float* dtable, int tokens, int cols, cudaStream_t s);
+// in place: logits (bf16, [rows, vocab]) become d(loss_sum)/dlogits * grad_scale; loss_sum/count accumulate
+int mdt_cross_entropy(void* logits, const long long* labels, float* loss_sum, float* count, int rows, int vocab,
+                      long long ld, int ignore_index, float grad_scale, cudaStream_t s);
+typedef struct MdtAdamTensor { void* p; const void* g; void* m; void* v; long long n; int p_fp32, g_fp32, s_fp32; } MdtAdamTensor;
+int mdt_adamw(const MdtAdamTensor* tensors_device, int num_tensors, long long max_n, float lr, float beta1, float beta2,
+              float eps, float weight_decay, float bc1, float bc2, float grad_scale, cudaStream_t s);
+int mdt_sumsq(const void* x, long long n, int fp32, float* out_accum, cudaStream_t s);
+int mdt_axpby(void* y, const void* x, long long n, float a, float b, int y_fp32, int x_fp32, cudaStream_t s);
+
+// ---- router and permutation (router.cu) -----------------------------------------------------------
+int mdt_router_fwd(const void* x, const void* w, void* scores, void* weights, int* idx, int tokens, int hidden,
+                   int experts, int top_k, int normalize, cudaStream_t s);
+int mdt_router_bwd(const void* x, const void* w, const void* scores, const void* weights, const int* idx,
+                   const void* dweights, const void* dscores, void* dx, float* dw, int tokens, int hidden, int experts,
+                   int top_k, int normalize, int accumulate_dx, cudaStream_t s);
+// counting sort of slots by expert id with block-padded groups; all outputs on device
+int mdt_make_plan(const int* expert_ids, int num_slots, int num_experts, int block, int capacity, int* counts,
+                  int* padded_offsets, int* dest_row, int* src_slot, int* scratch, cudaStream_t s);
+int mdt_gather_rows(const void* x, const int* src_slot, const int* padded_offsets, int num_experts, const void* slot_scale,
+                    void* out, int capacity, int cols, int top_k, cudaStream_t s);
+int mdt_combine_rows(const void* y, const int* dest_row, const void* weights, void* out, int tokens, int cols, int top_k,
+                     cudaStream_t s);
+int mdt_combine_wgrad(const void* y, const int* dest_row, const void* dout, void* dweights, int tokens, int cols, int top_k,
+                      cudaStream_t s);
+
+// ---- attention (attention.cu) -----------------------------------------------------------------------
+int mdt_attention_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens,
+                      int num_seqs, int total_tokens, int max_seqlen, int heads_q, int heads_kv, int head_dim,
+                      float scale, cudaStream_t s);
+int mdt_attention_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                      void* dq, void* dk, void* dv, float* delta, const int* cu_seqlens, int num_seqs, int total_tokens,
+                      int max_seqlen, int heads_q, int heads_kv, int head_dim, float scale, cudaStream_t s);
+
+long long mdt_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif

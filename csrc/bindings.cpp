@@ -1,0 +1,251 @@
+// Python bindings: torch tensors in, C launch interface (api.h) out.  No math happens here.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <optional>
+#include <vector>
+
+#include "api.h"
+
+extern "C" long long mdt_elementwise_launch_count();
+extern "C" long long mdt_router_launch_count();
+extern "C" long long mdt_attention_launch_count();
+extern "C" long long mdt_comm_launch_count();
+
+using torch::Tensor;
+typedef std::optional<Tensor> OptTensor;
+
+static cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+static void check(int rc, const char* what) { TORCH_CHECK(rc == 0, what, " failed with code ", rc); }
+static const void* cptr(const OptTensor& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+static void* mptr(const OptTensor& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+#define CHECK_BF16(t) TORCH_CHECK((t).scalar_type() == at::kBFloat16 && (t).is_cuda(), #t " must be a CUDA bf16 tensor")
+
+static void fill_operand(const Tensor& t, long long& rows, long long& cols, long long& ld) {
+  TORCH_CHECK(t.dim() == 2 && t.stride(1) == 1, "operand must be 2-D with unit inner stride");
+  rows = t.size(0); cols = t.size(1); ld = t.stride(0);
+}
+static void fill_operand3(const Tensor& t, long long& rows, long long& cols, long long& ld, long long& gs) {
+  if (t.dim() == 2) { fill_operand(t, rows, cols, ld); gs = rows * ld; return; }
+  TORCH_CHECK(t.dim() == 3 && t.stride(2) == 1, "B must be [G, rows, cols] with unit inner stride");
+  rows = t.size(1); cols = t.size(2); ld = t.stride(1); gs = t.stride(0);
+}
+
+// C = alpha * op(A) op(B) (+ LoRA segment) with the options of MdtGemmDesc; see csrc/api.h
+void gemm(int64_t mode, const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, Tensor& C, int64_t M, int64_t N, int64_t K,
+          int64_t G, const OptTensor& offsets, int64_t capacity_rows, const OptTensor& B2, const OptTensor& A_l,
+          bool a_mn_l, const OptTensor& B_l, const OptTensor& B2_l, bool b_mn_l, int64_t K_l, const OptTensor& C2,
+          const OptTensor& C3, bool accumulate, double alpha, const OptTensor& status) {
+  CHECK_BF16(A); CHECK_BF16(B);
+  c10::cuda::CUDAGuard guard(A.device());
+  MdtGemmDesc d;
+  memset(&d, 0, sizeof(d));
+  d.mode = (int)mode; d.M = (int)M; d.N = (int)N; d.K = (int)K; d.G = (int)G;
+  d.offsets = offsets.has_value() ? offsets->data_ptr<int>() : nullptr;
+  d.capacity_rows = capacity_rows;
+  d.A = A.data_ptr(); fill_operand(A, d.a_rows, d.a_cols, d.lda); d.a_mn = a_mn;
+  d.B = B.data_ptr(); fill_operand3(B, d.b_rows, d.b_cols, d.ldb, d.b_group_stride); d.b_mn = b_mn;
+  d.dual = B2.has_value();
+  d.B2 = cptr(B2);
+  d.K_l = (int)K_l;
+  if (K_l > 0) {
+    TORCH_CHECK(A_l.has_value() && B_l.has_value(), "LoRA segment needs A_l and B_l");
+    d.A_l = A_l->data_ptr(); fill_operand(*A_l, d.al_rows, d.al_cols, d.lda_l); d.a_mn_l = a_mn_l;
+    d.B_l = B_l->data_ptr(); fill_operand3(*B_l, d.bl_rows, d.bl_cols, d.ldb_l, d.bl_group_stride); d.b_mn_l = b_mn_l;
+    d.B2_l = cptr(B2_l);
+    TORCH_CHECK(!d.dual || B2_l.has_value(), "dual mode with LoRA needs B2_l");
+  }
+  TORCH_CHECK(C.is_cuda() && C.stride(-1) == 1, "C must be a CUDA tensor with unit inner stride");
+  d.C = C.data_ptr(); d.C2 = mptr(C2); d.C3 = mptr(C3);
+  d.ldc = C.stride(-2);
+  d.c_group_stride = C.dim() == 3 ? C.stride(0) : 0;
+  d.c_fp32 = C.scalar_type() == at::kFloat;
+  TORCH_CHECK(d.c_fp32 || C.scalar_type() == at::kBFloat16, "C must be bf16 or fp32");
+  d.accumulate = accumulate; d.alpha = (float)alpha;
+  d.status = status.has_value() ? status->data_ptr<int>() : nullptr;
+  check(mdt_gemm(&d, cur_stream()), "mdt_gemm");
+}
+
+std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
+  CHECK_BF16(x); CHECK_BF16(w);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto x2 = x.reshape({-1, x.size(-1)}).contiguous();
+  auto y = torch::empty_like(x2);
+  auto rstd = torch::empty({x2.size(0)}, x.options().dtype(at::kFloat));
+  check(mdt_rmsnorm_fwd(x2.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), (int)x2.size(0), (int)x2.size(1), (float)eps, cur_stream()), "rmsnorm_fwd");
+  return {y.view(x.sizes()), rstd};
+}
+std::vector<Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& w, const Tensor& dy, const Tensor& rstd) {
+  c10::cuda::CUDAGuard guard(x.device());
+  auto x2 = x.reshape({-1, x.size(-1)}).contiguous();
+  auto dy2 = dy.reshape({-1, x.size(-1)}).contiguous();
+  auto dx = torch::empty_like(x2);
+  const int rows = (int)x2.size(0), cols = (int)x2.size(1);
+  const int np = rows < 148 ? (rows < 1 ? 1 : rows) : 148;
+  auto dwp = torch::empty({np, cols}, x.options().dtype(at::kFloat));
+  check(mdt_rmsnorm_bwd(x2.data_ptr(), w.data_ptr(), dy2.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(), dwp.data_ptr<float>(), rows, cols, np, cur_stream()), "rmsnorm_bwd");
+  return {dx.view(x.sizes()), dwp};
+}
+Tensor rope(const Tensor& x, const Tensor& positions, double theta, bool inverse) {
+  CHECK_BF16(x);
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 3 && positions.scalar_type() == at::kInt);
+  auto xc = x.contiguous();
+  auto y = torch::empty_like(xc);
+  check(mdt_rope(xc.data_ptr(), y.data_ptr(), positions.data_ptr<int>(), (int)x.size(0), (int)x.size(1), (int)x.size(2), (float)theta, inverse, cur_stream()), "rope");
+  return y;
+}
+Tensor swiglu_fwd(const Tensor& g, const Tensor& u) {
+  c10::cuda::CUDAGuard guard(g.device());
+  auto h = torch::empty_like(g);
+  check(mdt_swiglu_fwd(g.data_ptr(), u.data_ptr(), h.data_ptr(), g.numel(), cur_stream()), "swiglu_fwd");
+  return h;
+}
+std::vector<Tensor> swiglu_bwd(const Tensor& g, const Tensor& u, const Tensor& dh) {
+  c10::cuda::CUDAGuard guard(g.device());
+  auto dg = torch::empty_like(g), du = torch::empty_like(u);
+  check(mdt_swiglu_bwd(g.data_ptr(), u.data_ptr(), dh.data_ptr(), dg.data_ptr(), du.data_ptr(), g.numel(), cur_stream()), "swiglu_bwd");
+  return {dg, du};
+}
+Tensor embedding(const Tensor& table, const Tensor& ids) {
+  CHECK_BF16(table);
+  c10::cuda::CUDAGuard guard(table.device());
+  TORCH_CHECK(ids.scalar_type() == at::kLong && ids.is_contiguous());
+  auto out = torch::empty({ids.numel(), table.size(1)}, table.options());
+  check(mdt_embedding(table.data_ptr(), ids.data_ptr<int64_t>() ? (const long long*)ids.data_ptr<int64_t>() : nullptr, out.data_ptr(), (int)ids.numel(), (int)table.size(1), cur_stream()), "embedding");
+  return out;
+}
+void embedding_bwd(const Tensor& dout, const Tensor& ids, Tensor& dtable) {
+  c10::cuda::CUDAGuard guard(dout.device());
+  TORCH_CHECK(dtable.scalar_type() == at::kFloat && dout.is_contiguous());
+  check(mdt_embedding_bwd(dout.data_ptr(), (const long long*)ids.data_ptr<int64_t>(), dtable.data_ptr<float>(), (int)ids.numel(), (int)dout.size(1), cur_stream()), "embedding_bwd");
+}
+// logits are overwritten with d(mean loss)/dlogits * grad_scale; returns [loss_sum, count]
+Tensor cross_entropy(Tensor& logits, const Tensor& labels, int64_t ignore_index, double grad_scale) {
+  CHECK_BF16(logits);
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1 && labels.scalar_type() == at::kLong && labels.is_contiguous());
+  auto out = torch::zeros({2}, logits.options().dtype(at::kFloat));
+  check(mdt_cross_entropy(logits.data_ptr(), (const long long*)labels.data_ptr<int64_t>(), out.data_ptr<float>(), out.data_ptr<float>() + 1,
+                          (int)logits.size(0), (int)logits.size(1), logits.stride(0), (int)ignore_index, (float)grad_scale, cur_stream()), "cross_entropy");
+  return out;
+}
+void adamw(std::vector<Tensor> ps, std::vector<Tensor> gs, std::vector<Tensor> ms, std::vector<Tensor> vs, double lr, double b1,
+           double b2, double eps, double wd, int64_t step, double grad_scale) {
+  if (ps.empty()) return;
+  c10::cuda::CUDAGuard guard(ps[0].device());
+  std::vector<MdtAdamTensor> host(ps.size());
+  long long max_n = 0;
+  for (size_t i = 0; i < ps.size(); ++i) {
+    TORCH_CHECK(ps[i].is_contiguous() && gs[i].is_contiguous() && ms[i].is_contiguous() && vs[i].is_contiguous());
+    host[i] = {ps[i].data_ptr(), gs[i].data_ptr(), ms[i].data_ptr(), vs[i].data_ptr(), ps[i].numel(),
+               ps[i].scalar_type() == at::kFloat, gs[i].scalar_type() == at::kFloat, ms[i].scalar_type() == at::kFloat};
+    max_n = std::max<long long>(max_n, ps[i].numel());
+  }
+  auto bytes = (int64_t)(host.size() * sizeof(MdtAdamTensor));
+  auto staging = torch::empty({bytes}, torch::dtype(torch::kUInt8).pinned_memory(true));
+  memcpy(staging.data_ptr(), host.data(), bytes);
+  auto dev = staging.to(ps[0].device(), /*non_blocking=*/true);
+  const float bc1 = 1.0f - (float)std::pow(b1, (double)step), bc2 = 1.0f - (float)std::pow(b2, (double)step);
+  check(mdt_adamw((const MdtAdamTensor*)dev.data_ptr(), (int)host.size(), max_n, (float)lr, (float)b1, (float)b2, (float)eps, (float)wd, bc1, bc2, (float)grad_scale, cur_stream()), "adamw");
+}
+void sumsq(const Tensor& x, Tensor& out) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && out.scalar_type() == at::kFloat);
+  check(mdt_sumsq(x.data_ptr(), x.numel(), x.scalar_type() == at::kFloat, out.data_ptr<float>(), cur_stream()), "sumsq");
+}
+void axpby(Tensor& y, const Tensor& x, double a, double b) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && y.is_contiguous() && x.numel() == y.numel());
+  check(mdt_axpby(y.data_ptr(), x.data_ptr(), x.numel(), (float)a, (float)b, y.scalar_type() == at::kFloat, x.scalar_type() == at::kFloat, cur_stream()), "axpby");
+}
+
+std::vector<Tensor> router_fwd(const Tensor& x, const Tensor& w, int64_t top_k, bool normalize) {
+  CHECK_BF16(x); CHECK_BF16(w);
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && w.is_contiguous());
+  const int T = (int)x.size(0), H = (int)x.size(1), E = (int)w.size(0);
+  auto scores = torch::empty({T, E}, x.options());
+  auto weights = torch::empty({T, top_k}, x.options());
+  auto idx = torch::empty({T, top_k}, x.options().dtype(at::kInt));
+  check(mdt_router_fwd(x.data_ptr(), w.data_ptr(), scores.data_ptr(), weights.data_ptr(), idx.data_ptr<int>(), T, H, E, (int)top_k, normalize, cur_stream()), "router_fwd");
+  return {scores, weights, idx};
+}
+std::vector<Tensor> router_bwd(const Tensor& x, const Tensor& w, const Tensor& idx, const Tensor& dweights, const OptTensor& dscores,
+                               bool normalize) {
+  c10::cuda::CUDAGuard guard(x.device());
+  const int T = (int)x.size(0), H = (int)x.size(1), E = (int)w.size(0), k = (int)idx.size(1);
+  auto dx = torch::empty_like(x);
+  auto buf = torch::zeros({(int64_t)E * H + (int64_t)T * E}, x.options().dtype(at::kFloat));
+  auto dwc = dweights.contiguous();
+  OptTensor dsc = dscores.has_value() ? OptTensor(dscores->contiguous()) : std::nullopt;
+  check(mdt_router_bwd(x.data_ptr(), w.data_ptr(), nullptr, nullptr, idx.data_ptr<int>(), dwc.data_ptr(), cptr(dsc), dx.data_ptr(),
+                       buf.data_ptr<float>(), T, H, E, k, normalize, 0, cur_stream()), "router_bwd");
+  return {dx, buf.narrow(0, 0, (int64_t)E * H).view({E, H})};
+}
+// returns counts[E], padded_offsets[E+1], dest_row[n], src_slot[capacity]
+std::vector<Tensor> make_plan(const Tensor& expert_ids, int64_t num_experts, int64_t block, int64_t capacity) {
+  c10::cuda::CUDAGuard guard(expert_ids.device());
+  TORCH_CHECK(expert_ids.scalar_type() == at::kInt && expert_ids.is_contiguous());
+  const int n = (int)expert_ids.numel();
+  auto opt = expert_ids.options();
+  auto counts = torch::empty({num_experts}, opt), offs = torch::empty({num_experts + 1}, opt);
+  auto dest = torch::empty({n}, opt), src = torch::empty({capacity}, opt);
+  auto scratch = torch::empty({((n + 255) / 256 + 1) * num_experts}, opt);
+  check(mdt_make_plan(expert_ids.data_ptr<int>(), n, (int)num_experts, (int)block, (int)capacity, counts.data_ptr<int>(), offs.data_ptr<int>(),
+                      dest.data_ptr<int>(), src.data_ptr<int>(), scratch.data_ptr<int>(), cur_stream()), "make_plan");
+  return {counts, offs, dest, src};
+}
+Tensor gather_rows(const Tensor& x, const Tensor& src_slot, const OptTensor& padded_offsets, int64_t num_experts, const OptTensor& slot_scale, int64_t top_k) {
+  CHECK_BF16(x);
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous());
+  auto out = torch::empty({src_slot.numel(), x.size(1)}, x.options());
+  check(mdt_gather_rows(x.data_ptr(), src_slot.data_ptr<int>(), padded_offsets.has_value() ? padded_offsets->data_ptr<int>() : nullptr, (int)num_experts,
+                        cptr(slot_scale), out.data_ptr(), (int)src_slot.numel(), (int)x.size(1), (int)top_k, cur_stream()), "gather_rows");
+  return out;
+}
+Tensor combine_rows(const Tensor& y, const Tensor& dest_row, const OptTensor& weights, int64_t top_k) {
+  CHECK_BF16(y);
+  c10::cuda::CUDAGuard guard(y.device());
+  TORCH_CHECK(y.is_contiguous());
+  const int T = (int)(dest_row.numel() / top_k);
+  auto out = torch::empty({T, y.size(1)}, y.options());
+  check(mdt_combine_rows(y.data_ptr(), dest_row.data_ptr<int>(), cptr(weights), out.data_ptr(), T, (int)y.size(1), (int)top_k, cur_stream()), "combine_rows");
+  return out;
+}
+Tensor combine_wgrad(const Tensor& y, const Tensor& dest_row, const Tensor& dout, int64_t top_k) {
+  c10::cuda::CUDAGuard guard(y.device());
+  TORCH_CHECK(y.is_contiguous() && dout.is_contiguous());
+  const int T = (int)(dest_row.numel() / top_k);
+  auto dw = torch::empty({T, top_k}, y.options());
+  check(mdt_combine_wgrad(y.data_ptr(), dest_row.data_ptr<int>(), dout.data_ptr(), dw.data_ptr(), T, (int)y.size(1), (int)top_k, cur_stream()), "combine_wgrad");
+  return dw;
+}
+
+int64_t launch_count() {
+  return mdt_gemm_launch_count() + mdt_elementwise_launch_count() + mdt_router_launch_count();
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rope", &rope);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("embedding", &embedding);
+  m.def("embedding_bwd", &embedding_bwd);
+  m.def("cross_entropy", &cross_entropy);
+  m.def("adamw", &adamw);
+  m.def("sumsq", &sumsq);
+  m.def("axpby", &axpby);
+  m.def("router_fwd", &router_fwd);
+  m.def("router_bwd", &router_bwd);
+  m.def("make_plan", &make_plan);
+  m.def("gather_rows", &gather_rows);
+  m.def("combine_rows", &combine_rows);
+  m.def("combine_wgrad", &combine_wgrad);
+  m.def("launch_count", &launch_count);
+}

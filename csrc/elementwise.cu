@@ -1,0 +1,411 @@
+// Memory-bound kernels: RMSNorm, RoPE, SwiGLU, embedding, softmax cross-entropy, AdamW, reductions.
+// All of them move 16 bytes per thread per access and keep intermediate math in fp32.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "api.h"
+
+namespace mdt {
+
+static long long g_ew_launches = 0;
+typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf162;
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const bf162* h = reinterpret_cast<const bf162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  bf162* h = reinterpret_cast<bf162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// block-wide sum; `red` is shared memory for 32 floats; every thread receives the result
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : -INFINITY;
+  return warp_max(t);
+}
+
+// ------------------------------------------------------------------------------------ RMSNorm
+__global__ void rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
+                                   float* __restrict__ rstd, int rows, int cols, float eps) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (long long)row * cols);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + (long long)row * cols);
+  const int nv = cols / 8;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    float f[8]; unpack8(xr[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  }
+  ss = block_sum(ss, red);
+  const float r = rsqrtf(ss / cols + eps);
+  if (threadIdx.x == 0 && rstd != nullptr) rstd[row] = r;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    float f[8], g[8]; unpack8(xr[i], f); unpack8(wr[i], g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = f[j] * r * g[j];
+    yr[i] = pack8(f);
+  }
+}
+
+// dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x));  dw partial sums per CTA (CTA loops over rows)
+__global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ dy,
+                                   const float* __restrict__ rstd, bf16* __restrict__ dx, float* __restrict__ dw_partial,
+                                   int rows, int cols) {
+  __shared__ float red[32];
+  const int nv = cols / 8;
+  // each thread owns vectors i = threadIdx.x + k*blockDim.x, k < 8 (cols <= 8*8*blockDim.x)
+  float acc[8][8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[k][j] = 0.f;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (long long)row * cols);
+    const uint4* dr = reinterpret_cast<const uint4*>(dy + (long long)row * cols);
+    uint4* ox = reinterpret_cast<uint4*>(dx + (long long)row * cols);
+    const float r = rstd[row];
+    float dot = 0.f;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+      float xf[8], df[8], wf[8]; unpack8(xr[i], xf); unpack8(dr[i], df); unpack8(wr[i], wf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot += df[j] * wf[j] * xf[j];
+    }
+    dot = block_sum(dot, red);
+    const float c = dot * r * r / cols;
+    int k = 0;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x, ++k) {
+      float xf[8], df[8], wf[8], o[8]; unpack8(xr[i], xf); unpack8(dr[i], df); unpack8(wr[i], wf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j] = r * (df[j] * wf[j] - xf[j] * c);
+        if (k < 8) acc[k][j] += df[j] * xf[j] * r;
+      }
+      ox[i] = pack8(o);
+    }
+  }
+  int k = 0;
+  for (int i = threadIdx.x; i < nv && k < 8; i += blockDim.x, ++k) {
+    float* dst = dw_partial + (long long)blockIdx.x * cols + i * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dst[j] = acc[k][j];
+  }
+}
+
+// ------------------------------------------------------------------------------------ RoPE
+// x: [tokens, heads, d]; pairs (i, i + d/2) rotated by pos * theta^(-2i/d); inverse negates the angle
+__global__ void rope_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const int* __restrict__ pos, int tokens,
+                            int heads, int d, float log2_theta, int inverse) {
+  const int t = blockIdx.x;
+  const int half = d / 2;
+  const float p = (float)pos[t];
+  for (int idx = threadIdx.x; idx < heads * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx - h * half;
+    const float inv_freq = exp2f(-log2_theta * (2.0f * i / d));
+    float s, c;
+    sincosf(p * inv_freq, &s, &c);
+    if (inverse) s = -s;
+    const long long base = ((long long)t * heads + h) * d;
+    const float a = __bfloat162float(x[base + i]), b = __bfloat162float(x[base + i + half]);
+    y[base + i] = __float2bfloat16(a * c - b * s);
+    y[base + i + half] = __float2bfloat16(b * c + a * s);
+  }
+}
+
+// ------------------------------------------------------------------------------------ SwiGLU
+__global__ void swiglu_fwd_kernel(const uint4* __restrict__ g, const uint4* __restrict__ u, uint4* __restrict__ h, long long nv) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv; i += (long long)gridDim.x * blockDim.x) {
+    float a[8], b[8]; unpack8(g[i], a); unpack8(u[i], b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = a[j] / (1.f + __expf(-a[j])) * b[j];
+    h[i] = pack8(a);
+  }
+}
+__global__ void swiglu_bwd_kernel(const uint4* __restrict__ g, const uint4* __restrict__ u, const uint4* __restrict__ dh,
+                                  uint4* __restrict__ dg, uint4* __restrict__ du, long long nv) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv; i += (long long)gridDim.x * blockDim.x) {
+    float a[8], b[8], d[8], og[8], ou[8]; unpack8(g[i], a); unpack8(u[i], b); unpack8(dh[i], d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sg = 1.f / (1.f + __expf(-a[j]));
+      const float silu = a[j] * sg;
+      ou[j] = d[j] * silu;
+      og[j] = d[j] * b[j] * sg * (1.f + a[j] * (1.f - sg));
+    }
+    dg[i] = pack8(og); du[i] = pack8(ou);
+  }
+}
+
+// ------------------------------------------------------------------------------------ embedding
+__global__ void embedding_kernel(const bf16* __restrict__ table, const long long* __restrict__ ids, bf16* __restrict__ out, int cols) {
+  const long long id = ids[blockIdx.x];
+  const uint4* src = reinterpret_cast<const uint4*>(table + id * cols);
+  uint4* dst = reinterpret_cast<uint4*>(out + (long long)blockIdx.x * cols);
+  for (int i = threadIdx.x; i < cols / 8; i += blockDim.x) dst[i] = src[i];
+}
+__global__ void embedding_bwd_kernel(const bf16* __restrict__ dout, const long long* __restrict__ ids, float* __restrict__ dtable, int cols) {
+  const long long id = ids[blockIdx.x];
+  const bf16* src = dout + (long long)blockIdx.x * cols;
+  float* dst = dtable + id * cols;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) atomicAdd(dst + i, __bfloat162float(src[i]));
+}
+
+// ------------------------------------------------------------------------------------ cross entropy
+// One CTA per row.  The row (vocab bf16 values) is staged in shared memory, so global memory is read
+// once and written once.  Output: logits <- (softmax - onehot) * grad_scale / max(count,1), or 0 for
+// ignored rows; loss_sum += lse - logit[label].  `count` must already hold the number of counted rows.
+__global__ void cross_entropy_kernel(bf16* __restrict__ logits, const long long* __restrict__ labels, float* __restrict__ loss_sum,
+                                     const float* __restrict__ count, int vocab, long long ld, int ignore_index, float grad_scale) {
+  extern __shared__ uint4 row_smem[];
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  uint4* gr = reinterpret_cast<uint4*>(logits + (long long)row * ld);
+  const int nv = vocab / 8;
+  const long long label = labels[row];
+  if (label == ignore_index) {
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) gr[i] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    uint4 u = gr[i]; row_smem[i] = u;
+    float f[8]; unpack8(u, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, f[j]);
+  }
+  mx = block_max(mx, red);
+  float se = 0.f;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    float f[8]; unpack8(row_smem[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) se += __expf(f[j] - mx);
+  }
+  se = block_sum(se, red);
+  const float lse = mx + logf(se);
+  const float scale = grad_scale / fmaxf(*count, 1.f);
+  const float inv = 1.f / se;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    float f[8]; unpack8(row_smem[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float pz = __expf(f[j] - mx) * inv;
+      if ((long long)i * 8 + j == label) {
+        pz -= 1.f;
+        atomicAdd(loss_sum, lse - f[j]);
+      }
+      f[j] = pz * scale;
+    }
+    gr[i] = pack8(f);
+  }
+}
+__global__ void count_labels_kernel(const long long* __restrict__ labels, int rows, int ignore_index, float* __restrict__ count) {
+  __shared__ float red[32];
+  float c = 0.f;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < rows; i += gridDim.x * blockDim.x) c += labels[i] != ignore_index ? 1.f : 0.f;
+  c = block_sum(c, red);
+  if (threadIdx.x == 0 && c != 0.f) atomicAdd(count, c);
+}
+
+// ------------------------------------------------------------------------------------ AdamW
+template <typename T> __device__ __forceinline__ float ldf(const T* p, long long i);
+template <> __device__ __forceinline__ float ldf<float>(const float* p, long long i) { return p[i]; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p, long long i) { return __bfloat162float(p[i]); }
+template <typename T> __device__ __forceinline__ void stf(T* p, long long i, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, long long i, float v) { p[i] = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, long long i, float v) { p[i] = __float2bfloat16(v); }
+
+__global__ void adamw_kernel(const MdtAdamTensor* __restrict__ tensors, float lr, float b1, float b2, float eps, float wd,
+                             float bc1, float bc2, float gscale) {
+  const MdtAdamTensor t = tensors[blockIdx.y];
+  const long long stride = (long long)gridDim.x * blockDim.x * 8;
+  for (long long base = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; base < t.n; base += stride) {
+    const int cnt = (t.n - base) < 8 ? (int)(t.n - base) : 8;
+    float p[8], g[8], m[8], v[8];
+    const bool vec = cnt == 8 && !t.p_fp32 && !t.g_fp32 && !t.s_fp32;
+    if (vec) {
+      unpack8(*reinterpret_cast<const uint4*>((const bf16*)t.p + base), p);
+      unpack8(*reinterpret_cast<const uint4*>((const bf16*)t.g + base), g);
+      unpack8(*reinterpret_cast<const uint4*>((const bf16*)t.m + base), m);
+      unpack8(*reinterpret_cast<const uint4*>((const bf16*)t.v + base), v);
+    } else {
+      for (int j = 0; j < cnt; ++j) {
+        p[j] = t.p_fp32 ? ldf((const float*)t.p, base + j) : ldf((const bf16*)t.p, base + j);
+        g[j] = t.g_fp32 ? ldf((const float*)t.g, base + j) : ldf((const bf16*)t.g, base + j);
+        m[j] = t.s_fp32 ? ldf((const float*)t.m, base + j) : ldf((const bf16*)t.m, base + j);
+        v[j] = t.s_fp32 ? ldf((const float*)t.v, base + j) : ldf((const bf16*)t.v, base + j);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (j < cnt) {
+        const float gg = g[j] * gscale;
+        m[j] = b1 * m[j] + (1.f - b1) * gg;
+        v[j] = b2 * v[j] + (1.f - b2) * gg * gg;
+        const float denom = sqrtf(v[j] / bc2) + eps;
+        p[j] = p[j] * (1.f - lr * wd) - lr * (m[j] / bc1) / denom;
+      }
+    }
+    if (vec) {
+      *reinterpret_cast<uint4*>((bf16*)t.p + base) = pack8(p);
+      *reinterpret_cast<uint4*>((bf16*)t.m + base) = pack8(m);
+      *reinterpret_cast<uint4*>((bf16*)t.v + base) = pack8(v);
+    } else {
+      for (int j = 0; j < cnt; ++j) {
+        if (t.p_fp32) stf((float*)t.p, base + j, p[j]); else stf((bf16*)t.p, base + j, p[j]);
+        if (t.s_fp32) { stf((float*)t.m, base + j, m[j]); stf((float*)t.v, base + j, v[j]); }
+        else { stf((bf16*)t.m, base + j, m[j]); stf((bf16*)t.v, base + j, v[j]); }
+      }
+    }
+  }
+}
+
+__global__ void sumsq_kernel(const void* __restrict__ x, long long n, int fp32, float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float v = fp32 ? ((const float*)x)[i] : __bfloat162float(((const bf16*)x)[i]);
+    s += v * v;
+  }
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) atomicAdd(out, s);
+}
+
+// y = a*y + b*x
+__global__ void axpby_kernel(void* __restrict__ y, const void* __restrict__ x, long long n, float a, float b, int y_fp32, int x_fp32) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float xv = x_fp32 ? ((const float*)x)[i] : __bfloat162float(((const bf16*)x)[i]);
+    const float yv = a == 0.f ? 0.f : a * (y_fp32 ? ((float*)y)[i] : __bfloat162float(((bf16*)y)[i]));
+    const float r = yv + b * xv;
+    if (y_fp32) ((float*)y)[i] = r; else ((bf16*)y)[i] = __float2bfloat16(r);
+  }
+}
+
+static inline int grid_for(long long work_items, int block, int cap = 148 * 16) {
+  long long g = (work_items + block - 1) / block;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+#define MDT_CHECK_LAUNCH() do { ++g_ew_launches; cudaError_t e_ = cudaGetLastError(); if (e_ != cudaSuccess) return -100 - (int)e_; } while (0)
+
+}  // namespace mdt
+
+using namespace mdt;
+
+extern "C" long long mdt_elementwise_launch_count() { return g_ew_launches; }
+
+extern "C" int mdt_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps, cudaStream_t s) {
+  if (cols % 8 != 0) return -1;
+  if (rows == 0) return 0;
+  rmsnorm_fwd_kernel<<<rows, 256, 0, s>>>((const bf16*)x, (const bf16*)w, (bf16*)y, rstd, rows, cols, eps);
+  MDT_CHECK_LAUNCH();
+  return 0;
+}
+extern "C" int mdt_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx, float* dw_partial,
+                               int rows, int cols, int n_partial, cudaStream_t s) {
+  if (cols % 8 != 0 || cols > 8 * 8 * 256) return -1;
+  rmsnorm_bwd_kernel<<<n_partial, 256, 0, s>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, (bf16*)dx, dw_partial, rows, cols);
+  MDT_CHECK_LAUNCH();
+  return 0;
+}
+extern "C" int mdt_rope(const void* x, void* y, const int* positions, int tokens, int heads, int head_dim, float theta,
+                        int inverse, cudaStream_t s) {
+  if (tokens == 0) return 0;
+  rope_kernel<<<tokens, 256, 0, s>>>((const bf16*)x, (bf16*)y, positions, tokens, heads, head_dim, log2f(theta), inverse);
+  MDT_CHECK_LAUNCH();
+  return 0;
+}
+extern "C" int mdt_swiglu_fwd(const void* g, const void* u, void* h, long long n, cudaStream_t s) {
+  if (n % 8 != 0) return -1;
+  if (n == 0) return 0;
+  swiglu_fwd_kernel<<<grid_for(n / 8, 256), 256, 0, s>>>((const uint4*)g, (const uint4*)u, (uint4*)h, n / 8);
+  MDT_CHECK_LAUNCH();
+  return 0;
+}
+extern "C" int mdt_swiglu_bwd(const void* g, const void* u, const void* dh, void* dg, void* du, long long n, cudaStream_t s) {
+  if (n % 8 != 0) return -1;
+  if (n == 0) return 0;
+  swiglu_bwd_kernel<<<grid_for(n / 8, 256), 256, 0, s>>>((const uint4*)g, (const uint4*)u, (const uint4*)dh, (uint4*)dg, (uint4*)du, n / 8);
+  MDT_CHECK_LAUNCH();
+  return 0;
+}
+extern "C" int mdt_embedding(const void* table, const long long* ids, void* out, int tokens, int cols, cudaStream_t s) {
+  if (cols % 8 != 0) return -1;
+  if (tokens == 0) return 0;
+  embedding_kernel<<<tokens, 128, 0, s>>>((const bf16*)table, ids, (bf16*)out, cols);
+  MDT_CHECK_LAUNCH();
+  return 0;
+}
+extern "C" int mdt_embedding_bwd(const void* dout, const long long* ids, float* dtable, int tokens, int cols, cudaStream_t s) {
+  if (tokens == 0) return 0;
+  embedding_bwd_kernel<<<tokens, 256, 0, s>>>((const bf16*)dout, ids, dtable, cols);
+  MDT_CHECK_LAUNCH();
+  return 0;
+}
+extern "C" int mdt_cross_entropy(void* logits, const long long* labels, float* loss_sum, float* count, int rows, int vocab,
+                                 long long ld, int ignore_index, float grad_scale, cudaStream_t s) {
+  if (vocab % 8 != 0 || ld % 8 != 0) return -1;
+  if (rows == 0) return 0;
+  const int smem = vocab * 2;
+  static int configured = 0;
+  if (smem > 48 * 1024 && configured < smem) {
+    if (cudaFuncSetAttribute(cross_entropy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -2;
+    configured = smem;
+  }
+  count_labels_kernel<<<grid_for(rows, 256, 64), 256, 0, s>>>(labels, rows, ignore_index, count);
+  MDT_CHECK_LAUNCH();
+  cross_entropy_kernel<<<rows, 512, smem, s>>>((bf16*)logits, labels, loss_sum, count, vocab, ld, ignore_index, grad_scale);
+  MDT_CHECK_LAUNCH();
+  return 0;
+}
+extern "C" int mdt_adamw(const MdtAdamTensor* tensors_device, int num_tensors, long long max_n, float lr, float beta1, float beta2,
+                         float eps, float weight_decay, float bc1, float bc2, float grad_scale, cudaStream_t s) {
+  if (num_tensors == 0) return 0;
+  dim3 grid(grid_for((max_n + 7) / 8, 256, 148 * 8), num_tensors);
+  adamw_kernel<<<grid, 256, 0, s>>>(tensors_device, lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale);
+  MDT_CHECK_LAUNCH();
+  return 0;
+}
+extern "C" int mdt_sumsq(const void* x, long long n, int fp32, float* out_accum, cudaStream_t s) {
+  if (n == 0) return 0;
+  sumsq_kernel<<<grid_for(n, 256 * 8, 148 * 4), 256, 0, s>>>(x, n, fp32, out_accum);
+  MDT_CHECK_LAUNCH();
+  return 0;
+}
+extern "C" int mdt_axpby(void* y, const void* x, long long n, float a, float b, int y_fp32, int x_fp32, cudaStream_t s) {
+  if (n == 0) return 0;
+  axpby_kernel<<<grid_for(n, 256 * 4), 256, 0, s>>>(y, x, n, a, b, y_fp32, x_fp32);
+  MDT_CHECK_LAUNCH();
+  return 0;
+}

@@ -1,0 +1,424 @@
+// Persistent warp-specialised bf16 GEMM family for sm_100a.
+//
+//   TMA (cp.async.bulk.tensor, 128-byte swizzle) -> shared memory ring -> tcgen05.mma (one issuing
+//   thread, fp32 accumulators in TMEM, two accumulator buffers) -> tcgen05.ld epilogue.
+//
+// One kernel covers every matrix product of the training step:
+//   mode 0  dense          C[M,N]        = A[M,K] * B[K,N]
+//   mode 1  grouped rows   C[rows of g]  = A[rows of g] * B_g      (expert forward / dgrad; row groups
+//                                                                   start on 128-row boundaries)
+//   mode 2  grouped depth  C_g[M,N]      = sum over rows of g  A[row,:]^T B[row,:]   (weight gradients)
+// Operands may be K-major or MN-major (the tensor core transposes from shared memory), so the same
+// kernel serves x*W^T, dy*W and dy^T*x without materialising a transpose.
+// Options: a second, short depth segment (LoRA: += (s*X*A) * B with its own tensor maps), a dual-B
+// mode that computes gate and up projections in one 256-wide MMA and applies SwiGLU in the
+// epilogue, alpha scaling and accumulation into C (gradient accumulation), fp32 or bf16 C.
+//
+// Role layout of a 192-thread CTA: warp 0 = TMA producer, warp 1 = MMA issuer (owns TMEM),
+// warps 2-5 = epilogue (each owns one 32-lane quarter of TMEM).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "api.h"
+#include "common/ptx.cuh"
+
+namespace mdt {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int GEMM_THREADS = 192;
+
+struct GemmParams {
+  CUtensorMap tmA, tmB, tmB2;        // main depth segment (tmB2: second B matrix of the dual mode)
+  CUtensorMap tmA_l, tmB_l, tmB2_l;  // optional LoRA depth segment
+  int M, N, K, K_l, G, mode;
+  int a_mn, b_mn, a_mn_l, b_mn_l, dual;
+  const int* offsets;
+  void* C; void* C2; void* C3;
+  long long ldc, c_group_stride;
+  int c_fp32, accumulate;
+  float alpha;
+  int store_gate_up;
+  int* status;
+};
+
+struct Tile {
+  int g, m0, n0, krow0, num_kb, num_kb_l;
+};
+
+// Maps a linear tile index to its coordinates; returns false past the last tile.
+template <int BN_OUT>
+__device__ __forceinline__ bool get_tile(const GemmParams& p, int t, Tile& o) {
+  const int n_blocks = (p.N + BN_OUT - 1) / BN_OUT;
+  o.num_kb_l = (p.K_l + BK - 1) / BK;
+  if (p.mode == 2) {
+    const int m_blocks = (p.M + BM - 1) / BM;
+    const int per_group = m_blocks * n_blocks;
+    if (t >= per_group * p.G) return false;
+    o.g = t / per_group;
+    int r = t - o.g * per_group;
+    o.m0 = (r % m_blocks) * BM;
+    o.n0 = (r / m_blocks) * BN_OUT;
+    int k_begin = 0, k_end = p.K;
+    if (p.offsets != nullptr) { k_begin = p.offsets[o.g]; k_end = p.offsets[o.g + 1]; }
+    o.krow0 = k_begin;
+    o.num_kb = (k_end - k_begin + BK - 1) / BK;
+    return true;
+  }
+  int rows = p.M;
+  if (p.mode == 1) rows = p.offsets[p.G];
+  const int m_blocks = (rows + BM - 1) / BM;
+  if (t >= m_blocks * n_blocks) return false;
+  o.m0 = (t % m_blocks) * BM;
+  o.n0 = (t / m_blocks) * BN_OUT;
+  o.g = 0;
+  if (p.mode == 1) {
+    int g = 0;
+    while (g + 1 < p.G && p.offsets[g + 1] <= o.m0) ++g;
+    o.g = g;
+  }
+  o.krow0 = 0;
+  o.num_kb = (p.K + BK - 1) / BK;
+  return true;
+}
+
+__device__ __forceinline__ void store8(void* C, long long idx, const float (&v)[8], int c_fp32, int accumulate) {
+  if (c_fp32) {
+    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(C) + idx);
+    float4 a = make_float4(v[0], v[1], v[2], v[3]), b = make_float4(v[4], v[5], v[6], v[7]);
+    if (accumulate) {
+      float4 oa = dst[0], ob = dst[1];
+      a.x += oa.x; a.y += oa.y; a.z += oa.z; a.w += oa.w;
+      b.x += ob.x; b.y += ob.y; b.z += ob.z; b.w += ob.w;
+    }
+    dst[0] = a; dst[1] = b;
+  } else {
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(C) + idx);
+    float w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = v[i];
+    if (accumulate) {
+      uint4 old = *dst;
+      const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(o2[i]); w[2 * i] += f.x; w[2 * i + 1] += f.y; }
+    }
+    uint4 out;
+    __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = __floats2bfloat162_rn(w[2 * i], w[2 * i + 1]);
+    *dst = out;
+  }
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __grid_constant__ GemmParams p) {
+  constexpr int B_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // 256 or 512: a power of two >= 32
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int BN_OUT = p.dual ? BN / 2 : BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto fail = [&](int code) {
+    *abort_flag = 1;
+    if (p.status != nullptr) atomicCAS(p.status, 0, code);
+  };
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    prefetch_tensormap(&p.tmA); prefetch_tensormap(&p.tmB);
+    uint32_t it = 0;
+    Tile t;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && (p.dual ? get_tile<BN / 2>(p, tile, t) : get_tile<BN>(p, tile, t)); tile += gridDim.x) {
+      const int total_kb = t.num_kb + (t.num_kb > 0 || p.mode != 2 ? t.num_kb_l : 0);
+      for (int kb = 0; kb < total_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!wait_parity(&empty_bar[s], ph ^ 1, abort_flag)) { fail(ST_TIMEOUT_EMPTY); ok = false; break; }
+        uint8_t* sA = smem + s * STAGE_BYTES;
+        uint8_t* sB = sA + A_BYTES;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        const bool lora = kb >= t.num_kb;
+        const int kk = (lora ? kb - t.num_kb : kb) * BK;
+        const CUtensorMap* mA = lora ? &p.tmA_l : &p.tmA;
+        const CUtensorMap* mB = lora ? &p.tmB_l : &p.tmB;
+        const CUtensorMap* mB2 = lora ? &p.tmB2_l : &p.tmB2;
+        const int a_mn = lora ? p.a_mn_l : p.a_mn, b_mn = lora ? p.b_mn_l : p.b_mn;
+        const int krow = (lora ? 0 : t.krow0) + kk;
+        if (a_mn == 0) {
+          tma_load_2d(sA, mA, &full_bar[s], kk, t.m0);
+        } else {
+          tma_load_2d(sA, mA, &full_bar[s], t.m0, krow);
+          tma_load_2d(sA + 8192, mA, &full_bar[s], t.m0 + 64, krow);
+        }
+        const int zB = (p.mode == 2) ? 0 : t.g;
+        if (b_mn == 0) {
+          if (p.dual) {
+            tma_load_3d(sB, mB, &full_bar[s], kk, t.n0, zB);
+            tma_load_3d(sB + B_BYTES / 2, mB2, &full_bar[s], kk, t.n0, zB);
+          } else {
+            tma_load_3d(sB, mB, &full_bar[s], kk, t.n0, zB);
+          }
+        } else {
+          if (p.dual) {
+#pragma unroll
+            for (int c = 0; c < BN / 128; ++c) {
+              tma_load_3d(sB + c * 8192, mB, &full_bar[s], t.n0 + 64 * c, krow, zB);
+              tma_load_3d(sB + B_BYTES / 2 + c * 8192, mB2, &full_bar[s], t.n0 + 64 * c, krow, zB);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_3d(sB + c * 8192, mB, &full_bar[s], t.n0 + 64 * c, krow, zB);
+          }
+        }
+      }
+    }
+    if (!ok) {  // give copies already in flight a bounded time to land before the CTA exits
+      for (int s = 0; s < STAGES; ++s) {
+        uint64_t t0 = global_timer_ns();
+        while (!mbar_try_wait(&full_bar[s], 0) && !mbar_try_wait(&full_bar[s], 1) && global_timer_ns() - t0 < 1000000ull) {}
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer
+    uint32_t it = 0, acc_it = 0;
+    Tile t;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && (p.dual ? get_tile<BN / 2>(p, tile, t) : get_tile<BN>(p, tile, t)); tile += gridDim.x) {
+      const int total_kb = t.num_kb + (t.num_kb > 0 || p.mode != 2 ? t.num_kb_l : 0);
+      if (total_kb == 0) continue;
+      const int buf = acc_it & 1;
+      const uint32_t aph = (acc_it >> 1) & 1;
+      if (!wait_parity(&tempty_bar[buf], aph ^ 1, abort_flag)) { fail(ST_TIMEOUT_TMEM_EMPTY); break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      for (int kb = 0; kb < total_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!wait_parity(&full_bar[s], ph, abort_flag)) { fail(ST_TIMEOUT_FULL); ok = false; break; }
+        tc_fence_after();
+        const bool lora = kb >= t.num_kb;
+        const int a_mn = lora ? p.a_mn_l : p.a_mn, b_mn = lora ? p.b_mn_l : p.b_mn;
+        const uint32_t idesc = make_idesc_bf16(BM, BN, a_mn, b_mn);
+        const uint32_t sA = smem_u32(smem + s * STAGE_BYTES);
+        const uint32_t sB = sA + A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {
+          const uint64_t da = a_mn ? make_smem_desc(sA + k * 2048, 8192, 1024) : make_smem_desc(sA + k * 32, 16, 1024);
+          const uint64_t db = b_mn ? make_smem_desc(sB + k * 2048, 8192, 1024) : make_smem_desc(sB + k * 32, 16, 1024);
+          umma_bf16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);   // frees the stage when these MMAs have read it
+      }
+      if (!ok) break;
+      umma_commit(&tfull_bar[buf]);   // accumulator complete
+      ++acc_it;
+    }
+  } else if (warp >= 2) {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;
+    uint32_t acc_it = 0;
+    Tile t;
+    for (int tile = blockIdx.x; (p.dual ? get_tile<BN / 2>(p, tile, t) : get_tile<BN>(p, tile, t)); tile += gridDim.x) {
+      const int total_kb = t.num_kb + (t.num_kb > 0 || p.mode != 2 ? t.num_kb_l : 0);
+      const int row = t.m0 + q * 32 + lane;
+      const int row_limit = (p.mode == 1) ? p.offsets[p.G] : p.M;
+      const bool row_ok = row < row_limit;
+      const long long base = (p.mode == 2 ? (long long)t.g * p.c_group_stride : 0) + (long long)row * p.ldc;
+      if (total_kb == 0) {
+        if (!p.accumulate && row_ok) {
+          float z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          for (int c = 0; c < BN_OUT; c += 8)
+            if (t.n0 + c < p.N) store8(p.C, base + t.n0 + c, z, p.c_fp32, 0);
+        }
+        continue;
+      }
+      const int buf = acc_it & 1;
+      const uint32_t aph = (acc_it >> 1) & 1;
+      if (!wait_parity(&tfull_bar[buf], aph, abort_flag)) { fail(ST_TIMEOUT_TMEM_FULL); break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
+      if (p.dual) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 2; c += 32) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(taddr + c, rg);
+          tmem_ld_32x32(taddr + BN / 2 + c, ru);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = t.n0 + c + v * 8;
+              if (col < p.N) {
+                float h[8], gg[8], uu[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  gg[i] = __uint_as_float(rg[v * 8 + i]);
+                  uu[i] = __uint_as_float(ru[v * 8 + i]);
+                  h[i] = gg[i] / (1.0f + __expf(-gg[i])) * uu[i];
+                }
+                store8(p.C, base + col, h, 0, 0);
+                if (p.store_gate_up) { store8(p.C2, base + col, gg, 0, 0); store8(p.C3, base + col, uu, 0, 0); }
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = t.n0 + c + v * 8;
+              if (col < p.N) {
+                float o[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(r[v * 8 + i]) * p.alpha;
+                store8(p.C, base + col, o, p.c_fp32, p.accumulate);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+      ++acc_it;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// bf16 tensor [d2][d1][d0] (d0 contiguous), strides in elements; box = {b0, b1, 1}
+static int make_map(CUtensorMap* m, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1, uint64_t s2,
+                    uint32_t b0, uint32_t b1, int rank) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {s1 * 2, s2 * 2};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (strides[0] & 15) || (rank == 3 && (strides[1] & 15))) return -2;
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+static int g_num_sms = 0;
+static long long g_launches = 0;
+
+template <int BN, int STAGES>
+static cudaError_t launch(const GemmParams& p, int grid, cudaStream_t stream) {
+  constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_sm100_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  gemm_sm100_kernel<BN, STAGES><<<grid, GEMM_THREADS, smem, stream>>>(p);
+  ++g_launches;
+  return cudaGetLastError();
+}
+
+}  // namespace mdt
+
+extern "C" long long mdt_gemm_launch_count() { return mdt::g_launches; }
+
+extern "C" int mdt_gemm(const MdtGemmDesc* d, cudaStream_t stream) {
+  using namespace mdt;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = d->M; p.N = d->N; p.K = d->K; p.K_l = d->K_l; p.G = d->G < 1 ? 1 : d->G; p.mode = d->mode;
+  p.a_mn = d->a_mn; p.b_mn = d->b_mn; p.a_mn_l = d->a_mn_l; p.b_mn_l = d->b_mn_l; p.dual = d->dual;
+  p.offsets = d->offsets; p.C = d->C; p.C2 = d->C2; p.C3 = d->C3; p.ldc = d->ldc; p.c_group_stride = d->c_group_stride;
+  p.c_fp32 = d->c_fp32; p.accumulate = d->accumulate; p.alpha = d->alpha; p.store_gate_up = d->C2 != nullptr;
+  p.status = d->status;
+  if (p.N % 8 != 0 || p.ldc % 8 != 0) return -10;
+  if (p.dual && (p.b_mn != 0 || p.c_fp32 || p.accumulate)) return -11;
+  const int BN = (p.dual || p.N > 128) ? 256 : 128;
+  const int bn_out = p.dual ? BN / 2 : BN;
+  int rc = 0;
+  // A: [a_rows, a_cols] row-major, a_cols contiguous.  K-major: rows = M, cols = K.  MN-major: rows = depth, cols = M.
+  rc |= make_map(&p.tmA, d->A, d->a_cols, d->a_rows, 1, d->lda, 0, 64, d->a_mn ? 64 : BM, 2);
+  // B: [G, b_rows, b_cols].  K-major: rows = N, cols = K.  MN-major: rows = depth, cols = N.
+  const uint32_t b_box_rows = d->b_mn ? 64 : bn_out;
+  rc |= make_map(&p.tmB, d->B, d->b_cols, d->b_rows, p.mode == 2 ? 1 : p.G, d->ldb, d->b_group_stride, 64, b_box_rows, 3);
+  if (p.dual) rc |= make_map(&p.tmB2, d->B2, d->b_cols, d->b_rows, p.G, d->ldb, d->b_group_stride, 64, b_box_rows, 3);
+  if (p.K_l > 0) {
+    rc |= make_map(&p.tmA_l, d->A_l, d->al_cols, d->al_rows, 1, d->lda_l, 0, 64, d->a_mn_l ? 64 : BM, 2);
+    const uint32_t bl_box_rows = d->b_mn_l ? 64 : bn_out;
+    rc |= make_map(&p.tmB_l, d->B_l, d->bl_cols, d->bl_rows, p.G, d->ldb_l, d->bl_group_stride, 64, bl_box_rows, 3);
+    if (p.dual) rc |= make_map(&p.tmB2_l, d->B2_l, d->bl_cols, d->bl_rows, p.G, d->ldb_l, d->bl_group_stride, 64, bl_box_rows, 3);
+  }
+  if (rc != 0) return rc;
+  // upper bound on the number of tiles (the exact count may depend on device-side offsets)
+  long long rows = (p.mode == 1) ? d->capacity_rows : p.M;
+  long long tiles = ((rows + BM - 1) / BM) * ((p.N + bn_out - 1) / bn_out) * (p.mode == 2 ? p.G : 1);
+  int grid = (int)(tiles < g_num_sms ? (tiles < 1 ? 1 : tiles) : g_num_sms);
+  cudaError_t e = (BN == 256) ? launch<256, 4>(p, grid, stream) : launch<128, 6>(p, grid, stream);
+  return e == cudaSuccess ? 0 : -100 - (int)e;
+}

@@ -1,0 +1,411 @@
+// Router (linear + softmax + top-k + L1 normalise), the counting sort that places (token, choice)
+// slots into block-padded expert groups, and the row gather / gate-weighted combine kernels.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "api.h"
+
+namespace mdt {
+
+typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf162;
+static long long g_rt_launches = 0;
+constexpr int MAX_E = 64;   // experts held in registers per lane in the router kernels
+constexpr int MAX_K = 8;
+
+__device__ __forceinline__ void unpack8r(const uint4& u, float (&f)[8]) {
+  const bf162* h = reinterpret_cast<const bf162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 pack8r(const float (&f)[8]) {
+  uint4 u;
+  bf162* h = reinterpret_cast<bf162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+__device__ __forceinline__ float wsum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// logits[e] = <x[t,:], w[e,:]> for one token per warp; every lane ends with all E logits
+template <int E_T>
+__device__ __forceinline__ void token_logits(const bf16* __restrict__ x, const bf16* __restrict__ w, int hidden, int experts,
+                                             int lane, float (&logit)[E_T]) {
+#pragma unroll
+  for (int e = 0; e < E_T; ++e) logit[e] = 0.f;
+  const uint4* xr = reinterpret_cast<const uint4*>(x);
+  for (int i = lane; i < hidden / 8; i += 32) {
+    float xf[8]; unpack8r(xr[i], xf);
+#pragma unroll
+    for (int e = 0; e < E_T; ++e) {
+      if (e < experts) {
+        float wf[8]; unpack8r(reinterpret_cast<const uint4*>(w + (long long)e * hidden)[i], wf);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) logit[e] += xf[j] * wf[j];
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < E_T; ++e) logit[e] = wsum(logit[e]);
+}
+
+template <int E_T>
+__device__ __forceinline__ void softmax_topk(const float (&logit)[E_T], int experts, int top_k, int normalize,
+                                             float (&prob)[E_T], int (&sel)[MAX_K], float (&wsel)[MAX_K], float& denom) {
+  float mx = -INFINITY;
+#pragma unroll
+  for (int e = 0; e < E_T; ++e) if (e < experts) mx = fmaxf(mx, logit[e]);
+  float se = 0.f;
+#pragma unroll
+  for (int e = 0; e < E_T; ++e) { prob[e] = e < experts ? __expf(logit[e] - mx) : 0.f; se += prob[e]; }
+  const float inv = 1.f / se;
+#pragma unroll
+  for (int e = 0; e < E_T; ++e) prob[e] *= inv;
+  unsigned long long taken = 0ull;
+  denom = 0.f;
+  for (int c = 0; c < top_k; ++c) {
+    int best = 0; float bv = -1.f;
+#pragma unroll
+    for (int e = 0; e < E_T; ++e)
+      if (e < experts && !((taken >> e) & 1ull) && prob[e] > bv) { bv = prob[e]; best = e; }
+    taken |= 1ull << best;
+    sel[c] = best; wsel[c] = bv; denom += bv;
+  }
+  if (!normalize) denom = 1.f;
+}
+
+template <int E_T>
+__global__ void router_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ scores,
+                                  bf16* __restrict__ weights, int* __restrict__ idx, int tokens, int hidden, int experts,
+                                  int top_k, int normalize) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < tokens; t += gridDim.x * warps_per_block) {
+    float logit[E_T], prob[E_T], wsel[MAX_K], denom;
+    int sel[MAX_K];
+    token_logits<E_T>(x + (long long)t * hidden, w, hidden, experts, lane, logit);
+    softmax_topk<E_T>(logit, experts, top_k, normalize, prob, sel, wsel, denom);
+    if (lane == 0) {
+#pragma unroll
+      for (int e = 0; e < E_T; ++e) if (e < experts) scores[(long long)t * experts + e] = __float2bfloat16(prob[e]);
+      for (int c = 0; c < top_k; ++c) {
+        weights[(long long)t * top_k + c] = __float2bfloat16(wsel[c] / denom);
+        idx[(long long)t * top_k + c] = sel[c];
+      }
+    }
+  }
+}
+
+// Backward through normalise, top-k selection and softmax; writes dlogits (fp32 [tokens, experts]) and
+// dx (+)= dlogits * W.  dW is produced by router_dw_kernel from dlogits.
+template <int E_T>
+__global__ void router_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const int* __restrict__ idx,
+                                  const bf16* __restrict__ dweights, const bf16* __restrict__ dscores, bf16* __restrict__ dx,
+                                  float* __restrict__ dlogits, int tokens, int hidden, int experts, int top_k, int normalize,
+                                  int accumulate_dx) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < tokens; t += gridDim.x * warps_per_block) {
+    float logit[E_T], prob[E_T], ds[E_T], wsel[MAX_K], denom;
+    int sel[MAX_K];
+    token_logits<E_T>(x + (long long)t * hidden, w, hidden, experts, lane, logit);
+    softmax_topk<E_T>(logit, experts, top_k, normalize, prob, sel, wsel, denom);
+    // the forward's selection is authoritative (ties): take the saved indices
+    for (int c = 0; c < top_k; ++c) sel[c] = idx[(long long)t * top_k + c];
+    denom = 0.f;
+    for (int c = 0; c < top_k; ++c) {
+      float pv = 0.f;
+#pragma unroll
+      for (int e = 0; e < E_T; ++e) if (e == sel[c]) pv = prob[e];
+      wsel[c] = pv; denom += pv;
+    }
+    if (!normalize) denom = 1.f;
+#pragma unroll
+    for (int e = 0; e < E_T; ++e) ds[e] = (dscores != nullptr && e < experts) ? __bfloat162float(dscores[(long long)t * experts + e]) : 0.f;
+    float dot = 0.f;
+    if (normalize)
+      for (int c = 0; c < top_k; ++c) dot += __bfloat162float(dweights[(long long)t * top_k + c]) * wsel[c] / denom;
+    for (int c = 0; c < top_k; ++c) {
+      const float g = (__bfloat162float(dweights[(long long)t * top_k + c]) - dot) / denom;
+#pragma unroll
+      for (int e = 0; e < E_T; ++e) if (e == sel[c]) ds[e] += g;
+    }
+    float sdot = 0.f;
+#pragma unroll
+    for (int e = 0; e < E_T; ++e) sdot += prob[e] * ds[e];
+    float dl[E_T];
+#pragma unroll
+    for (int e = 0; e < E_T; ++e) dl[e] = prob[e] * (ds[e] - sdot);
+    if (lane == 0) {
+#pragma unroll
+      for (int e = 0; e < E_T; ++e) if (e < experts) dlogits[(long long)t * experts + e] = dl[e];
+    }
+    uint4* dxr = reinterpret_cast<uint4*>(dx + (long long)t * hidden);
+    for (int i = lane; i < hidden / 8; i += 32) {
+      float acc[8];
+      if (accumulate_dx) unpack8r(dxr[i], acc);
+      else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      }
+#pragma unroll
+      for (int e = 0; e < E_T; ++e) {
+        if (e < experts) {
+          float wf[8]; unpack8r(reinterpret_cast<const uint4*>(w + (long long)e * hidden)[i], wf);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += dl[e] * wf[j];
+        }
+      }
+      dxr[i] = pack8r(acc);
+    }
+  }
+}
+
+// dW[e, col] = sum_t dlogits[t, e] * x[t, col]; one thread per column, tokens split over blockIdx.y
+template <int E_T>
+__global__ void router_dw_kernel(const bf16* __restrict__ x, const float* __restrict__ dlogits, float* __restrict__ dw,
+                                 int tokens, int hidden, int experts) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= hidden) return;
+  float acc[E_T];
+#pragma unroll
+  for (int e = 0; e < E_T; ++e) acc[e] = 0.f;
+  const int chunk = (tokens + gridDim.y - 1) / gridDim.y;
+  const int t0 = blockIdx.y * chunk, t1 = min(tokens, t0 + chunk);
+  for (int t = t0; t < t1; ++t) {
+    const float xv = __bfloat162float(x[(long long)t * hidden + col]);
+#pragma unroll
+    for (int e = 0; e < E_T; ++e) if (e < experts) acc[e] += dlogits[(long long)t * experts + e] * xv;
+  }
+#pragma unroll
+  for (int e = 0; e < E_T; ++e) if (e < experts) atomicAdd(dw + (long long)e * hidden + col, acc[e]);
+}
+
+// ---------------------------------------------------------------------------------- counting sort
+constexpr int PLAN_CHUNK = 256;
+
+__global__ void plan_hist_kernel(const int* __restrict__ ids, int n, int experts, int* __restrict__ block_counts) {
+  __shared__ int hist[MAX_E];
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int i = blockIdx.x * PLAN_CHUNK + threadIdx.x;
+  if (i < n) {
+    const int e = ids[i];
+    if (e >= 0 && e < experts) atomicAdd(&hist[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) block_counts[blockIdx.x * experts + e] = hist[e];
+}
+
+// single CTA: totals, padded group offsets, and per-(block, expert) first rows (in place in block_counts)
+__global__ void plan_scan_kernel(int* __restrict__ block_counts, int num_blocks, int experts, int block,
+                                 int* __restrict__ counts, int* __restrict__ padded_offsets) {
+  __shared__ int total[MAX_E];
+  __shared__ int start[MAX_E + 1];
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    int run = 0;
+    for (int b = 0; b < num_blocks; ++b) {
+      const int c = block_counts[b * experts + e];
+      block_counts[b * experts + e] = run;
+      run += c;
+    }
+    total[e] = run;
+    counts[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0;
+    for (int e = 0; e < experts; ++e) {
+      start[e] = off;
+      padded_offsets[e] = off;
+      off += (total[e] + block - 1) / block * block;
+    }
+    start[experts] = off;
+    padded_offsets[experts] = off;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < num_blocks * experts; i += blockDim.x) block_counts[i] += start[i % experts];
+}
+
+__global__ void plan_scatter_kernel(const int* __restrict__ ids, int n, int experts, const int* __restrict__ block_base,
+                                    int capacity, int* __restrict__ dest_row, int* __restrict__ src_slot) {
+  __shared__ int warp_cnt[PLAN_CHUNK / 32][MAX_E];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int i = blockIdx.x * PLAN_CHUNK + threadIdx.x;
+  int my = (i < n) ? ids[i] : -1;
+  if (my >= experts) my = -1;
+  int rank_in_warp = 0;
+  for (int e = 0; e < experts; ++e) {
+    const unsigned m = __ballot_sync(0xffffffffu, my == e);
+    if (lane == 0) warp_cnt[w][e] = __popc(m);
+    if (my == e) rank_in_warp = __popc(m & ((1u << lane) - 1u));
+  }
+  __syncthreads();
+  if (my >= 0) {
+    int before = 0;
+    for (int ww = 0; ww < w; ++ww) before += warp_cnt[ww][my];
+    const int row = block_base[blockIdx.x * experts + my] + before + rank_in_warp;
+    dest_row[i] = row;
+    if (row < capacity) src_slot[row] = i;
+  } else if (i < n) {
+    dest_row[i] = 0;
+  }
+}
+
+// ---------------------------------------------------------------------------------- gather / combine
+// out[r, :] = scale * x[src_slot[r] / top_k, :]; padding rows (src_slot < 0) are written as zeros;
+// rows at or beyond padded_offsets[E] are not touched.
+__global__ void gather_rows_kernel(const bf16* __restrict__ x, const int* __restrict__ src_slot, const int* __restrict__ padded_offsets,
+                                   int experts, const bf16* __restrict__ slot_scale, bf16* __restrict__ out, int cols, int top_k) {
+  const int r = blockIdx.x;
+  if (padded_offsets != nullptr && r >= padded_offsets[experts]) return;
+  const int slot = src_slot[r];
+  uint4* dst = reinterpret_cast<uint4*>(out + (long long)r * cols);
+  if (slot < 0) {
+    for (int i = threadIdx.x; i < cols / 8; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(x + (long long)(slot / top_k) * cols);
+  if (slot_scale == nullptr) {
+    for (int i = threadIdx.x; i < cols / 8; i += blockDim.x) dst[i] = src[i];
+  } else {
+    const float s = __bfloat162float(slot_scale[slot]);
+    for (int i = threadIdx.x; i < cols / 8; i += blockDim.x) {
+      float f[8]; unpack8r(src[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] *= s;
+      dst[i] = pack8r(f);
+    }
+  }
+}
+
+// out[t, :] = sum_c weights[t, c] * y[dest_row[t*k + c], :]
+__global__ void combine_rows_kernel(const bf16* __restrict__ y, const int* __restrict__ dest_row, const bf16* __restrict__ weights,
+                                    bf16* __restrict__ out, int cols, int top_k) {
+  const int t = blockIdx.x;
+  uint4* dst = reinterpret_cast<uint4*>(out + (long long)t * cols);
+  for (int i = threadIdx.x; i < cols / 8; i += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int c = 0; c < top_k; ++c) {
+      const int row = dest_row[(long long)t * top_k + c];
+      const float wv = weights != nullptr ? __bfloat162float(weights[(long long)t * top_k + c]) : 1.f;
+      float f[8]; unpack8r(reinterpret_cast<const uint4*>(y + (long long)row * cols)[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += wv * f[j];
+    }
+    dst[i] = pack8r(acc);
+  }
+}
+
+// dweights[t, c] = <y[dest_row[t*k + c], :], dout[t, :]>; one warp per (t, c)
+__global__ void combine_wgrad_kernel(const bf16* __restrict__ y, const int* __restrict__ dest_row, const bf16* __restrict__ dout,
+                                     bf16* __restrict__ dweights, int slots, int cols, int top_k) {
+  const int lane = threadIdx.x & 31;
+  const int s = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (s >= slots) return;
+  const int t = s / top_k;
+  const uint4* a = reinterpret_cast<const uint4*>(y + (long long)dest_row[s] * cols);
+  const uint4* b = reinterpret_cast<const uint4*>(dout + (long long)t * cols);
+  float acc = 0.f;
+  for (int i = lane; i < cols / 8; i += 32) {
+    float fa[8], fb[8]; unpack8r(a[i], fa); unpack8r(b[i], fb);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += fa[j] * fb[j];
+  }
+  acc = wsum(acc);
+  if (lane == 0) dweights[s] = __float2bfloat16(acc);
+}
+
+#define MDT_RT_CHECK() do { ++g_rt_launches; cudaError_t e_ = cudaGetLastError(); if (e_ != cudaSuccess) return -100 - (int)e_; } while (0)
+
+}  // namespace mdt
+
+using namespace mdt;
+
+extern "C" long long mdt_router_launch_count() { return g_rt_launches; }
+
+extern "C" int mdt_router_fwd(const void* x, const void* w, void* scores, void* weights, int* idx, int tokens, int hidden,
+                              int experts, int top_k, int normalize, cudaStream_t s) {
+  if (hidden % 8 != 0 || experts > MAX_E || top_k > MAX_K || top_k > experts) return -1;
+  if (tokens == 0) return 0;
+  const int grid = (tokens + 3) / 4;
+  if (experts <= 8)
+    router_fwd_kernel<8><<<grid, 128, 0, s>>>((const bf16*)x, (const bf16*)w, (bf16*)scores, (bf16*)weights, idx, tokens, hidden, experts, top_k, normalize);
+  else if (experts <= 16)
+    router_fwd_kernel<16><<<grid, 128, 0, s>>>((const bf16*)x, (const bf16*)w, (bf16*)scores, (bf16*)weights, idx, tokens, hidden, experts, top_k, normalize);
+  else
+    router_fwd_kernel<MAX_E><<<grid, 128, 0, s>>>((const bf16*)x, (const bf16*)w, (bf16*)scores, (bf16*)weights, idx, tokens, hidden, experts, top_k, normalize);
+  MDT_RT_CHECK();
+  return 0;
+}
+
+extern "C" int mdt_router_bwd(const void* x, const void* w, const void* scores, const void* weights, const int* idx,
+                              const void* dweights, const void* dscores, void* dx, float* dw, int tokens, int hidden, int experts,
+                              int top_k, int normalize, int accumulate_dx, cudaStream_t s) {
+  // `dw` must hold experts*hidden floats (accumulated into) followed by tokens*experts floats of scratch.
+  if (hidden % 8 != 0 || experts > MAX_E || top_k > MAX_K) return -1;
+  if (tokens == 0) return 0;
+  float* dlogits = dw + (long long)experts * hidden;
+  const int grid = (tokens + 3) / 4;
+  dim3 g2((hidden + 127) / 128, 16);
+#define RT_BWD(ET)                                                                                                          \
+  router_bwd_kernel<ET><<<grid, 128, 0, s>>>((const bf16*)x, (const bf16*)w, idx, (const bf16*)dweights, (const bf16*)dscores, \
+                                             (bf16*)dx, dlogits, tokens, hidden, experts, top_k, normalize, accumulate_dx);    \
+  MDT_RT_CHECK();                                                                                                           \
+  router_dw_kernel<ET><<<g2, 128, 0, s>>>((const bf16*)x, dlogits, dw, tokens, hidden, experts);                             \
+  MDT_RT_CHECK();
+  if (experts <= 8) { RT_BWD(8) } else if (experts <= 16) { RT_BWD(16) } else { RT_BWD(MAX_E) }
+#undef RT_BWD
+  return 0;
+}
+
+extern "C" int mdt_make_plan(const int* expert_ids, int num_slots, int num_experts, int block, int capacity, int* counts,
+                             int* padded_offsets, int* dest_row, int* src_slot, int* scratch, cudaStream_t s) {
+  if (num_experts > MAX_E || block < 1) return -1;
+  const int nb = (num_slots + PLAN_CHUNK - 1) / PLAN_CHUNK;
+  cudaMemsetAsync(src_slot, 0xFF, (size_t)capacity * sizeof(int), s);
+  if (nb > 0) {
+    plan_hist_kernel<<<nb, PLAN_CHUNK, 0, s>>>(expert_ids, num_slots, num_experts, scratch);
+    MDT_RT_CHECK();
+  }
+  plan_scan_kernel<<<1, 256, 0, s>>>(scratch, nb, num_experts, block, counts, padded_offsets);
+  MDT_RT_CHECK();
+  if (nb > 0) {
+    plan_scatter_kernel<<<nb, PLAN_CHUNK, 0, s>>>(expert_ids, num_slots, num_experts, scratch, capacity, dest_row, src_slot);
+    MDT_RT_CHECK();
+  }
+  return 0;
+}
+
+extern "C" int mdt_gather_rows(const void* x, const int* src_slot, const int* padded_offsets, int num_experts, const void* slot_scale,
+                               void* out, int capacity, int cols, int top_k, cudaStream_t s) {
+  if (cols % 8 != 0) return -1;
+  if (capacity == 0) return 0;
+  gather_rows_kernel<<<capacity, 128, 0, s>>>((const bf16*)x, src_slot, padded_offsets, num_experts, (const bf16*)slot_scale, (bf16*)out, cols, top_k);
+  MDT_RT_CHECK();
+  return 0;
+}
+extern "C" int mdt_combine_rows(const void* y, const int* dest_row, const void* weights, void* out, int tokens, int cols, int top_k,
+                                cudaStream_t s) {
+  if (cols % 8 != 0) return -1;
+  if (tokens == 0) return 0;
+  combine_rows_kernel<<<tokens, 128, 0, s>>>((const bf16*)y, dest_row, (const bf16*)weights, (bf16*)out, cols, top_k);
+  MDT_RT_CHECK();
+  return 0;
+}
+extern "C" int mdt_combine_wgrad(const void* y, const int* dest_row, const void* dout, void* dweights, int tokens, int cols, int top_k,
+                                 cudaStream_t s) {
+  if (cols % 8 != 0) return -1;
+  const int slots = tokens * top_k;
+  if (slots == 0) return 0;
+  combine_wgrad_kernel<<<(slots + 3) / 4, 128, 0, s>>>((const bf16*)y, dest_row, (const bf16*)dout, (bf16*)dweights, slots, cols, top_k);
+  MDT_RT_CHECK();
+  return 0;
+}

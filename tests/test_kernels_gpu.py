@@ -1,0 +1,287 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 statement of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / b.norm().clamp(min=1e-12)).item()
+
+
+def _close(a, b, tol=2e-2, name=""):
+    err = _rel_err(a, b)
+    assert err < tol, f"{name}: relative error {err:.4g} (tolerance {tol})"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from moe_distributed_training_b200.ops import cuda_ops
+    return cuda_ops
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
+
+
+# ------------------------------------------------------------------------------------------ GEMM family
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 128), (300, 520, 200), (1024, 4096, 4096), (77, 136, 4096)])
+def test_gemm_nt(ops, M, N, K):
+    torch.manual_seed(0)
+    x, w = _rand(M, K), _rand(N, K, scale=0.05)
+    y = ops.mm_nt(x, w)
+    _close(y, x.float() @ w.float().t(), name=f"nt {M}x{N}x{K}")
+    ops.check_status(DEV)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (300, 520, 200), (1024, 4096, 1024)])
+def test_gemm_nn(ops, M, N, K):
+    torch.manual_seed(1)
+    x, w = _rand(M, K), _rand(K, N, scale=0.05)
+    _close(ops.mm_nn(x, w), x.float() @ w.float(), name=f"nn {M}x{N}x{K}")
+    ops.check_status(DEV)
+
+
+@pytest.mark.parametrize("R,M,N", [(128, 128, 128), (200, 136, 264), (1000, 1024, 4096), (64, 16, 512), (512, 4096, 16)])
+def test_gemm_tn(ops, R, M, N):
+    torch.manual_seed(2)
+    a, b = _rand(R, M), _rand(R, N, scale=0.05)
+    _close(ops.mm_tn(a, b), a.float().t() @ b.float(), name=f"tn {R}x{M}x{N}")
+    out32 = torch.ones(M, N, device=DEV)
+    ops.mm_tn(a, b, out=out32, alpha=0.5, accumulate=True)
+    _close(out32, 1.0 + 0.5 * (a.float().t() @ b.float()), name="tn accumulate fp32")
+    ops.check_status(DEV)
+
+
+def test_gemm_lora_segment(ops):
+    torch.manual_seed(3)
+    M, N, K, r = 300, 512, 1024, 16
+    x, w = _rand(M, K), _rand(N, K, scale=0.03)
+    t, b = _rand(M, r), _rand(N, r, scale=0.1)
+    y = ops.mm_nt(x, w, lora=(t, b))
+    _close(y, x.float() @ w.float().t() + t.float() @ b.float().t(), name="nt + lora")
+    w2, b2 = _rand(K, N, scale=0.03), _rand(r, N, scale=0.1)
+    y2 = ops.mm_nn(x, w2, lora=(t, b2))
+    _close(y2, x.float() @ w2.float() + t.float() @ b2.float(), name="nn + lora")
+    ops.check_status(DEV)
+
+
+def _plan(ops, T, k, E, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    logits = torch.randn(T, E, device=DEV, generator=g)
+    top = logits.topk(k, dim=-1).indices.int()
+    return top, ops.make_plan(top, E)
+
+
+@pytest.mark.parametrize("T,k,E", [(64, 2, 4), (1000, 2, 8), (5000, 2, 8), (300, 1, 2)])
+def test_make_plan(ops, T, k, E):
+    from moe_distributed_training_b200.ops import reference
+    top, plan = _plan(ops, T, k, E)
+    ref = reference.make_plan(top.cpu(), E)
+    assert torch.equal(plan.tokens_per_expert.cpu(), ref.tokens_per_expert)
+    assert torch.equal(plan.padded_offsets.cpu(), ref.padded_offsets)
+    assert torch.equal(plan.dest_row.cpu(), ref.dest_row)
+    assert torch.equal(plan.src_slot.cpu(), ref.src_slot)
+
+
+def test_gather_combine(ops):
+    from moe_distributed_training_b200.ops import reference
+    torch.manual_seed(4)
+    T, k, E, H = 700, 2, 8, 512
+    top, plan = _plan(ops, T, k, E)
+    x = _rand(T, H).requires_grad_(True)
+    w = torch.rand(T, k, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    xg = ops.gather_rows(x, plan)
+    n_used = int(plan.padded_offsets[-1])
+    ref_xg = reference.gather_rows(x.detach().float(), plan.src_slot, k)
+    _close(xg[:n_used], ref_xg[:n_used], 1e-6, "gather")
+    y = ops.combine_rows(xg * 1.0, plan, w)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = reference.combine_rows(reference.gather_rows(xr, plan.src_slot, k), plan.dest_row, wr, k)
+    _close(y, yr, 1e-2, "combine")
+    go = _rand(T, H)
+    y.backward(go)
+    yr.backward(go.float())
+    _close(x.grad, xr.grad, 1e-2, "combine->gather dx")
+    _close(w.grad, wr.grad, 2e-2, "combine dweights")
+
+
+@pytest.mark.parametrize("T,E,H,F,lora", [(600, 4, 256, 512, False), (1500, 8, 1024, 2048, False), (600, 4, 256, 512, True)])
+def test_grouped_swiglu_mlp(ops, T, E, H, F, lora):
+    from moe_distributed_training_b200.ops import reference
+    torch.manual_seed(5)
+    k, r = 2, 16
+    top, plan = _plan(ops, T, k, E)
+    x = _rand(T, H)
+    ws = [(_rand(E, F, H, scale=0.05)).requires_grad_(True) for _ in range(3)]
+    lo, lo_ref, lparams = None, None, []
+    if lora:
+        lo, lo_ref = {}, {}
+        for name in ("w1", "w2", "w3"):
+            fin, fout = (F, H) if name == "w2" else (H, F)
+            A = _rand(E, fin, r, scale=0.05).requires_grad_(True)
+            B = _rand(E, r, fout, scale=0.05).requires_grad_(True)
+            lparams += [A, B]
+            lo[name] = (A, B, 2.0)
+    xg = ops.gather_rows(x, plan).detach().requires_grad_(True)
+    y = ops.grouped_swiglu_mlp(xg, ws[0], ws[1], ws[2], plan, lo, 0.5)
+    # fp32 reference on the same rows
+    xr = xg.detach().float().requires_grad_(True)
+    wr = [w.detach().float().requires_grad_(True) for w in ws]
+    lr_params = []
+    if lora:
+        lo_ref = {}
+        for i, name in enumerate(("w1", "w2", "w3")):
+            A, B = lparams[2 * i].detach().float().requires_grad_(True), lparams[2 * i + 1].detach().float().requires_grad_(True)
+            lr_params += [A, B]
+            lo_ref[name] = (A, B, 2.0)
+    yr = reference.grouped_swiglu_mlp(xr, wr[0], wr[1], wr[2], plan.padded_offsets, plan.tokens_per_expert, lo_ref, 0.5)
+    n_used = int(plan.padded_offsets[-1])
+    valid = (plan.src_slot[:n_used] >= 0)
+    _close(y[:n_used][valid], yr[:n_used][valid], 2e-2, "mlp forward")
+    go = torch.zeros_like(y)
+    go[:n_used][valid] = _rand(int(valid.sum()), H)
+    y.backward(go)
+    yr.backward(go.float())
+    _close(xg.grad[:n_used][valid], xr.grad[:n_used][valid], 3e-2, "mlp dx")
+    for i in range(3):
+        _close(ws[i].grad, wr[i].grad, 3e-2, f"mlp dw{i + 1}")
+    for i, (p, q) in enumerate(zip(lparams, lr_params)):
+        _close(p.grad, q.grad, 4e-2, f"mlp lora grad {i}")
+    ops.check_status(DEV)
+
+
+# ------------------------------------------------------------------------------------------ small ops
+def test_linear_lora_backward(ops):
+    from moe_distributed_training_b200.ops import reference
+    torch.manual_seed(6)
+    M, K, N, r = 200, 512, 1024, 16
+    x = _rand(M, K).requires_grad_(True)
+    w = _rand(N, K, scale=0.05).requires_grad_(True)
+    A = _rand(r, K, scale=0.05).requires_grad_(True)
+    B = _rand(N, r, scale=0.05).requires_grad_(True)
+    y = ops.linear(x, w, (A, B, 2.0))
+    ref_in = [t.detach().float().requires_grad_(True) for t in (x, w, A, B)]
+    yr = reference.linear(ref_in[0], ref_in[1], (ref_in[2], ref_in[3], 2.0))
+    _close(y, yr, 2e-2, "linear+lora fwd")
+    go = _rand(M, N)
+    y.backward(go); yr.backward(go.float())
+    for t, rt, name in zip((x, w, A, B), ref_in, "x w A B".split()):
+        _close(t.grad, rt.grad, 3e-2, f"linear+lora d{name}")
+
+
+def test_rmsnorm(ops):
+    from moe_distributed_training_b200.ops import reference
+    torch.manual_seed(7)
+    x = _rand(333, 4096).requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(4096, device=DEV)).to(torch.bfloat16).requires_grad_(True)
+    y = ops.rmsnorm(x, w, 1e-5)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = reference.rmsnorm(xr, wr, 1e-5)
+    _close(y, yr, 1e-2, "rmsnorm fwd")
+    go = _rand(333, 4096)
+    y.backward(go); yr.backward(go.float())
+    _close(x.grad, xr.grad, 1e-2, "rmsnorm dx")
+    _close(w.grad, wr.grad, 2e-2, "rmsnorm dw")
+
+
+def test_rope(ops):
+    from moe_distributed_training_b200.ops import reference
+    torch.manual_seed(8)
+    x = _rand(500, 8, 128).requires_grad_(True)
+    pos = torch.arange(500, device=DEV, dtype=torch.int32)
+    y = ops.rope(x, pos, 1e6)
+    xr = x.detach().float().requires_grad_(True)
+    yr = reference.rope(xr, pos, 1e6)
+    _close(y, yr, 1e-2, "rope fwd")
+    go = _rand(500, 8, 128)
+    y.backward(go); yr.backward(go.float())
+    _close(x.grad, xr.grad, 1e-2, "rope bwd")
+
+
+def test_router(ops):
+    from moe_distributed_training_b200.ops import reference
+    torch.manual_seed(9)
+    T, H, E, k = 777, 1024, 8, 2
+    x = _rand(T, H).requires_grad_(True)
+    w = _rand(E, H, scale=0.05).requires_grad_(True)
+    s, wt, idx = ops.router(x, w, k, True)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    sr, wtr, idxr = reference.router(xr, wr, k, True)
+    assert (idx == idxr).float().mean() > 0.995
+    _close(s, sr, 1e-2, "router scores")
+    same = (idx == idxr).all(dim=1)
+    _close(wt[same], wtr[same], 1e-2, "router weights")
+    go = torch.rand(T, k, device=DEV).to(torch.bfloat16)
+    go = go * same[:, None]
+    wt.backward(go)
+    wtr.backward(go.float())
+    _close(x.grad, xr.grad, 3e-2, "router dx")
+    _close(w.grad, wr.grad, 3e-2, "router dw")
+
+
+def test_embedding_and_cross_entropy(ops):
+    from moe_distributed_training_b200.ops import reference
+    torch.manual_seed(10)
+    T, H, V = 300, 256, 2048
+    table = _rand(V, H).requires_grad_(True)
+    ids = torch.randint(0, V, (T,), device=DEV)
+    e = ops.embedding(ids, table)
+    assert torch.equal(e, table.detach()[ids])
+    e.backward(torch.ones_like(e))
+    ref = torch.zeros(V, H, device=DEV)
+    ref.index_add_(0, ids, torch.ones(T, H, device=DEV))
+    _close(table.grad, ref, 1e-3, "embedding bwd")
+    hidden = _rand(T, H).requires_grad_(True)
+    head = _rand(V, H, scale=0.05).requires_grad_(True)
+    labels = torch.randint(0, V, (T,), device=DEV)
+    labels[: T // 3] = -100
+    ls, n = ops.cross_entropy_sum(hidden, head, labels)
+    loss = ls / n
+    hr, wr = hidden.detach().float().requires_grad_(True), head.detach().float().requires_grad_(True)
+    lsr, nr = reference.cross_entropy_sum(hr, wr, labels)
+    lossr = lsr / nr
+    assert abs(loss.item() - lossr.item()) < 2e-2 * abs(lossr.item())
+    assert int(n.item()) == int(nr.item())
+    (loss * 3.0).backward(); (lossr * 3.0).backward()
+    _close(hidden.grad, hr.grad, 3e-2, "ce dhidden")
+    _close(head.grad, wr.grad, 3e-2, "ce dhead")
+
+
+def test_adamw(ops):
+    from moe_distributed_training_b200.ops import reference
+    torch.manual_seed(11)
+    shapes = [(1000,), (257, 33), (4096, 512)]
+    ps = [_rand(*s) for s in shapes]
+    gs = [_rand(*s, scale=0.1) for s in shapes]
+    ms = [torch.zeros_like(p) for p in ps]
+    vs = [torch.zeros_like(p) for p in ps]
+    ref = [[t.clone().float() for t in group] for group in (ps, gs, ms, vs)]
+    for step in (1, 2, 3):
+        ops.adamw_multi(ps, gs, ms, vs, 1e-2, 0.9, 0.999, 1e-8, 0.01, step, 0.5)
+        for p, g, m, v in zip(*ref):
+            reference.adamw_step(p, g, m, v, 1e-2, 0.9, 0.999, 1e-8, 0.01, step, 0.5)
+    for p, pr in zip(ps, ref[0]):
+        _close(p, pr, 1e-2, "adamw param")
+
+
+def test_end_to_end_matches_reference_path(ops):
+    """One training step of a small bf16 model: CUDA kernels vs the PyTorch statement of every op."""
+    from moe_distributed_training_b200 import MixtralConfig
+    from moe_distributed_training_b200.data.synthetic import SyntheticInstructionDataset, batches
+    from moe_distributed_training_b200.train.engine import build_engine
+    cfg = MixtralConfig(vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                        num_attention_heads=2, num_key_value_heads=1, head_dim=128, num_local_experts=4, num_experts_per_tok=2)
+    ds = SyntheticInstructionDataset(cfg.vocab_size, 2, 100, 200)
+    mbs = list(batches(ds, 1))
+    eng = build_engine(cfg, dtype=torch.bfloat16, device_type="cuda", learning_rate=1e-3, seed=0)
+    l_gpu = [float(eng.train_step(mbs)["loss"]) for _ in range(3)]
+    ref = build_engine(cfg, dtype=torch.float32, device_type="cpu", learning_rate=1e-3, seed=0)
+    l_ref = [float(ref.train_step(mbs)["loss"]) for _ in range(3)]
+    ops.check_status(DEV)
+    for a, b in zip(l_gpu, l_ref):
+        assert abs(a - b) < 0.05 * abs(b), (l_gpu, l_ref)
+    assert l_gpu[-1] < l_gpu[0]
