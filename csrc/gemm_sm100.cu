@@ -385,6 +385,10 @@ extern "C" long long mdt_gemm_launch_count() { return mdt::g_launches; }
 
 extern "C" int mdt_gemm(const MdtGemmDesc* d, cudaStream_t stream) {
   using namespace mdt;
+  // Tensor-map encoding is a driver call: make sure this host thread has the device's primary context
+  // bound (a thread that has issued no runtime work yet, e.g. a fresh autograd worker, has none).
+  static thread_local bool context_bound = false;
+  if (!context_bound) { cudaFree(nullptr); context_bound = true; }
   if (g_num_sms == 0) {
     int dev = 0;
     cudaGetDevice(&dev);

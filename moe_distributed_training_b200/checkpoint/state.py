@@ -1,0 +1,200 @@
+"""Saving models (HF Mixtral safetensors, peft adapter files) and resumable training state.
+
+The reference never writes a checkpoint from its FSDP2 script and has no mapping
+from its expert layout back to HF keys (train_accelerate_fsdp2.py has no save;
+accelerate.yaml:30 only configures FSDP1's FULL_STATE_DICT).  This module adds:
+
+  save_model            HF-format export.  Every rank writes the experts it owns to
+                        its own `model-rank{r}.safetensors`; rank 0 also writes the
+                        gathered dense parameters and the merged index json.
+  save_adapter          LoRA factors under peft's key names in `adapter_model.safetensors`
+                        plus `adapter_config.json`.
+  save/load_training_state   per-rank optimizer moments, scheduler and step counter.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Dict
+
+import torch
+import torch.distributed as dist
+from safetensors.torch import load_file, save_file
+
+from . import hf_safetensors as hfst
+
+
+def _world():
+    return (dist.get_rank(), dist.get_world_size()) if dist.is_initialized() else (0, 1)
+
+
+def _gather_dense(engine) -> Dict[str, torch.Tensor]:
+    out = {}
+    for u in engine.runner.all_units():
+        for name, t in engine.runner.full_state(u).items():
+            out[name] = t
+    return out
+
+
+def _expert_ids(engine, moe):
+    args = moe.args
+    E = args.moe_num_experts
+    if args.moe_expert_model_parallelism and args.expert_parallel_group is not None:
+        r, n = dist.get_rank(args.expert_parallel_group), dist.get_world_size(args.expert_parallel_group)
+        return list(range(r * (E // n), (r + 1) * (E // n)))
+    return list(range(E))
+
+
+def save_model(engine, out_dir: str):
+    """Write the model in HF Mixtral safetensors layout (base weights; adapters go to save_adapter)."""
+    rank, world = _world()
+    os.makedirs(out_dir, exist_ok=True)
+    dense = _gather_dense(engine)  # collective: every rank participates
+    mine: Dict[str, torch.Tensor] = {}
+    layers = engine.model.model.layers
+    for i, layer in enumerate(layers):
+        moe = layer.block_sparse_moe
+        prefix = f"model.layers.{i}"
+        if moe.router.layer.weight is None:
+            # experts were sharded like dense parameters: rebuild the HF tensors from the gathered flat state
+            E, F, H = moe.args.moe_num_experts, moe.args.ffn_hidden_size, moe.args.hidden_size
+            if rank == 0:
+                mine[f"{prefix}.block_sparse_moe.gate.weight"] = dense.pop(f"{prefix}.block_sparse_moe.router.layer.weight").cpu().contiguous()
+                for w in ("w1", "w2", "w3"):
+                    full = dense.pop(f"{prefix}.block_sparse_moe.experts.mlp.{w}").view(E, F, H)
+                    for e in range(E):
+                        t = full[e].t() if w == "w2" else full[e]
+                        mine[f"{prefix}.block_sparse_moe.experts.{e}.{w}.weight"] = t.cpu().contiguous()
+            continue
+        if moe.args.tensor_parallel_size > 1:
+            mine.update(_export_tp_layer(moe, prefix))
+            continue
+        ids = _expert_ids(engine, moe)
+        dp_rank = dist.get_rank(engine.runner.expert_dp_group) if (engine.runner.expert_dp_group is not None) else 0
+        if dp_rank == 0:  # one replica writes
+            exp = hfst.export_moe_layer(moe, prefix, "block_sparse_moe", ids)
+            if rank != 0:
+                exp.pop(f"{prefix}.block_sparse_moe.gate.weight")
+            mine.update(exp)
+    files = {}
+    if rank == 0:
+        for name, t in dense.items():
+            if "lora_" in name:
+                continue
+            mine[name] = t.cpu().contiguous()
+    if mine:
+        files[f"model-rank{rank:05d}.safetensors"] = mine
+    wm = hfst.save_sharded(files, out_dir, write_index=False) if files else {}
+    if world > 1:
+        maps = [None] * world
+        dist.all_gather_object(maps, wm)
+        dist.barrier()
+    else:
+        maps = [wm]
+    if rank == 0:
+        hfst.merge_index(out_dir, maps)
+        engine.model.config.save_pretrained(out_dir)
+    if any("lora_" in n for n, _ in engine.model.named_parameters()) or any("lora_" in n for n in dense):
+        save_adapter(engine, out_dir, dense)
+    if world > 1:
+        dist.barrier()
+
+
+def _export_tp_layer(moe, prefix):
+    """Tensor-parallel experts: gather the FFN slices over the group, group rank 0 writes."""
+    args = moe.args
+    group = args.tensor_parallel_group
+    n, r = dist.get_world_size(group), dist.get_rank(group)
+    E, Fl, H = args.moe_num_experts, moe.experts.mlp.features_per_rank, args.hidden_size
+    out = {}
+    for w in ("w1", "w2", "w3"):
+        local = getattr(moe.experts.mlp, w).detach().view(E, Fl, H).contiguous()
+        parts = [torch.empty_like(local) for _ in range(n)]
+        dist.all_gather(parts, local, group=group)
+        if r == 0 and dist.get_rank() == 0:
+            full = torch.cat(parts, dim=1)
+            for e in range(E):
+                t = full[e].t() if w == "w2" else full[e]
+                out[f"{prefix}.block_sparse_moe.experts.{e}.{w}.weight"] = t.cpu().contiguous()
+    if r == 0 and dist.get_rank() == 0:
+        out[f"{prefix}.block_sparse_moe.gate.weight"] = moe.router.layer.weight.detach().cpu().contiguous()
+    return out
+
+
+def save_adapter(engine, out_dir: str, dense: Dict[str, torch.Tensor] = None):
+    """peft-style adapter files.  Expert adapters are stored per global expert:
+    `...block_sparse_moe.experts.{e}.{w}.lora_A.weight` is `[r, in]`, `lora_B.weight` is `[out, r]`."""
+    rank, world = _world()
+    dense = dense if dense is not None else _gather_dense(engine)
+    tensors = {}
+    if rank == 0:
+        for name, t in dense.items():
+            if "lora_" in name:
+                key = "base_model.model." + name.replace(".default", "")
+                tensors[key] = t.cpu().contiguous()
+    for i, layer in enumerate(engine.model.model.layers):
+        experts = layer.block_sparse_moe.experts
+        lora = getattr(experts, "lora", None)
+        if lora is None:
+            continue
+        dp_rank = dist.get_rank(engine.runner.expert_dp_group) if engine.runner.expert_dp_group is not None else 0
+        if dp_rank != 0:
+            continue
+        ids = _expert_ids(engine, layer.block_sparse_moe)
+        for w in lora.lora_A:
+            A, B = lora.lora_A[w].detach(), lora.lora_B[w].detach()
+            for j, e in enumerate(ids):
+                base = f"base_model.model.model.layers.{i}.block_sparse_moe.experts.{e}.{w}"
+                tensors[f"{base}.lora_A.weight"] = A[j].t().cpu().contiguous()
+                tensors[f"{base}.lora_B.weight"] = B[j].t().cpu().contiguous()
+    fname = "adapter_model.safetensors" if world == 1 else f"adapter_model-rank{rank:05d}.safetensors"
+    if tensors:
+        save_file(tensors, os.path.join(out_dir, fname), metadata={"format": "pt"})
+    if rank == 0:
+        cfg = engine.model.peft_config["default"].to_dict() if hasattr(engine.model, "peft_config") else {}
+        with open(os.path.join(out_dir, "adapter_config.json"), "w") as f:
+            json.dump(cfg, f, indent=2)
+
+
+def save_training_state(engine, out_dir: str, step: int):
+    rank, _ = _world()
+    os.makedirs(out_dir, exist_ok=True)
+    params = [p for g in engine.optimizer.param_groups for p in g["params"]]
+    state = {"step": step, "scheduler": engine.scheduler.state_dict(), "moments": []}
+    for p in params:
+        st = engine.optimizer.state.get(p, {})
+        state["moments"].append({k: (v.cpu() if torch.is_tensor(v) else v) for k, v in st.items()})
+    state["params"] = [p.detach().cpu() for p in params]
+    torch.save(state, os.path.join(out_dir, f"training_state-rank{rank:05d}.pt"))
+
+
+def load_training_state(engine, in_dir: str) -> int:
+    rank, _ = _world()
+    state = torch.load(os.path.join(in_dir, f"training_state-rank{rank:05d}.pt"), map_location="cpu", weights_only=False)
+    params = [p for g in engine.optimizer.param_groups for p in g["params"]]
+    assert len(params) == len(state["params"]), "training state does not match this model / sharding"
+    with torch.no_grad():
+        for p, saved, st in zip(params, state["params"], state["moments"]):
+            p.copy_(saved.to(p.device))
+            if st:
+                engine.optimizer.state[p] = {k: (v.to(p.device) if torch.is_tensor(v) else v) for k, v in st.items()}
+    engine.scheduler.load_state_dict(state["scheduler"])
+    engine.step_count = state["step"]
+    return int(state["step"])
+
+
+def load_adapter(engine, in_dir: str):
+    """Load attention adapters written by save_adapter on a single rank."""
+    path = os.path.join(in_dir, "adapter_model.safetensors")
+    tensors = load_file(path)
+    named = dict(engine.model.named_parameters())
+    missing = []
+    for key, t in tensors.items():
+        name = key[len("base_model.model."):].replace(".lora_A.weight", ".lora_A.default.weight").replace(
+            ".lora_B.weight", ".lora_B.default.weight")
+        if name in named:
+            with torch.no_grad():
+                named[name].copy_(t.to(named[name].dtype))
+        else:
+            missing.append(key)
+    return missing

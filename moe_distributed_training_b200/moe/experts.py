@@ -64,5 +64,14 @@ class SparseMLPv2(nn.Module):
     def forward(self, xg: torch.Tensor, plan) -> torch.Tensor:
         """xg: block-padded expert-grouped rows [R, hidden]; returns rows of the same layout."""
         w1, w2, w3 = self.weight_views()
+        wgrad_out = None
+        if xg.is_cuda and ops.get_backend() == "native" and torch.is_grad_enabled() and self.w1.requires_grad:
+            # the weight-gradient GEMMs add straight into .grad (scaled), so no per-micro-batch
+            # gradient tensors of the size of the expert weights are created
+            E, Fr, H = self.experts_per_rank, self.features_per_rank, self.args.hidden_size
+            for w in (self.w1, self.w2, self.w3):
+                if w.grad is None:
+                    w.grad = torch.zeros_like(w)
+            wgrad_out = tuple(w.grad.view(E, Fr, H) for w in (self.w1, self.w2, self.w3))
         return ops.grouped_swiglu_mlp(xg, w1, w2, w3, plan, self.lora_views(),
-                                      wgrad_scale=self.gradient_scale or 1.0)
+                                      wgrad_scale=self.gradient_scale or 1.0, wgrad_out=wgrad_out)

@@ -5,7 +5,7 @@ import torch
 import torch.nn.functional as F
 
 
-def attention(q, k, v, cu_seqlens, max_seqlen=None):
+def sdpa_attention(q, k, v, cu_seqlens, max_seqlen=None):
     """q [T, Hq, d], k/v [T, Hkv, d]; one causal attention problem per sequence in cu_seqlens."""
     T = q.shape[0]
     nseq = cu_seqlens.numel() - 1
@@ -21,3 +21,7 @@ def attention(q, k, v, cu_seqlens, max_seqlen=None):
                                            v[s:e].transpose(0, 1)[None], is_causal=True, enable_gqa=True)
         outs.append(o[0].transpose(0, 1))
     return outs[0].contiguous() if len(outs) == 1 else torch.cat(outs, 0)
+
+
+def attention(q, k, v, cu_seqlens, max_seqlen=None):
+    return sdpa_attention(q, k, v, cu_seqlens, max_seqlen)

@@ -326,19 +326,61 @@ def grouped_swiglu_mlp(xg, w1, w2, w3, plan, lora=None, wgrad_scale=1.0, wgrad_o
     return _GroupedSwiGLUMLP.apply(xg.contiguous(), w1, w2, w3, plan, lora, float(wgrad_scale), wgrad_out, ids, *tensors)
 
 
-def grouped_linear(x, w, plan, trans_b, lora=None):
-    """Forward-only grouped linear (used by tests and the isolated kernel benchmarks)."""
-    G = w.shape[0]
-    N = w.shape[1] if trans_b else w.shape[2]
-    K = x.shape[1]
-    out = torch.empty(x.shape[0], N, dtype=x.dtype, device=x.device)
-    kw = {}
-    if lora is not None:
-        A, B, s = lora
-        t = torch.empty(x.shape[0], A.shape[2], dtype=x.dtype, device=x.device)
-        _g(1, x, False, A, True, t, A.shape[2], K, plan, alpha=s)
-        kw = dict(A_l=t, B_l=B, b_mn_l=True, K_l=A.shape[2])
-    return _g(1, x.contiguous(), False, w, not trans_b, out, N, K, plan, **kw)
+class _GroupedLinear(torch.autograd.Function):
+    """y[rows of g] = x[rows of g] W_g (+ s (x A_g) B_g); W is [G,N,K] if trans_b else [G,K,N]."""
+
+    @staticmethod
+    def forward(ctx, x, w, plan, trans_b, A, B, scaling, wgrad_scale):
+        x = x.contiguous()
+        R, K = x.shape
+        N = w.shape[1] if trans_b else w.shape[2]
+        out = torch.empty(R, N, dtype=x.dtype, device=x.device)
+        kw, t = {}, None
+        if A is not None:
+            r = A.shape[2]
+            t = torch.empty(R, r, dtype=x.dtype, device=x.device)
+            _g(1, x, False, A, True, t, r, K, plan, alpha=scaling)
+            kw = dict(A_l=t, B_l=B, b_mn_l=True, K_l=r)
+        _g(1, x, False, w, not trans_b, out, N, K, plan, **kw)
+        ctx.plan, ctx.trans_b, ctx.scaling, ctx.ws = plan, trans_b, scaling, wgrad_scale
+        ctx.save_for_backward(x, w, A, B, t)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, A, B, t = ctx.saved_tensors
+        plan, trans_b, ws = ctx.plan, ctx.trans_b, ctx.ws
+        dy = dy.contiguous()
+        R, K = x.shape
+        N = dy.shape[1]
+        dx = dw = dA = dB = None
+        kw, dt = {}, None
+        if A is not None:
+            r = A.shape[2]
+            dt = torch.empty(R, r, dtype=x.dtype, device=x.device)
+            _g(1, dy, False, B, False, dt, r, N, plan, alpha=ctx.scaling)      # s * dy B^T
+            kw = dict(A_l=dt, B_l=A, b_mn_l=False, K_l=r)
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty(R, K, dtype=x.dtype, device=x.device)
+            _g(1, dy, False, w, trans_b, dx, K, N, plan, **kw)
+        if ctx.needs_input_grad[1]:
+            dw = torch.empty_like(w)
+            if trans_b:
+                _g(2, dy, True, x, True, dw, K, 0, plan, alpha=ws)
+            else:
+                _g(2, x, True, dy, True, dw, N, 0, plan, alpha=ws)
+        if A is not None and ctx.needs_input_grad[4]:
+            dA = torch.empty_like(A); _g(2, x, True, dt, True, dA, A.shape[2], 0, plan, alpha=ws)
+        if B is not None and ctx.needs_input_grad[5]:
+            dB = torch.empty_like(B); _g(2, t, True, dy, True, dB, N, 0, plan, alpha=ws)
+        return dx, dw, None, None, dA, dB, None, None
+
+
+def grouped_linear(x, w, plan, trans_b, lora=None, wgrad_scale=1.0):
+    if lora is None:
+        return _GroupedLinear.apply(x, w, plan, trans_b, None, None, 0.0, float(wgrad_scale))
+    A, B, s = lora
+    return _GroupedLinear.apply(x, w, plan, trans_b, A, B, float(s), float(wgrad_scale))
 
 
 # ----------------------------------------------------------------------------------------------- small ops

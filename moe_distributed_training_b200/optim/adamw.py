@@ -44,7 +44,8 @@ class FusedAdamW(torch.optim.Optimizer):
                 ps.append(p.data); gs.append(p.grad); ms.append(st["exp_avg"]); vs.append(st["exp_avg_sq"])
             if not ps:
                 continue
-            if ps[0].is_cuda:
+            from .. import ops as _ops
+            if ps[0].is_cuda and _ops.get_backend() == "native":
                 from ..ops import cuda_ops
                 cuda_ops.adamw_multi(ps, gs, ms, vs, group["lr"], b1, b2, group["eps"],
                                      group["weight_decay"], step, self.grad_scale)
