@@ -76,7 +76,7 @@ int mdt_attention_fwd(const void* q, const void* k, const void* v, void* o, floa
                       int num_seqs, int total_tokens, int max_seqlen, int heads_q, int heads_kv, int head_dim,
                       float scale, cudaStream_t s);
 int mdt_attention_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
-                      void* dq, void* dk, void* dv, float* delta, const int* cu_seqlens, int num_seqs, int total_tokens,
+                      void* dq, void* dk, void* dv, float* scratch, const int* cu_seqlens, int num_seqs, int total_tokens,
                       int max_seqlen, int heads_q, int heads_kv, int head_dim, float scale, cudaStream_t s);
 
 long long mdt_launch_count(void);

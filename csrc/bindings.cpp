@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "api.h"
+#include "comm.h"
 
 extern "C" long long mdt_elementwise_launch_count();
 extern "C" long long mdt_router_launch_count();
@@ -224,8 +225,101 @@ Tensor combine_wgrad(const Tensor& y, const Tensor& dest_row, const Tensor& dout
   return dw;
 }
 
+// q [T, Hq, 128], k/v [T, Hkv, 128] -> (o [T, Hq, 128], lse [T, Hq])
+std::vector<Tensor> attention_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& cu_seqlens, int64_t max_seqlen, double scale) {
+  CHECK_BF16(q); CHECK_BF16(k); CHECK_BF16(v);
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(q.is_contiguous() && k.is_contiguous() && v.is_contiguous() && cu_seqlens.scalar_type() == at::kInt);
+  const int T = (int)q.size(0), Hq = (int)q.size(1), Hkv = (int)k.size(1), D = (int)q.size(2);
+  auto o = torch::empty_like(q);
+  auto lse = torch::empty({T, Hq}, q.options().dtype(at::kFloat));
+  check(mdt_attention_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), cu_seqlens.data_ptr<int>(),
+                          (int)cu_seqlens.numel() - 1, T, (int)max_seqlen, Hq, Hkv, D, (float)scale, cur_stream()), "attention_fwd");
+  return {o, lse};
+}
+std::vector<Tensor> attention_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& dout, const Tensor& lse,
+                                  const Tensor& cu_seqlens, int64_t max_seqlen, double scale) {
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(dout.is_contiguous() && o.is_contiguous());
+  const int T = (int)q.size(0), Hq = (int)q.size(1), Hkv = (int)k.size(1), D = (int)q.size(2);
+  auto dq = torch::empty_like(q), dk = torch::empty_like(k), dv = torch::empty_like(v);
+  auto scratch = torch::empty({(int64_t)T * Hq * (1 + 3 * D)}, q.options().dtype(at::kFloat));
+  check(mdt_attention_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dout.data_ptr(), lse.data_ptr<float>(), dq.data_ptr(),
+                          dk.data_ptr(), dv.data_ptr(), scratch.data_ptr<float>(), cu_seqlens.data_ptr<int>(), (int)cu_seqlens.numel() - 1, T,
+                          (int)max_seqlen, Hq, Hkv, D, (float)scale, cur_stream()), "attention_bwd");
+  return {dq, dk, dv};
+}
+
+// ---- peer-memory communication (comm.cu).  `layout` = [ws, E, capacity_rows, capacity_slots, off_counts,
+// off_count_flags, off_arrive_x, off_arrive_y, off_recv_x, off_recv_y]; peer_base = int64 device tensor of
+// the peers' workspace base addresses.
+static MdtEpLayout to_layout(const std::vector<int64_t>& v) {
+  TORCH_CHECK(v.size() == 10, "layout needs 10 entries");
+  MdtEpLayout L;
+  L.ws = (int)v[0]; L.num_experts = (int)v[1]; L.capacity_rows = (int)v[2]; L.capacity_slots = (int)v[3];
+  L.off_counts = v[4]; L.off_count_flags = v[5]; L.off_arrive_x = v[6]; L.off_arrive_y = v[7]; L.off_recv_x = v[8]; L.off_recv_y = v[9];
+  return L;
+}
+static const long long* ptrs(const Tensor& t) {
+  TORCH_CHECK(t.scalar_type() == at::kLong && t.is_cuda() && t.is_contiguous(), "pointer table must be a CUDA int64 tensor");
+  return (const long long*)t.data_ptr<int64_t>();
+}
+void ep_counts_send(const Tensor& counts, const Tensor& peer_base, std::vector<int64_t> layout, int64_t rank, int64_t parity, int64_t epoch) {
+  c10::cuda::CUDAGuard guard(counts.device());
+  check(mdt_ep_counts_send(counts.data_ptr<int>(), ptrs(peer_base), to_layout(layout), (int)rank, (int)parity, (unsigned)epoch, cur_stream()), "ep_counts_send");
+}
+void ep_counts_wait_meta(int64_t my_base, std::vector<int64_t> layout, int64_t rank, int64_t parity, int64_t epoch, Tensor& meta, Tensor& status) {
+  c10::cuda::CUDAGuard guard(meta.device());
+  MdtEpLayout L = to_layout(layout);
+  TORCH_CHECK(meta.scalar_type() == at::kInt && meta.numel() >= mdt_ep_meta_size(L.ws, L.num_experts));
+  check(mdt_ep_counts_wait_meta(my_base, L, (int)rank, (int)parity, (unsigned)epoch, meta.data_ptr<int>(), status.data_ptr<int>(), cur_stream()), "ep_counts_wait_meta");
+}
+void ep_dispatch(const Tensor& x, const Tensor& src_slot, const Tensor& expert_of_slot, const OptTensor& slot_scale, const Tensor& meta,
+                 const Tensor& peer_base, std::vector<int64_t> layout, int64_t top_k, int64_t parity) {
+  CHECK_BF16(x);
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && expert_of_slot.scalar_type() == at::kInt && expert_of_slot.is_contiguous());
+  check(mdt_ep_dispatch(x.data_ptr(), src_slot.data_ptr<int>(), expert_of_slot.data_ptr<int>(), cptr(slot_scale), meta.data_ptr<int>(), ptrs(peer_base),
+                        to_layout(layout), (int)expert_of_slot.numel(), (int)top_k, (int)x.size(1), (int)parity, cur_stream()), "ep_dispatch");
+}
+void ep_recv_prepare(int64_t my_base, std::vector<int64_t> layout, const Tensor& meta, int64_t cols, int64_t parity, Tensor& status) {
+  c10::cuda::CUDAGuard guard(meta.device());
+  check(mdt_ep_recv_prepare(my_base, to_layout(layout), meta.data_ptr<int>(), (int)cols, (int)parity, status.data_ptr<int>(), cur_stream()), "ep_recv_prepare");
+}
+void ep_combine_send(const Tensor& y, const Tensor& meta, const Tensor& peer_base, std::vector<int64_t> layout, int64_t rank, int64_t max_rows, int64_t parity) {
+  CHECK_BF16(y);
+  c10::cuda::CUDAGuard guard(y.device());
+  TORCH_CHECK(y.is_contiguous());
+  check(mdt_ep_combine_send(y.data_ptr(), meta.data_ptr<int>(), ptrs(peer_base), to_layout(layout), (int)rank, (int)max_rows, (int)y.size(1), (int)parity, cur_stream()), "ep_combine_send");
+}
+void ep_wait_rows(int64_t my_base, std::vector<int64_t> layout, const Tensor& meta, int64_t parity, Tensor& status) {
+  c10::cuda::CUDAGuard guard(meta.device());
+  check(mdt_ep_wait_rows(my_base, to_layout(layout), meta.data_ptr<int>(), (int)parity, status.data_ptr<int>(), cur_stream()), "ep_wait_rows");
+}
+std::vector<int64_t> ep_meta_offsets(int64_t ws, int64_t E) {
+  return {mdt_ep_meta_counts(ws, E), mdt_ep_meta_recv_tot(ws, E), mdt_ep_meta_recv_off(ws, E), mdt_ep_meta_dst_row(ws, E),
+          mdt_ep_meta_send_start(ws, E), mdt_ep_meta_seg_row(ws, E), mdt_ep_meta_seg_pos(ws, E), mdt_ep_meta_scalars(ws, E), mdt_ep_meta_size(ws, E)};
+}
+void ag_pull(Tensor& out, const Tensor& peer_shard, int64_t ws, int64_t bytes_per_rank) {
+  c10::cuda::CUDAGuard guard(out.device());
+  check(mdt_ag_pull(out.data_ptr(), ptrs(peer_shard), (int)ws, bytes_per_rank, cur_stream()), "ag_pull");
+}
+void rs_pull(Tensor& out, const Tensor& peer_full, int64_t ws, int64_t rank, bool in_fp32, double scale, bool accumulate) {
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(out.is_contiguous());
+  check(mdt_rs_pull(out.data_ptr(), ptrs(peer_full), (int)ws, (int)rank, out.numel(), in_fp32, out.scalar_type() == at::kFloat, (float)scale, accumulate, cur_stream()), "rs_pull");
+}
+void barrier_arrive(const Tensor& peer_flags, int64_t ws, int64_t rank, int64_t epoch) {
+  c10::cuda::CUDAGuard guard(peer_flags.device());
+  check(mdt_barrier_arrive(ptrs(peer_flags), (int)ws, (int)rank, (unsigned)epoch, cur_stream()), "barrier_arrive");
+}
+void barrier_wait(int64_t my_flags, int64_t ws, int64_t epoch, Tensor& status, int64_t limit_ms) {
+  c10::cuda::CUDAGuard guard(status.device());
+  check(mdt_barrier_wait((const void*)my_flags, (int)ws, (unsigned)epoch, status.data_ptr<int>(), limit_ms, cur_stream()), "barrier_wait");
+}
+
 int64_t launch_count() {
-  return mdt_gemm_launch_count() + mdt_elementwise_launch_count() + mdt_router_launch_count();
+  return mdt_gemm_launch_count() + mdt_elementwise_launch_count() + mdt_router_launch_count() + mdt_attention_launch_count() + mdt_comm_launch_count();
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -247,5 +341,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gather_rows", &gather_rows);
   m.def("combine_rows", &combine_rows);
   m.def("combine_wgrad", &combine_wgrad);
+  m.def("attention_fwd", &attention_fwd);
+  m.def("attention_bwd", &attention_bwd);
+  m.def("ep_counts_send", &ep_counts_send);
+  m.def("ep_counts_wait_meta", &ep_counts_wait_meta);
+  m.def("ep_dispatch", &ep_dispatch);
+  m.def("ep_recv_prepare", &ep_recv_prepare);
+  m.def("ep_combine_send", &ep_combine_send);
+  m.def("ep_wait_rows", &ep_wait_rows);
+  m.def("ep_meta_offsets", &ep_meta_offsets);
+  m.def("ag_pull", &ag_pull);
+  m.def("rs_pull", &rs_pull);
+  m.def("barrier_arrive", &barrier_arrive);
+  m.def("barrier_wait", &barrier_wait);
   m.def("launch_count", &launch_count);
 }

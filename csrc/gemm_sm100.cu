@@ -267,6 +267,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       const int buf = acc_it & 1;
       const uint32_t aph = (acc_it >> 1) & 1;
       if (!wait_parity(&tfull_bar[buf], aph, abort_flag)) { fail(ST_TIMEOUT_TMEM_FULL); break; }
+      __syncwarp();   // lanes may leave the wait loop at different times; the TMEM loads below are warp-aligned
       tc_fence_after();
       const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
       if (p.dual) {

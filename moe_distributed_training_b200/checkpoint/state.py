@@ -160,7 +160,8 @@ def save_training_state(engine, out_dir: str, step: int):
     rank, _ = _world()
     os.makedirs(out_dir, exist_ok=True)
     params = [p for g in engine.optimizer.param_groups for p in g["params"]]
-    state = {"step": step, "scheduler": engine.scheduler.state_dict(), "moments": []}
+    state = {"step": step, "scheduler": engine.scheduler.state_dict(), "moments": [],
+             "lrs": [g["lr"] for g in engine.optimizer.param_groups]}
     for p in params:
         st = engine.optimizer.state.get(p, {})
         state["moments"].append({k: (v.cpu() if torch.is_tensor(v) else v) for k, v in st.items()})
@@ -179,6 +180,8 @@ def load_training_state(engine, in_dir: str) -> int:
             if st:
                 engine.optimizer.state[p] = {k: (v.to(p.device) if torch.is_tensor(v) else v) for k, v in st.items()}
     engine.scheduler.load_state_dict(state["scheduler"])
+    for g, lr in zip(engine.optimizer.param_groups, state.get("lrs", [])):
+        g["lr"] = lr
     engine.step_count = state["step"]
     return int(state["step"])
 

@@ -111,7 +111,8 @@ class ParallelDroplessMLP(nn.Module):
     def _dispatch_impl(self, x: torch.Tensor) -> str:
         impl = self.args.dispatch_impl
         if impl == "auto":
-            impl = "fused" if x.is_cuda else "nccl"
+            from ..parallel import fused_ep
+            impl = "fused" if (x.is_cuda and fused_ep.available()) else "nccl"
         return impl
 
     # -- single-rank path --------------------------------------------------

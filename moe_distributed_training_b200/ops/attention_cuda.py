@@ -1,12 +1,19 @@
-"""Causal grouped-query attention over packed sequences on CUDA."""
+"""Causal grouped-query attention over packed sequences on CUDA.
+
+head_dim 128 (Mixtral) runs on the tcgen05 kernels of `csrc/attention.cu`.  Other head sizes are
+only used by toy configurations; they go through torch's SDPA, stated here explicitly rather than
+hidden as a fallback.
+"""
 from __future__ import annotations
+
+import os
 
 import torch
 import torch.nn.functional as F
 
 
 def sdpa_attention(q, k, v, cu_seqlens, max_seqlen=None):
-    """q [T, Hq, d], k/v [T, Hkv, d]; one causal attention problem per sequence in cu_seqlens."""
+    """Library path (cuDNN / flash SDPA): the baseline, and the route for head_dim != 128."""
     T = q.shape[0]
     nseq = cu_seqlens.numel() - 1
     if nseq == 1:
@@ -23,5 +30,25 @@ def sdpa_attention(q, k, v, cu_seqlens, max_seqlen=None):
     return outs[0].contiguous() if len(outs) == 1 else torch.cat(outs, 0)
 
 
+class _Attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, scale):
+        from .cuda_ops import ext
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o, lse = ext.attention_fwd(q, k, v, cu_seqlens, max_seqlen, scale)
+        ctx.save_for_backward(q, k, v, o, lse, cu_seqlens)
+        ctx.max_seqlen, ctx.scale = max_seqlen, scale
+        return o
+
+    @staticmethod
+    def backward(ctx, dout):
+        from .cuda_ops import ext
+        q, k, v, o, lse, cu = ctx.saved_tensors
+        dq, dk, dv = ext.attention_bwd(q, k, v, o, dout.contiguous(), lse, cu, ctx.max_seqlen, ctx.scale)
+        return dq, dk, dv, None, None, None
+
+
 def attention(q, k, v, cu_seqlens, max_seqlen=None):
-    return sdpa_attention(q, k, v, cu_seqlens, max_seqlen)
+    if q.shape[-1] != 128 or os.environ.get("MDT_ATTENTION_IMPL") == "sdpa":  # env switch: A/B timing against the library
+        return sdpa_attention(q, k, v, cu_seqlens, max_seqlen)
+    return _Attention.apply(q, k, v, cu_seqlens.int(), int(max_seqlen or q.shape[0]), float(q.shape[-1]) ** -0.5)

@@ -16,18 +16,13 @@ CSRC = os.path.join(_ROOT, "csrc")
 EXT_DIR = os.path.join(_PKG, "_ext")
 EXT_NAME = "mdt_ext"
 
-SOURCES = ["bindings.cpp", "gemm_sm100.cu", "elementwise.cu", "router.cu"]
+SOURCES = ["bindings.cpp", "gemm_sm100.cu", "elementwise.cu", "router.cu", "attention.cu", "comm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 
 
 def sources():
-    out = [os.path.join(CSRC, s) for s in SOURCES]
-    for extra in ("attention.cu", "comm.cu", "noalloc.cu"):
-        p = os.path.join(CSRC, extra)
-        if os.path.exists(p):
-            out.append(p)
-    return out
+    return [os.path.join(CSRC, s) for s in SOURCES]
 
 
 def build(verbose: bool = False):
@@ -35,9 +30,6 @@ def build(verbose: bool = False):
     os.makedirs(EXT_DIR, exist_ok=True)
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
     defines = []
-    for extra in ("attention", "comm", "noalloc"):
-        if os.path.exists(os.path.join(CSRC, extra + ".cu")):
-            defines.append(f"-DMDT_HAVE_{extra.upper()}=1")
     return cpp_extension.load(
         name=EXT_NAME, sources=sources(), extra_include_paths=[CSRC],
         extra_cflags=["-O2", "-std=c++17"] + defines, extra_cuda_cflags=NVCC_FLAGS + defines,

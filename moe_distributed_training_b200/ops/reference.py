@@ -60,10 +60,11 @@ class RoutingPlan:
     src_slot: torch.Tensor           # [capacity] int32, slot held by a row or -1
     top_k: int
     num_experts: int
+    capacity_rows: Optional[int] = None   # set when the plan describes a buffer it has no slot map for
 
     @property
     def capacity(self) -> int:
-        return self.src_slot.numel()
+        return self.capacity_rows if self.capacity_rows is not None else self.src_slot.numel()
 
 
 def plan_capacity(num_slots: int, num_experts: int, block: int = BLOCK_ROWS) -> int:

@@ -1,0 +1,106 @@
+"""Peer-memory communication kernels, with several ranks emulated inside one GPU.
+
+The kernels of all pretend ranks run one after another on one device: first every rank's send kernel,
+then every rank's wait kernel, so no kernel ever waits for work that has not been launched yet.  The
+"peers" are separate buffers on the same GPU, addressed through the same pointer tables a real
+multi-GPU run uses.
+"""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def cops():
+    from moe_distributed_training_b200.ops import cuda_ops
+    return cuda_ops
+
+
+@pytest.mark.parametrize("ws,E,k,tokens", [(2, 4, 2, [300, 77]), (4, 8, 2, [513, 128, 1000, 5]), (1, 4, 2, [200])])
+def test_dispatch_and_combine_emulated_ranks(cops, ws, E, k, tokens):
+    from moe_distributed_training_b200.parallel import symm
+    ext = cops.ext
+    H, El = 256, E // ws
+    torch.manual_seed(0)
+    spaces = symm.emulate_ep_workspaces(ws, E, H, max(tokens), k, DEV)
+    status = cops.status_tensor(DEV)
+    xs = [torch.randn(t, H, device=DEV).to(torch.bfloat16) for t in tokens]
+    tops = [torch.randn(t, E, device=DEV).topk(k, -1).indices.int() for t in tokens]
+    plans = [cops.make_plan(tp, E, 1, tp.numel()) for tp in tops]
+    off = [int(v) for v in ext.ep_meta_offsets(ws, E)]
+    metas = [torch.zeros(off[8], dtype=torch.int32, device=DEV) for _ in range(ws)]
+    for epoch in (1, 2):      # two exchanges in a row: parities alternate, counters are re-used
+        par = epoch & 1
+        for r, w in enumerate(spaces):
+            ext.ep_counts_send(plans[r].tokens_per_expert, w.peer_base, w.layout, r, par, epoch)
+        for r, w in enumerate(spaces):
+            ext.ep_counts_wait_meta(w.my_base, w.layout, r, par, epoch, metas[r], status)
+        for r, w in enumerate(spaces):
+            ext.ep_dispatch(xs[r], plans[r].src_slot, tops[r].reshape(-1).contiguous(), None, metas[r], w.peer_base, w.layout, k, par)
+        for r, w in enumerate(spaces):
+            ext.ep_recv_prepare(w.my_base, w.layout, metas[r], H, par, status)
+        cops.check_status(DEV)
+        # oracle of every receive buffer
+        for d, w in enumerate(spaces):
+            rows = []
+            for le in range(El):
+                e = d * El + le
+                seg = []
+                for s in range(ws):
+                    flat = tops[s].reshape(-1)
+                    slots = (flat == e).nonzero().flatten()          # stable slot order
+                    seg.append(xs[s][slots // k])
+                seg = torch.cat(seg)
+                pad = (-seg.shape[0]) % 128
+                rows.append(torch.cat([seg, torch.zeros(pad, H, device=DEV, dtype=torch.bfloat16)]))
+            want = torch.cat(rows)
+            m = metas[d].cpu()
+            assert int(m[off[7] + 2]) == want.shape[0]
+            assert torch.equal(w.recv_x()[:want.shape[0]], want), f"rank {d} receive buffer"
+        # combine: send 2x the received rows back
+        ys = [w.recv_x() * 2 for w in spaces]
+        for r, w in enumerate(spaces):
+            ext.ep_combine_send(ys[r], metas[r], w.peer_base, w.layout, r, w.capacity_rows, par)
+        for r, w in enumerate(spaces):
+            ext.ep_wait_rows(w.my_base, w.layout, metas[r], par, status)
+        cops.check_status(DEV)
+        for r, w in enumerate(spaces):
+            n = tops[r].numel()
+            want = 2 * xs[r][(plans[r].src_slot[:n] // k).long()]
+            assert torch.equal(w.recv_y()[:n], want), f"rank {r} returned rows"
+
+
+def test_flat_all_gather_and_reduce_scatter_emulated(cops):
+    ext = cops.ext
+    ws, n = 4, 4096 + 512
+    torch.manual_seed(1)
+    shards = [torch.randn(n, device=DEV).to(torch.bfloat16) for _ in range(ws)]
+    table = torch.tensor([s.data_ptr() for s in shards], dtype=torch.int64, device=DEV)
+    out = torch.empty(ws * n, dtype=torch.bfloat16, device=DEV)
+    ext.ag_pull(out, table, ws, n * 2)
+    assert torch.equal(out, torch.cat(shards))
+    fulls = [torch.randn(ws * n, device=DEV) for _ in range(ws)]
+    ftable = torch.tensor([f.data_ptr() for f in fulls], dtype=torch.int64, device=DEV)
+    for rank in range(ws):
+        acc = torch.ones(n, dtype=torch.bfloat16, device=DEV)
+        ext.rs_pull(acc, ftable, ws, rank, True, 0.25, True)
+        want = 1.0 + 0.25 * sum(f[rank * n:(rank + 1) * n] for f in fulls)
+        assert torch.allclose(acc.float(), want, atol=2e-2, rtol=2e-2)
+
+
+def test_peer_wait_gives_up_with_a_status_code(cops):
+    """A flag that nothing sets: the wait runs out after its (here 200 ms) limit, the kernel returns and
+    reports code 5 in the status word; the context stays usable."""
+    ext = cops.ext
+    flags = torch.zeros(8, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ext.barrier_wait(flags.data_ptr(), 2, 1, status, 200)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 5
+    flags.fill_(1)
+    status.zero_()
+    ext.barrier_wait(flags.data_ptr(), 2, 1, status, 200)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0

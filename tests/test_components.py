@@ -1,0 +1,142 @@
+"""CPU unit tests of the small components: routing plan, router, collator, CLI, schedules, flags."""
+import pytest
+import torch
+
+from moe_distributed_training_b200.ops import reference
+
+
+def test_plan_is_a_stable_padded_counting_sort():
+    top = torch.tensor([[1, 0], [1, 2], [0, 1], [2, 1]], dtype=torch.int32)
+    plan = reference.make_plan(top, 4, block=4)
+    assert plan.tokens_per_expert.tolist() == [2, 4, 2, 0]
+    assert plan.padded_offsets.tolist() == [0, 4, 8, 12, 12]
+    # expert 1 receives slots 0, 2, 5, 7 in that (stable) order
+    assert plan.dest_row[[0, 2, 5, 7]].tolist() == [4, 5, 6, 7]
+    assert plan.src_slot[:12].tolist() == [1, 4, -1, -1, 0, 2, 5, 7, 3, 6, -1, -1]
+    x = torch.arange(4, dtype=torch.float32)[:, None].repeat(1, 3)
+    xg = reference.gather_rows(x, plan.src_slot, 2)
+    assert xg[:12, 0].tolist() == [0, 2, 0, 0, 0, 1, 2, 3, 1, 3, 0, 0]
+    w = torch.full((4, 2), 0.5)
+    assert torch.allclose(reference.combine_rows(xg, plan.dest_row, w, 2), x)
+
+
+def test_router_matches_definition():
+    torch.manual_seed(0)
+    x, w = torch.randn(50, 32), torch.randn(8, 32)
+    s, wt, idx = reference.router(x, w, 2, True)
+    ref = (x @ w.t()).softmax(-1)
+    tw, ti = ref.topk(2, -1)
+    assert torch.equal(idx.long(), ti)
+    assert torch.allclose(wt, tw / tw.sum(-1, keepdim=True))
+    assert torch.allclose(wt.sum(-1), torch.ones(50))
+
+
+def test_collator_masks_prompt_and_pads():
+    from moe_distributed_training_b200.data.collator import DataCollatorForCompletionOnlyLM
+    c = DataCollatorForCompletionOnlyLM([7, 8], pad_token_id=0)
+    b = c([{"input_ids": [1, 2, 7, 8, 5, 6]}, {"input_ids": [3, 7, 8, 4]}, {"input_ids": [1, 2, 3]}])
+    assert b["input_ids"].shape == (3, 6)
+    assert b["labels"][0].tolist() == [-100, -100, -100, -100, 5, 6]
+    assert b["labels"][1].tolist() == [-100, -100, -100, 4, -100, -100]
+    assert b["labels"][2].tolist() == [-100] * 6
+    assert b["attention_mask"][1].tolist() == [1, 1, 1, 1, 0, 0]
+
+
+def test_synthetic_data_shape():
+    from moe_distributed_training_b200.data.synthetic import SyntheticInstructionDataset
+    ds = SyntheticInstructionDataset(1000, 20, 128, 1024, seed=1)
+    for ex in ds.examples:
+        n = ex["input_ids"].numel()
+        assert 128 <= n <= 1024
+        k = int(0.4 * n)
+        assert (ex["labels"][:k] == -100).all() and (ex["labels"][k:] == ex["input_ids"][k:]).all()
+
+
+def test_cli_parses_fire_style_flags():
+    from moe_distributed_training_b200.cli import parse_kwargs
+
+    def main(a: int = 1, flag: bool = False, name: str = "x", lr: float = 1e-5, deg: int = None):
+        pass
+    kw = parse_kwargs(main, ["--a", "3", "--flag", "True", "--name=abc", "--lr", "5e-5", "--deg", "4"])
+    assert kw == {"a": 3, "flag": True, "name": "abc", "lr": 5e-5, "deg": 4}
+    assert parse_kwargs(main, ["--flag"]) == {"flag": True}
+    with pytest.raises(SystemExit):
+        parse_kwargs(main, ["--nope", "1"])
+
+
+def test_linear_schedule_decays_to_zero():
+    from moe_distributed_training_b200.optim.schedulers import get_scheduler
+    p = torch.nn.Parameter(torch.zeros(1))
+    opt = torch.optim.SGD([p], lr=1.0)
+    s = get_scheduler("linear", opt, 2, 10)
+    lrs = []
+    for _ in range(10):
+        lrs.append(opt.param_groups[0]["lr"]); opt.step(); s.step()
+    assert lrs[0] == 0.0 and lrs[2] == 1.0 and abs(lrs[6] - 0.5) < 1e-9 and opt.param_groups[0]["lr"] == 0.0
+
+
+def test_flag_validation_follows_the_reference_rules():
+    from moe_distributed_training_b200.train.run import validate_flags
+    with pytest.raises(ValueError):
+        validate_flags(False, True, False, "none", 8, None)      # scattermoe needs a sharding mode
+    with pytest.raises(ValueError):
+        validate_flags(True, False, True, "none", 8, None)       # exactly one of megablocks / tp
+    assert validate_flags(True, False, False, "all", 8, None) == 8   # expert_degree defaults to world size
+    assert validate_flags(True, True, False, "attn-only", 8, 4) == 4
+    assert validate_flags(False, False, False, "none", 8, None) == 1
+
+
+def test_get_moe_kwargs_and_constants():
+    from megablocks_utils.shard_moe_utils import (DIM_EXPERT, KEY_DATA_PARALLEL, KEY_EXPERT_PARALLEL, KEY_EXPERTS,
+                                                  KEY_ROUTER, get_moe_kwargs)
+    from moe_distributed_training_b200 import MixtralConfig
+    kw = get_moe_kwargs(MixtralConfig.mixtral_8x7b(), bf16=True, mlp_impl="scattermoe")
+    assert kw["ffn_hidden_size"] == 14336 and kw["moe_num_experts"] == 8 and kw["moe_top_k"] == 2
+    assert kw["moe_expert_model_parallelism"] and kw["moe_normalize_expert_weights"] is True
+    assert (KEY_DATA_PARALLEL, KEY_EXPERT_PARALLEL, DIM_EXPERT) == ("data_parallel", "expert_parallel", 0)
+    assert (KEY_ROUTER, KEY_EXPERTS) == ("router.layer.weight", "experts.mlp")
+
+
+def test_moe_block_contract_and_param_names():
+    from moe_distributed_training_b200 import MixtralConfig
+    from moe_distributed_training_b200.models.mixtral import MixtralForCausalLM
+    cfg = MixtralConfig.tiny()
+    m = MixtralForCausalLM(cfg)
+    names = dict(m.named_parameters())
+    assert names["model.layers.0.block_sparse_moe.router.layer.weight"].shape == (4, 256)
+    assert names["model.layers.1.block_sparse_moe.experts.mlp.w2"].shape == (4 * 512, 256)
+    out, aux = m.model.layers[0].block_sparse_moe(torch.randn(2, 5, 256))
+    assert out.shape == (2, 5, 256) and aux is None
+
+
+def test_parallel_linear_lora_matches_expert_model():
+    """The scenario of the reference's unit test: 10 tokens, 2 experts, fixed routing, LoRA r=16/alpha=32."""
+    from scattermoe_utils.parallel_linear_lora import parallel_linear_lora
+    torch.manual_seed(42)
+    E, K, N, r, alpha = 2, 128, 16, 16, 32
+    X = torch.randn(10, K, requires_grad=True)
+    W = torch.randn(E, K, N) * 0.1
+    A = (torch.randn(E, K, r) * 0.1).requires_grad_(True)
+    B = (torch.randn(E, r, N) * 0.1).requires_grad_(True)
+    sorted_expert_idxs = torch.tensor([0, 0, 0, 0, 1, 1, 1, 1, 1, 1])
+    sorted_scattered_idxs = torch.tensor([4, 6, 8, 9, 0, 1, 2, 3, 5, 7])
+    out = parallel_linear_lora(X, W, A, B, r, alpha, 1, sorted_expert_idxs, sorted_scattered_idxs)
+    Xr, Ar, Br = (t.detach().clone().requires_grad_(True) for t in (X, A, B))
+    ref = torch.zeros(10, N)
+    for e in range(E):
+        rows = sorted_scattered_idxs[sorted_expert_idxs == e]
+        ref[rows] = Xr[rows] @ W[e] + (alpha / r) * (Xr[rows] @ Ar[e]) @ Br[e]
+    assert torch.allclose(out, ref, atol=1e-5)
+    go = torch.randn(10, N)
+    out.backward(go); ref.backward(go)
+    for a, b in ((X, Xr), (A, Ar), (B, Br)):
+        assert torch.allclose(a.grad, b.grad, atol=1e-5)
+    # top-2 fan-out with gates, and the primitives under the reference's names
+    from scattermoe_utils.kernels.ops import group_bwd_AB, padded_block_indices, scatter2scatter_lora
+    pbi, eo = padded_block_indices(torch.tensor([0] * 300 + [1] * 200), 2)
+    assert pbi.tolist() == [0, 128, 256, 300, 428] and eo.tolist() == [300, 500]
+    y = scatter2scatter_lora(X.detach(), W, A.detach(), B.detach(), alpha / r, sorted_expert_idxs, sorted_scattered_idxs, 1)
+    assert torch.allclose(y, ref.detach(), atol=1e-5)
+    xs = X.detach()[sorted_scattered_idxs]
+    dA, dB = group_bwd_AB(go[sorted_scattered_idxs], xs, A.detach(), B.detach(), alpha / r, torch.tensor([4, 10]), 2)
+    assert torch.allclose(dA, Ar.grad, atol=1e-5) and torch.allclose(dB, Br.grad, atol=1e-5)

@@ -285,3 +285,22 @@ def test_end_to_end_matches_reference_path(ops):
     for a, b in zip(l_gpu, l_ref):
         assert abs(a - b) < 0.05 * abs(b), (l_gpu, l_ref)
     assert l_gpu[-1] < l_gpu[0]
+
+
+@pytest.mark.parametrize("lens", [[128], [200], [577], [1024], [100, 300, 77], [256, 256]])
+def test_attention(ops, lens):
+    from moe_distributed_training_b200.ops import reference
+    torch.manual_seed(12)
+    T, Hq, Hkv, d = sum(lens), 8, 2, 128
+    q, k, v = (_rand(T, h, d).requires_grad_(True) for h in (Hq, Hkv, Hkv))
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    o = ops.attention(q, k, v, cu, max(lens))
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    orf = reference.attention(qr, kr, vr, cu)
+    _close(o, orf, 2e-2, f"attention fwd {lens}")
+    go = _rand(T, Hq, d)
+    o.backward(go); orf.backward(go.float())
+    _close(q.grad, qr.grad, 3e-2, "attention dq")
+    _close(k.grad, kr.grad, 3e-2, "attention dk")
+    _close(v.grad, vr.grad, 3e-2, "attention dv")
+    ops.check_status(DEV)
