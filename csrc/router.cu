@@ -409,3 +409,56 @@ extern "C" int mdt_combine_wgrad(const void* y, const int* dest_row, const void*
   MDT_RT_CHECK();
   return 0;
 }
+
+// ---------------------------------------------------------------------------------- allocation-free plan builder
+#include "noalloc.h"
+
+namespace mdt {
+constexpr int NOALLOC_MAX_BLOCKS = MDT_NOALLOC_MAX_SLOTS / PLAN_CHUNK;
+constexpr int NOALLOC_MAX_DEVICES = 64;
+// Scratch of mdt_make_plan_noalloc: per-(block, expert) counts, later first rows.  One copy per GPU.
+static __device__ __align__(256) int g_plan_scratch[(NOALLOC_MAX_BLOCKS + 1) * MDT_NOALLOC_MAX_EXPERTS];
+// Device address of g_plan_scratch on each device (the symbol itself is only a host-side handle).
+static int* g_plan_scratch_addr[NOALLOC_MAX_DEVICES] = {nullptr};
+}  // namespace mdt
+
+extern "C" const char* mdt_make_plan_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case MDT_NOALLOC_TOO_LARGE: return "problem larger than the built-in scratch (MDT_NOALLOC_MAX_SLOTS slots, MDT_NOALLOC_MAX_EXPERTS experts)";
+    case MDT_NOALLOC_BAD_DEVICE: return "current device ordinal is beyond this library's per-device table";
+    case MDT_NOALLOC_NO_SYMBOL: return "cudaGetSymbolAddress failed for the scratch array on the current device";
+    case MDT_NOALLOC_BAD_ARGUMENT: return "invalid argument (block < 1, negative size or null pointer)";
+    default: return code <= -100 ? "CUDA launch error (code = -100 - cudaError_t)" : "unknown code";
+  }
+}
+
+extern "C" int mdt_make_plan_noalloc(const int* expert_ids, int num_slots, int num_experts, int block, int capacity,
+                                     int* counts, int* padded_offsets, int* dest_row, int* src_slot, cudaStream_t s) {
+  if (block < 1 || num_slots < 0 || num_experts < 1 || capacity < 0 || counts == nullptr || padded_offsets == nullptr ||
+      (num_slots > 0 && (expert_ids == nullptr || dest_row == nullptr)) || (capacity > 0 && src_slot == nullptr))
+    return MDT_NOALLOC_BAD_ARGUMENT;
+  if (num_slots > MDT_NOALLOC_MAX_SLOTS || num_experts > MDT_NOALLOC_MAX_EXPERTS) return MDT_NOALLOC_TOO_LARGE;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return MDT_NOALLOC_BAD_DEVICE;
+  if (g_plan_scratch_addr[dev] == nullptr) {   // set-up, once per device, with that device current
+    int* addr = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_plan_scratch) != cudaSuccess || addr == nullptr)
+      return MDT_NOALLOC_NO_SYMBOL;
+    g_plan_scratch_addr[dev] = addr;
+  }
+  int* scratch = g_plan_scratch_addr[dev];
+  const int nb = (num_slots + PLAN_CHUNK - 1) / PLAN_CHUNK;
+  if (capacity > 0) cudaMemsetAsync(src_slot, 0xFF, (size_t)capacity * sizeof(int), s);
+  if (nb > 0) {
+    plan_hist_kernel<<<nb, PLAN_CHUNK, 0, s>>>(expert_ids, num_slots, num_experts, scratch);
+    MDT_RT_CHECK();
+  }
+  plan_scan_kernel<<<1, 256, 0, s>>>(scratch, nb, num_experts, block, counts, padded_offsets);
+  MDT_RT_CHECK();
+  if (nb > 0) {
+    plan_scatter_kernel<<<nb, PLAN_CHUNK, 0, s>>>(expert_ids, num_slots, num_experts, scratch, capacity, dest_row, src_slot);
+    MDT_RT_CHECK();
+  }
+  return 0;
+}
