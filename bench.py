@@ -131,7 +131,7 @@ def main():
     eng = build_engine(cfg, dtype=torch.bfloat16, device_type="cuda", ep_size=ep if world > 1 else 1,
                        use_lora=use_lora, lora_r=16, lora_alpha=32 if use_lora != "none" else 16, learning_rate=5e-5,
                        lr_scheduler_type="linear", num_training_steps=total_steps, max_grad_norm=1.0, seed=0,
-                       dispatch_impl=args.dispatch)
+                       dispatch_impl=args.dispatch, ep_max_tokens=args.max_len)
     dev = eng.device
     ga = args.grad_accum
 

@@ -349,19 +349,22 @@ __global__ void __launch_bounds__(128, 1) attn_bwd_kernel(const __grid_constant_
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       uint32_t raw[32];
-      tmem_ld_32x32(t_row + c * 32, raw);
+      tmem_ld_32x32(t_row + c * 32, raw);      // warp-aligned: every lane takes part, valid row or not
       tmem_ld_wait();
       if (qvalid) {
 #pragma unroll
         for (int x = 0; x < 32; ++x) atomicAdd(dqrow + c * 32 + x, __uint_as_float(raw[x]));
       }
+      __syncwarp();
     }
     tc_fence_before();
     __syncthreads();
   }
   if (!ok && tid == 0 && p.status) atomicCAS(p.status, 0, ST_TIMEOUT_TMEM_FULL);
   const int krow = k0 + r;
-  if (ok && krow < seq_end) {
+  const bool kvalid = krow < seq_end;
+  ok = __all_sync(0xffffffffu, ok);
+  if (ok) {   // warp-uniform: `ok` only changes together with the shared abort flag
     float* dv = p.dv + ((long long)krow * p.heads_q + h) * HD;
     float* dk = p.dk + ((long long)krow * p.heads_q + h) * HD;
 #pragma unroll
@@ -370,11 +373,14 @@ __global__ void __launch_bounds__(128, 1) attn_bwd_kernel(const __grid_constant_
       tmem_ld_32x32(t_row + 256 + c * 32, a);
       tmem_ld_32x32(t_row + 384 + c * 32, b);
       tmem_ld_wait();
+      if (kvalid) {
 #pragma unroll
-      for (int x = 0; x < 32; x += 4) {
-        *reinterpret_cast<float4*>(dv + c * 32 + x) = make_float4(__uint_as_float(a[x]), __uint_as_float(a[x + 1]), __uint_as_float(a[x + 2]), __uint_as_float(a[x + 3]));
-        *reinterpret_cast<float4*>(dk + c * 32 + x) = make_float4(__uint_as_float(b[x]), __uint_as_float(b[x + 1]), __uint_as_float(b[x + 2]), __uint_as_float(b[x + 3]));
+        for (int x = 0; x < 32; x += 4) {
+          *reinterpret_cast<float4*>(dv + c * 32 + x) = make_float4(__uint_as_float(a[x]), __uint_as_float(a[x + 1]), __uint_as_float(a[x + 2]), __uint_as_float(a[x + 3]));
+          *reinterpret_cast<float4*>(dk + c * 32 + x) = make_float4(__uint_as_float(b[x]), __uint_as_float(b[x + 1]), __uint_as_float(b[x + 2]), __uint_as_float(b[x + 3]));
+        }
       }
+      __syncwarp();
     }
   }
   tc_fence_before();

@@ -294,6 +294,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
               }
             }
           }
+          __syncwarp();   // the next TMEM load is warp-aligned
         }
       } else {
 #pragma unroll 1
@@ -313,6 +314,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
               }
             }
           }
+          __syncwarp();   // the next TMEM load is warp-aligned
         }
       }
       tc_fence_before();

@@ -121,6 +121,9 @@ class MoEArguments:
     # which token-exchange implementation the EP layer uses: "nccl" = torch all_to_all_single
     # (works on gloo too), "fused" = in-kernel peer stores over NVLink.
     dispatch_impl: str = "auto"
+    # most tokens one rank feeds into an MoE layer per call; sizes the symmetric receive buffers of the
+    # fused exchange for the dropless worst case
+    ep_max_tokens: int = 4096
 
     @property
     def dtype(self) -> torch.dtype:

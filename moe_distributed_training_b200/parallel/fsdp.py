@@ -25,6 +25,7 @@ what passing that mesh to `fully_shard` does in the reference
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional
 
 import torch
@@ -232,12 +233,64 @@ class ShardedMixtral:
         self._slot = {}
         self._root_leaves: List[torch.Tensor] = []
         self._grad_tmp = {}
+        self.peers = None
+        if self.is_cuda and self.ws > 1 and not sync_each_batch and os.environ.get("MDT_PEER_COLLECTIVES", "1") != "0":
+            self._setup_peer_arena()
         model.layer_runner = self
+
+    # ------------------------------------------------------------------ peer-memory arena
+    def _setup_peer_arena(self):
+        """Move every flat shard (and the fp32 gradient accumulators) into one symmetric buffer, so that the
+        all-gather / reduce-scatter kernels of `csrc/comm.cu` can read the peers' copies directly."""
+        from ..ops import cuda_ops
+        from . import symm
+        groups = [g for u in self.all_units() for g in u.groups]
+        off = 0
+        for g in groups:
+            g.arena_shard_off = off
+            off = symm._align(off + g.shard_numel * g.shard.element_size())
+            if g.trainable:
+                g.arena_acc_off = off
+                off = symm._align(off + g.padded * 4)
+        self.peers = symm.FlatPeers(self.shard_group, off, self.device)
+        self._ext = cuda_ops.ext
+        self._status = cuda_ops.status_tensor(self.device)
+        buf = self.peers.buffer
+        for g in groups:
+            nb = g.shard_numel * g.shard.element_size()
+            view = buf[g.arena_shard_off:g.arena_shard_off + nb].view(g.dtype)
+            view.copy_(g.shard.data)
+            g.shard.data = view
+            g.shard_table = self.peers.table(g.arena_shard_off)
+            if g.trainable:
+                g.acc = buf[g.arena_acc_off:g.arena_acc_off + g.padded * 4].view(torch.float32)
+                g.acc.zero_()
+                g._acc_dirty = False
+                g.acc_table = self.peers.table(g.arena_acc_off)
+        self._flag_off = self.peers.nbytes - self.peers.flag_bytes
+        self._flag_table = self.peers.table(self._flag_off)
+        self.peer_barrier()
+
+    def peer_barrier(self):
+        """Device-side barrier over the shard group (arrive on every peer's flag row, wait for all)."""
+        if self.peers is None:
+            return
+        p = self.peers
+        p.epoch += 1
+        self._ext.barrier_arrive(self._flag_table, p.ws, p.rank, p.epoch)
+        self._ext.barrier_wait(p.bases[p.rank] + self._flag_off, p.ws, p.epoch, self._status, 0)
+
+    def after_optimizer_step(self):
+        """Peers must not gather a shard that its owner is still updating."""
+        self.peer_barrier()
 
     # ------------------------------------------------------------------ buffers
     def _gather_into(self, unit: FsdpUnit, buffers):
         for g, buf in zip(unit.groups, buffers):
-            coll.all_gather_flat(buf[:g.padded], g.shard.data, g.group)
+            if self.peers is not None:
+                self._ext.ag_pull(buf[:g.padded], g.shard_table, g.ws, g.shard_numel * g.shard.element_size())
+            else:
+                coll.all_gather_flat(buf[:g.padded], g.shard.data, g.group)
 
     def _start_gather(self, idx: int):
         """Issue the all-gather of unit idx (on the side stream when there is one)."""
@@ -317,16 +370,34 @@ class ShardedMixtral:
     def reduce_gradients(self):
         """Finish the gradient reductions of one optimizer step (call after the last backward)."""
         scale = 1.0 / (self.ws * self.rep)
+        if self.peers is not None:
+            self.peer_barrier()          # every rank has finished adding into its accumulators
         for u in self.units + [self.root]:
             g = u.trainable_group
             if g is None:
                 continue
             if g.acc is not None and getattr(g, "_acc_dirty", False):
-                if g.shard.grad is None:
-                    g.shard.grad = torch.zeros_like(g.shard.data)
-                coll.reduce_scatter_flat(g.shard.grad, g.acc, g.group, scale=scale, accumulate=True)
+                if self.peers is not None:
+                    # read the peers' accumulators; scale, cast and write the shard gradient in one pass
+                    fresh = g.shard.grad is None
+                    if fresh:
+                        g.shard.grad = torch.empty_like(g.shard.data)
+                    self._ext.rs_pull(g.shard.grad, g.acc_table, g.ws, g.rank, True, scale, not fresh)
+                else:
+                    if g.shard.grad is None:
+                        g.shard.grad = torch.zeros_like(g.shard.data)
+                    coll.reduce_scatter_flat(g.shard.grad, g.acc, g.group, scale=scale, accumulate=True)
+        if self.peers is not None:
+            self.peer_barrier()          # every rank has finished reading before the accumulators are cleared
+        for u in self.units + [self.root]:
+            g = u.trainable_group
+            if g is not None and g.acc is not None and getattr(g, "_acc_dirty", False):
                 g.acc.zero_()
                 g._acc_dirty = False
+        for u in self.units + [self.root]:
+            g = u.trainable_group
+            if g is None:
+                continue
             if self.rep > 1 and g.shard.grad is not None:
                 coll.all_reduce_flat(g.shard.grad, self.replicate_group)
         # router: mean over all ranks; experts (and their LoRA factors): mean over expert replicas

@@ -99,8 +99,7 @@ class FusedExpertParallel:
     def for_group(cls, group, args, device, max_tokens: Optional[int] = None):
         key = (group.group_name, torch.device(device).index)
         if key not in cls._instances:
-            import os
-            max_tokens = max_tokens or int(os.environ.get("MDT_EP_MAX_TOKENS", "4096"))
+            max_tokens = max_tokens or args.ep_max_tokens
             ws = symm.create_ep_workspace(group, args.moe_num_experts, args.hidden_size, max_tokens, args.moe_top_k, device)
             cls._instances[key] = cls(ws, args.moe_top_k, device)
         return cls._instances[key]

@@ -100,6 +100,8 @@ class Engine:
         if self.max_grad_norm is not None and self.max_grad_norm > 0:
             grad_norm = clip_grad_norm_(self.model, self.max_grad_norm, self.shard_group, self.ep_group, self.optimizer)
         self.optimizer.step()
+        if hasattr(self.runner, "after_optimizer_step"):
+            self.runner.after_optimizer_step()
         self.scheduler.step()
         self.optimizer.zero_grad(set_to_none=True)
         self.step_count += 1
@@ -133,21 +135,21 @@ def build_engine(cfg: MixtralConfig, *, dtype: torch.dtype = torch.bfloat16, dev
                  max_grad_norm: Optional[float] = 1.0, weight_decay: float = 0.01,
                  checkpoint: Optional[str] = None, seed: int = 0, mlp_impl: str = "sparse",
                  dispatch_impl: str = "auto", sync_each_batch: bool = False,
-                 optimizer_state_dtype: Optional[torch.dtype] = None) -> Engine:
+                 optimizer_state_dtype: Optional[torch.dtype] = None, ep_max_tokens: int = 4096) -> Engine:
     rank, world, device = init_distributed(device_type)
     ep_size = ep_size or 1
     if ep_size > 1 and world % ep_size != 0:
         raise ValueError("world_size must be a multiple of expert_degree")
 
     moe_args = moe_args_from_config(cfg, dtype, "meta")
-    moe_args.mlp_impl, moe_args.dispatch_impl = mlp_impl, dispatch_impl
+    moe_args.mlp_impl, moe_args.dispatch_impl, moe_args.ep_max_tokens = mlp_impl, dispatch_impl, ep_max_tokens
     model = MixtralForCausalLM(cfg, moe_args, dtype=dtype, device="meta")
 
     mesh = None
     if world > 1 and ep_size > 1:
         kw = get_moe_kwargs(cfg, bf16=dtype == torch.bfloat16, fp16=dtype == torch.float16, mlp_impl=mlp_impl,
                             use_tensor_parallelism=use_tp_sharding)
-        kw["dispatch_impl"] = dispatch_impl
+        kw["dispatch_impl"], kw["ep_max_tokens"] = dispatch_impl, ep_max_tokens
         mesh = shard_moe(model, dMoE, checkpoint, rank, world, ep_size, kw, device_type=device_type,
                          parallize_tensor=use_tp_sharding, seed=seed)
     elif world > 1:

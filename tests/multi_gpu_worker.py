@@ -1,0 +1,46 @@
+"""Worker of the multi-GPU tests (one process per GPU, started by torch.distributed.run).
+
+Runs the same training steps with the library token exchange ("nccl") and with the peer-memory
+exchange ("fused") and writes the per-step losses and a parameter checksum of both to a JSON file.
+"""
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    out_path, mode = sys.argv[1], sys.argv[2]
+    from moe_distributed_training_b200 import MixtralConfig
+    from moe_distributed_training_b200.data.synthetic import SyntheticInstructionDataset, collate_packed
+    from moe_distributed_training_b200.train.engine import build_engine
+    import torch.distributed as dist
+    rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+    cfg = MixtralConfig(vocab_size=2048, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                        num_attention_heads=4, num_key_value_heads=2, head_dim=128, num_local_experts=4, num_experts_per_tok=2)
+    use_lora = "all" if mode == "lora" else "none"
+    ds = SyntheticInstructionDataset(cfg.vocab_size, 6, 100, 400, seed=3, rank=rank)
+    mbs = [collate_packed([ex]) for ex in ds.examples]
+    result = {}
+    for impl in ("nccl", "fused"):
+        eng = build_engine(cfg, dtype=torch.bfloat16, device_type="cuda", ep_size=world, use_lora=use_lora, learning_rate=1e-3,
+                           seed=0, dispatch_impl=impl, ep_max_tokens=512, lr_scheduler_type="constant")
+        losses = [float(eng.train_step(mbs[2 * s:2 * s + 2])["loss"]) for s in range(3)]
+        from moe_distributed_training_b200.ops import cuda_ops
+        cuda_ops.check_status(eng.device)
+        chk = sum(float(p.detach().float().abs().sum()) for p in eng.model.parameters() if p.requires_grad)
+        result[impl] = {"losses": losses, "checksum": chk}
+    gathered = [None] * world
+    dist.all_gather_object(gathered, result)
+    if rank == 0:
+        with open(out_path, "w") as f:
+            json.dump(gathered, f)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

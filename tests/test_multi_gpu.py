@@ -1,0 +1,37 @@
+"""Multi-GPU tests (skipped with fewer than two GPUs): the peer-memory exchange and the peer-memory
+parameter collectives reproduce the library (NCCL) path.  Ranks are child processes; NVLS is off."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(n, mode, tmp_path, port):
+    out = str(tmp_path / f"res_{mode}.json")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "multi_gpu_worker.py"), out, mode]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    return json.load(open(out))
+
+
+@pytest.mark.parametrize("mode", ["full", "lora"])
+def test_fused_exchange_matches_nccl_exchange(tmp_path, mode):
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    n = 4 if n >= 4 else 2
+    res = _run(n, mode, tmp_path, 29610 + (mode == "lora"))
+    for rank_res in res:
+        a, b = rank_res["nccl"], rank_res["fused"]
+        for la, lb in zip(a["losses"], b["losses"]):
+            assert abs(la - lb) < 2e-2 * abs(la), (a, b)
+        assert abs(a["checksum"] - b["checksum"]) < 1e-3 * abs(a["checksum"]), (a, b)
+        assert a["losses"][-1] < a["losses"][0]
