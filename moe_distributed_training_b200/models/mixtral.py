@@ -21,6 +21,7 @@ a `[B, S]` batch is the special case of B equal-length sequences.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -115,7 +116,15 @@ class MixtralDecoderLayer(nn.Module):
         self.block_sparse_moe = dMoE(moe_args)
 
     def forward(self, x: torch.Tensor, batch: PackedBatch) -> torch.Tensor:
-        x = x + self.self_attn(self.input_layernorm(x), batch)
+        fused = x.is_cuda and ops.get_backend() == "native" and x.dim() == 2 and os.environ.get("MDT_FUSED_BLOCKS", "1") != "0"
+        if fused:
+            from ..ops import fused_blocks
+        if fused and self.self_attn.head_dim == 128:
+            x = fused_blocks.attention_block(self, x, batch)      # one autograd node for the whole sub-block
+        else:
+            x = x + self.self_attn(self.input_layernorm(x), batch)
+        if fused and fused_blocks.moe_block_supported(self, x):
+            return fused_blocks.moe_block(self, x)
         moe_out, _ = self.block_sparse_moe(self.post_attention_layernorm(x))
         return x + moe_out
 

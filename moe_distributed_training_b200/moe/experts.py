@@ -61,6 +61,18 @@ class SparseMLPv2(nn.Module):
             return None
         return {name: (A, B, alpha / r) for name, (A, B, r, alpha, _, _) in self._lora_pointers.items()}
 
+    def call_args(self, xg: torch.Tensor):
+        """(w1, w2, w3 views, LoRA dict, weight-gradient scale, direct-accumulation buffers) for one call."""
+        w1, w2, w3 = self.weight_views()
+        wgrad_out = None
+        if xg.is_cuda and ops.get_backend() == "native" and torch.is_grad_enabled() and self.w1.requires_grad:
+            E, Fr, H = self.experts_per_rank, self.features_per_rank, self.args.hidden_size
+            for w in (self.w1, self.w2, self.w3):
+                if w.grad is None:
+                    w.grad = torch.zeros_like(w)
+            wgrad_out = tuple(w.grad.view(E, Fr, H) for w in (self.w1, self.w2, self.w3))
+        return w1, w2, w3, self.lora_views(), self.gradient_scale or 1.0, wgrad_out
+
     def forward(self, xg: torch.Tensor, plan) -> torch.Tensor:
         """xg: block-padded expert-grouped rows [R, hidden]; returns rows of the same layout."""
         w1, w2, w3 = self.weight_views()

@@ -77,16 +77,30 @@ class FlatParamGroup:
         self.acc: Optional[torch.Tensor] = None  # fp32 full-size local accumulation (sync_each_batch=False)
 
     def install(self, full: torch.Tensor, as_leaves: bool) -> List[torch.Tensor]:
-        """Point the modules' weights at views of `full`; optionally as autograd leaves."""
+        """Point the modules' weights at views of `full`.
+
+        Trainable groups always get autograd-leaf views (harmless in graph-free forwards, needed by the
+        recomputing backward); the views of every distinct buffer are built once and re-used, and
+        nothing is done at all when the same buffer is already installed.
+        """
         self.full = full
-        leaves = []
-        for mod, name, shape, n, o in self.specs:
-            v = full[o:o + n].view(shape)
-            if as_leaves and self.trainable:
-                v = v.detach().requires_grad_(True)
-                leaves.append(v)
-            setattr(mod, name, v)
-        return leaves
+        key = full.data_ptr()
+        cache = self.__dict__.setdefault("_view_cache", {})
+        entry = cache.get(key)
+        if entry is None:
+            views, leaves = [], []
+            for mod, name, shape, n, o in self.specs:
+                v = full[o:o + n].view(shape)
+                if self.trainable:
+                    v = v.detach().requires_grad_(True)
+                    leaves.append(v)
+                views.append(v)
+            entry = cache[key] = (views, leaves)
+        if self.__dict__.get("_installed_key") != key:
+            for (mod, name, shape, n, o), v in zip(self.specs, entry[0]):
+                setattr(mod, name, v)
+            self._installed_key = key
+        return entry[1]
 
     def flat_grad(self, grads: List[Optional[torch.Tensor]], out: torch.Tensor) -> torch.Tensor:
         """Write per-parameter grads into the flat layout (zeros where a grad is missing)."""
@@ -362,9 +376,14 @@ class ShardedMixtral:
             if g.acc is None:
                 g.acc = torch.zeros(g.padded, dtype=torch.float32, device=self.device)
                 g._acc_dirty = False
-            for (mod, name, shape, n, o), gr in zip(g.specs, grads):
-                if gr is not None:
-                    g.acc[o:o + n].add_(gr.reshape(-1))
+            views = g.__dict__.get("_acc_views")
+            if views is None or g.__dict__.get("_acc_views_ptr") != g.acc.data_ptr():
+                views = g._acc_views = [g.acc[o:o + n].view(shape) for (mod, name, shape, n, o) in g.specs]
+                g._acc_views_ptr = g.acc.data_ptr()
+            dst = [v for v, gr in zip(views, grads) if gr is not None]
+            src = [gr for gr in grads if gr is not None]
+            if dst:
+                torch._foreach_add_(dst, src)
             g._acc_dirty = True
 
     def reduce_gradients(self):

@@ -304,3 +304,90 @@ def test_attention(ops, lens):
     _close(k.grad, kr.grad, 3e-2, "attention dk")
     _close(v.grad, vr.grad, 3e-2, "attention dv")
     ops.check_status(DEV)
+
+
+@pytest.mark.parametrize("lora", [False, True])
+def test_fused_attention_block_matches_composed_ops(ops, lora):
+    """The single-node attention sub-block against the same layer evaluated op by op."""
+    from moe_distributed_training_b200 import MixtralConfig
+    from moe_distributed_training_b200.models.mixtral import MixtralDecoderLayer, PackedBatch, moe_args_from_config
+    from moe_distributed_training_b200.ops import fused_blocks
+    torch.manual_seed(13)
+    cfg = MixtralConfig(vocab_size=512, hidden_size=512, intermediate_size=512, num_hidden_layers=1, num_attention_heads=4,
+                        num_key_value_heads=2, head_dim=128, num_local_experts=2, num_experts_per_tok=1)
+    layer = MixtralDecoderLayer(cfg, moe_args_from_config(cfg, torch.bfloat16, DEV), torch.bfloat16, DEV)
+    with torch.no_grad():
+        for n, p in layer.named_parameters():
+            if "layernorm" in n:
+                p.copy_(1 + 0.1 * torch.randn_like(p))
+            else:
+                p.normal_(0, 0.05)
+    if lora:
+        for lin in (layer.self_attn.q_proj, layer.self_attn.k_proj, layer.self_attn.v_proj, layer.self_attn.o_proj):
+            lin.add_lora(16, 32)
+            with torch.no_grad():
+                lin.lora_B["default"].weight.normal_(0, 0.05)
+    lens = [150, 300]
+    T = sum(lens)
+    cu = torch.tensor([0, 150, 450], dtype=torch.int32, device=DEV)
+    pos = torch.cat([torch.arange(n, device=DEV) for n in lens]).int()
+    batch = PackedBatch(cu, pos, max(lens))
+    x1 = _rand(T, 512).requires_grad_(True)
+    x2 = x1.detach().clone().requires_grad_(True)
+    params = [p for n, p in layer.named_parameters() if "block_sparse_moe" not in n and "post_attention" not in n and p.requires_grad]
+    y1 = fused_blocks.attention_block(layer, x1, batch)
+    y2 = x2 + layer.self_attn(layer.input_layernorm(x2), batch)
+    _close(y1, y2, 1e-2, "fused attention block fwd")
+    go = _rand(T, 512)
+    g1 = torch.autograd.grad(y1, [x1] + params, go)
+    g2 = torch.autograd.grad(y2, [x2] + params, go)
+    for a, b, n in zip(g1, g2, ["x"] + [str(i) for i in range(len(params))]):
+        _close(a, b, 2e-2, f"fused attention block grad {n}")
+    ops.check_status(DEV)
+
+
+@pytest.mark.parametrize("lora", [False, True])
+def test_fused_moe_block_matches_composed_ops(ops, lora):
+    """The single-node MoE sub-block (local experts) against the same layer evaluated op by op."""
+    from moe_distributed_training_b200 import MixtralConfig
+    from moe_distributed_training_b200.models.mixtral import MixtralDecoderLayer, moe_args_from_config
+    from moe_distributed_training_b200.ops import fused_blocks
+    from moe_distributed_training_b200.peft.lora import add_expert_lora
+    torch.manual_seed(14)
+    cfg = MixtralConfig(vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=1, num_attention_heads=4,
+                        num_key_value_heads=2, head_dim=128, num_local_experts=4, num_experts_per_tok=2)
+    layer = MixtralDecoderLayer(cfg, moe_args_from_config(cfg, torch.bfloat16, DEV), torch.bfloat16, DEV)
+    with torch.no_grad():
+        for n, p in layer.named_parameters():
+            if "layernorm" in n:
+                p.copy_(1 + 0.1 * torch.randn_like(p))
+            else:
+                p.normal_(0, 0.05)
+    if lora:
+        add_expert_lora(layer.block_sparse_moe.experts, 16, 32)
+        with torch.no_grad():
+            for p in layer.block_sparse_moe.experts.lora.lora_B.values():
+                p.normal_(0, 0.05)
+    T = 700
+    x1 = _rand(T, 512).requires_grad_(True)
+    x2 = x1.detach().clone().requires_grad_(True)
+    params = [p for n, p in layer.named_parameters() if ("block_sparse_moe" in n or "post_attention" in n) and p.requires_grad]
+    assert fused_blocks.moe_block_supported(layer, x1)
+    y1 = fused_blocks.moe_block(layer, x1)
+    g1 = torch.autograd.grad(y1, [x1] + params, torch.ones_like(y1) * 0.01, allow_unused=True)
+    direct = {id(p): p.grad.clone() for p in params if p.grad is not None}     # expert weights accumulate straight into .grad
+    for p in params:
+        p.grad = None
+    moe_out, _ = layer.block_sparse_moe(layer.post_attention_layernorm(x2))
+    y2 = x2 + moe_out
+    _close(y1, y2, 1e-2, "fused moe block fwd")
+    g2 = torch.autograd.grad(y2, [x2] + params, torch.ones_like(y2) * 0.01, allow_unused=True)
+    for i, (a, b, p) in enumerate(zip(g1, g2, [None] + params)):
+        if a is None and p is not None:
+            a = direct.get(id(p))
+        if b is None and p is not None and p.grad is not None:
+            b = p.grad
+        assert (a is None) == (b is None), i
+        if a is not None:
+            _close(a, b, 3e-2, f"fused moe block grad {i}")
+    ops.check_status(DEV)

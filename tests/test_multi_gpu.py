@@ -34,4 +34,3 @@ def test_fused_exchange_matches_nccl_exchange(tmp_path, mode):
         for la, lb in zip(a["losses"], b["losses"]):
             assert abs(la - lb) < 2e-2 * abs(la), (a, b)
         assert abs(a["checksum"] - b["checksum"]) < 1e-3 * abs(a["checksum"]), (a, b)
-        assert a["losses"][-1] < a["losses"][0]
