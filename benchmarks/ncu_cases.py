@@ -1,0 +1,76 @@
+"""Small single-GPU cases for profiler captures: one kernel family per case, a handful of launches.
+
+    python benchmarks/ncu_cases.py gemm|expert_mlp|attention|dispatch
+
+Sizes keep the working set above the 126 MB L2 where DRAM figures matter, but far below a GB of launches.
+"""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    case = sys.argv[1]
+    from moe_distributed_training_b200.ops import cuda_ops as C
+    dev, bf = "cuda", torch.bfloat16
+    torch.manual_seed(0)
+    if case == "gemm":
+        x = torch.randn(8192, 4096, device=dev, dtype=bf)
+        w = torch.randn(8192, 4096, device=dev, dtype=bf)
+        out = torch.empty(8192, 8192, device=dev, dtype=bf)
+        for _ in range(4):
+            C.mm_nt(x, w, out=out)
+    elif case == "expert_mlp":
+        E, F, H, rows = 1, 14336, 4096, 1152
+        top = torch.zeros(rows, 1, dtype=torch.int32, device=dev)
+        plan = C.make_plan(top, E)
+        xg = C.ext.gather_rows(torch.randn(rows, H, device=dev, dtype=bf), plan.src_slot, plan.padded_offsets, E, None, 1)
+        w1, w2, w3 = (torch.randn(E, F, H, device=dev, dtype=bf) * 0.02 for _ in range(3))
+        with torch.no_grad():
+            for _ in range(3):
+                C.grouped_swiglu_mlp(xg, w1, w2, w3, plan)
+    elif case == "attention":
+        T, Hq, Hkv, d = 1024, 32, 8, 128
+        q = torch.randn(T, Hq, d, device=dev, dtype=bf, requires_grad=True)
+        k = torch.randn(T, Hkv, d, device=dev, dtype=bf, requires_grad=True)
+        v = torch.randn(T, Hkv, d, device=dev, dtype=bf, requires_grad=True)
+        cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        for _ in range(3):
+            o = C.attention(q, k, v, cu, T)
+            o.backward(o)
+    elif case == "dispatch":
+        from moe_distributed_training_b200.parallel import symm
+        ws, E, k, H, T = 2, 8, 2, 4096, 8192
+        spaces = symm.emulate_ep_workspaces(ws, E, H, T, k, dev)
+        status = C.status_tensor(dev)
+        xs = [torch.randn(T, H, device=dev, dtype=bf) for _ in range(ws)]
+        tops = [torch.randn(T, E, device=dev).topk(k, -1).indices.int() for _ in range(ws)]
+        plans = [C.make_plan(tp, E, 1, tp.numel()) for tp in tops]
+        off = [int(v) for v in C.ext.ep_meta_offsets(ws, E)]
+        metas = [torch.zeros(off[8], dtype=torch.int32, device=dev) for _ in range(ws)]
+        for epoch in (1, 2, 3):
+            par = epoch & 1
+            for r, w in enumerate(spaces):
+                C.ext.ep_counts_send(plans[r].tokens_per_expert, w.peer_base, w.layout, r, par, epoch)
+            for r, w in enumerate(spaces):
+                C.ext.ep_counts_wait_meta(w.my_base, w.layout, r, par, epoch, metas[r], status)
+            for r, w in enumerate(spaces):
+                C.ext.ep_dispatch(xs[r], plans[r].src_slot, tops[r].reshape(-1).contiguous(), None, metas[r], w.peer_base, w.layout, k, par)
+            for r, w in enumerate(spaces):
+                C.ext.ep_recv_prepare(w.my_base, w.layout, metas[r], H, par, status, True)
+            for r, w in enumerate(spaces):
+                C.ext.ep_combine_send(w.recv_x(), metas[r], w.peer_base, w.layout, r, w.capacity_rows, par)
+            for r, w in enumerate(spaces):
+                C.ext.ep_wait_rows(w.my_base, w.layout, metas[r], par, status, 1)
+    else:
+        raise SystemExit("unknown case")
+    torch.cuda.synchronize()
+    C.check_status(dev)
+    print("ok", case)
+
+
+if __name__ == "__main__":
+    main()

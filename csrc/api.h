@@ -31,6 +31,13 @@ typedef struct MdtGemmDesc {
   int accumulate;      // C += alpha * (A*B) instead of C = alpha * (A*B)
   float alpha;
   int* status;         // optional device word: set to a non-zero code if a wait inside the kernel gave up
+  // mode 1, optional: the A rows are being delivered by peer GPUs.  Before a CTA loads the 128-row tile t of A it
+  // waits (bounded) until tile_ready[t] >= tile_expected[t] (counters incremented by the senders with release).
+  const unsigned* tile_ready; const int* tile_expected;
+  // mode 0/1, optional: instead of writing C, the epilogue stores row r of the result at row row_dest_row[r] of the
+  // buffer peer_out[row_dest_rank[r]] (bf16, row stride ldc; rank < 0: row dropped) and then adds, per tile and
+  // destination, the number of rows delivered to the counter peer_arrive[rank] (release, system scope).
+  const int* row_dest_rank; const int* row_dest_row; const long long* peer_out; const long long* peer_arrive; int num_peers;
 } MdtGemmDesc;
 
 int mdt_gemm(const MdtGemmDesc* desc, cudaStream_t stream);

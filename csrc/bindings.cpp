@@ -37,7 +37,9 @@ static void fill_operand3(const Tensor& t, long long& rows, long long& cols, lon
 void gemm(int64_t mode, const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, Tensor& C, int64_t M, int64_t N, int64_t K,
           int64_t G, const OptTensor& offsets, int64_t capacity_rows, const OptTensor& B2, const OptTensor& A_l,
           bool a_mn_l, const OptTensor& B_l, const OptTensor& B2_l, bool b_mn_l, int64_t K_l, const OptTensor& C2,
-          const OptTensor& C3, bool accumulate, double alpha, const OptTensor& status) {
+          const OptTensor& C3, bool accumulate, double alpha, const OptTensor& status, const OptTensor& tile_ready,
+          const OptTensor& tile_expected, const OptTensor& row_dest_rank, const OptTensor& row_dest_row, const OptTensor& peer_out,
+          const OptTensor& peer_arrive) {
   CHECK_BF16(A); CHECK_BF16(B);
   c10::cuda::CUDAGuard guard(A.device());
   MdtGemmDesc d;
@@ -65,6 +67,15 @@ void gemm(int64_t mode, const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, 
   TORCH_CHECK(d.c_fp32 || C.scalar_type() == at::kBFloat16, "C must be bf16 or fp32");
   d.accumulate = accumulate; d.alpha = (float)alpha;
   d.status = status.has_value() ? status->data_ptr<int>() : nullptr;
+  if (tile_ready.has_value()) {
+    d.tile_ready = (const unsigned*)tile_ready->data_ptr();
+    d.tile_expected = tile_expected->data_ptr<int>();
+  }
+  if (row_dest_rank.has_value()) {
+    d.row_dest_rank = row_dest_rank->data_ptr<int>(); d.row_dest_row = row_dest_row->data_ptr<int>();
+    d.peer_out = (const long long*)peer_out->data_ptr<int64_t>(); d.peer_arrive = (const long long*)peer_arrive->data_ptr<int64_t>();
+    d.num_peers = (int)peer_out->numel();
+  }
   check(mdt_gemm(&d, cur_stream()), "mdt_gemm");
 }
 
@@ -254,10 +265,10 @@ std::vector<Tensor> attention_bwd(const Tensor& q, const Tensor& k, const Tensor
 // off_count_flags, off_arrive_x, off_arrive_y, off_recv_x, off_recv_y]; peer_base = int64 device tensor of
 // the peers' workspace base addresses.
 static MdtEpLayout to_layout(const std::vector<int64_t>& v) {
-  TORCH_CHECK(v.size() == 10, "layout needs 10 entries");
+  TORCH_CHECK(v.size() == 11, "layout needs 11 entries");
   MdtEpLayout L;
   L.ws = (int)v[0]; L.num_experts = (int)v[1]; L.capacity_rows = (int)v[2]; L.capacity_slots = (int)v[3];
-  L.off_counts = v[4]; L.off_count_flags = v[5]; L.off_arrive_x = v[6]; L.off_arrive_y = v[7]; L.off_recv_x = v[8]; L.off_recv_y = v[9];
+  L.off_counts = v[4]; L.off_count_flags = v[5]; L.off_arrive_x = v[6]; L.off_arrive_y = v[7]; L.off_recv_x = v[8]; L.off_recv_y = v[9]; L.off_tile_ctr = v[10];
   return L;
 }
 static const long long* ptrs(const Tensor& t) {
@@ -282,9 +293,9 @@ void ep_dispatch(const Tensor& x, const Tensor& src_slot, const Tensor& expert_o
   check(mdt_ep_dispatch(x.data_ptr(), src_slot.data_ptr<int>(), expert_of_slot.data_ptr<int>(), cptr(slot_scale), meta.data_ptr<int>(), ptrs(peer_base),
                         to_layout(layout), (int)expert_of_slot.numel(), (int)top_k, (int)x.size(1), (int)parity, cur_stream()), "ep_dispatch");
 }
-void ep_recv_prepare(int64_t my_base, std::vector<int64_t> layout, const Tensor& meta, int64_t cols, int64_t parity, Tensor& status) {
+void ep_recv_prepare(int64_t my_base, std::vector<int64_t> layout, const Tensor& meta, int64_t cols, int64_t parity, Tensor& status, bool wait_all) {
   c10::cuda::CUDAGuard guard(meta.device());
-  check(mdt_ep_recv_prepare(my_base, to_layout(layout), meta.data_ptr<int>(), (int)cols, (int)parity, status.data_ptr<int>(), cur_stream()), "ep_recv_prepare");
+  check(mdt_ep_recv_prepare(my_base, to_layout(layout), meta.data_ptr<int>(), (int)cols, (int)parity, wait_all, status.data_ptr<int>(), cur_stream()), "ep_recv_prepare");
 }
 void ep_combine_send(const Tensor& y, const Tensor& meta, const Tensor& peer_base, std::vector<int64_t> layout, int64_t rank, int64_t max_rows, int64_t parity) {
   CHECK_BF16(y);
@@ -292,9 +303,19 @@ void ep_combine_send(const Tensor& y, const Tensor& meta, const Tensor& peer_bas
   TORCH_CHECK(y.is_contiguous());
   check(mdt_ep_combine_send(y.data_ptr(), meta.data_ptr<int>(), ptrs(peer_base), to_layout(layout), (int)rank, (int)max_rows, (int)y.size(1), (int)parity, cur_stream()), "ep_combine_send");
 }
-void ep_wait_rows(int64_t my_base, std::vector<int64_t> layout, const Tensor& meta, int64_t parity, Tensor& status) {
+void ep_wait_rows(int64_t my_base, std::vector<int64_t> layout, const Tensor& meta, int64_t parity, Tensor& status, int64_t mult) {
   c10::cuda::CUDAGuard guard(meta.device());
-  check(mdt_ep_wait_rows(my_base, to_layout(layout), meta.data_ptr<int>(), (int)parity, status.data_ptr<int>(), cur_stream()), "ep_wait_rows");
+  check(mdt_ep_wait_rows(my_base, to_layout(layout), meta.data_ptr<int>(), (int)parity, (int)mult, status.data_ptr<int>(), cur_stream()), "ep_wait_rows");
+}
+// row_rank / row_pos [capacity_rows] and tile_expected [capacity_rows / 128] of this rank's receive layout
+std::vector<Tensor> ep_fused_meta(const Tensor& meta, std::vector<int64_t> layout, int64_t rank) {
+  c10::cuda::CUDAGuard guard(meta.device());
+  MdtEpLayout L = to_layout(layout);
+  auto rr = torch::full({L.capacity_rows}, -1, meta.options());
+  auto rp = torch::full({L.capacity_rows}, -1, meta.options());
+  auto te = torch::zeros({L.capacity_rows / 128}, meta.options());
+  check(mdt_ep_fused_meta(meta.data_ptr<int>(), L, (int)rank, rr.data_ptr<int>(), rp.data_ptr<int>(), te.data_ptr<int>(), cur_stream()), "ep_fused_meta");
+  return {rr, rp, te};
 }
 std::vector<int64_t> ep_meta_offsets(int64_t ws, int64_t E) {
   return {mdt_ep_meta_counts(ws, E), mdt_ep_meta_recv_tot(ws, E), mdt_ep_meta_recv_off(ws, E), mdt_ep_meta_dst_row(ws, E),
@@ -349,6 +370,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ep_recv_prepare", &ep_recv_prepare);
   m.def("ep_combine_send", &ep_combine_send);
   m.def("ep_wait_rows", &ep_wait_rows);
+  m.def("ep_fused_meta", &ep_fused_meta);
   m.def("ep_meta_offsets", &ep_meta_offsets);
   m.def("ag_pull", &ag_pull);
   m.def("rs_pull", &rs_pull);

@@ -33,29 +33,6 @@ typedef __nv_bfloat16 bf16;
 #define MDT_PEER_WAIT_LIMIT_NS 10000000000ull   // 10 s: covers start-up skew between ranks
 #endif
 
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ void red_add_release_sys(unsigned* p, unsigned v) {
-  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-// spin until *p >= target (acquire); false after the time limit
-__device__ __forceinline__ bool wait_ge(const unsigned* p, unsigned target, unsigned long long limit_ns) {
-  if (ld_acquire_sys(p) >= target) return true;
-  const unsigned long long t0 = global_timer_ns();
-  unsigned spins = 0;
-  while (ld_acquire_sys(p) < target) {
-    if ((++spins & 63u) == 0 && global_timer_ns() - t0 > limit_ns) return false;
-    __nanosleep(64);
-  }
-  return true;
-}
-
 // ---------------------------------------------------------------------------------------- counts
 __global__ void ep_counts_send_kernel(const int* __restrict__ counts, const long long* __restrict__ peer_base, MdtEpLayout L,
                                       int rank, int parity, unsigned epoch) {
@@ -176,7 +153,14 @@ __global__ void ep_dispatch_kernel(const bf16* __restrict__ x, const int* __rest
     uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(peer_base[d] + L.off_recv_x) + row * cols);
     const bool scaled = slot_scale != nullptr;
     copy_row(src, dst, cols / 8, lane, scaled ? __bfloat162float(slot_scale[slot]) : 1.f, scaled);
-    if (lane == 0) atomicAdd(&sent[d], 1u);
+    // rows-arrived counter of the destination's 128-row tile (read by a GEMM that waits tile by tile)
+    __threadfence_system();
+    __syncwarp();
+    if (lane == 0) {
+      unsigned* tctr = reinterpret_cast<unsigned*>(peer_base[d] + L.off_tile_ctr) + (long long)parity * (L.capacity_rows / 128) + row / 128;
+      red_add_release_sys(tctr, 1u);
+      atomicAdd(&sent[d], 1u);
+    }
   }
   __threadfence_system();
   __syncthreads();
@@ -188,7 +172,7 @@ __global__ void ep_dispatch_kernel(const bf16* __restrict__ x, const int* __rest
 
 // zero the padding rows of my receive buffer; block 0 additionally waits for all expected rows
 __global__ void ep_recv_prepare_kernel(long long my_base, MdtEpLayout L, const int* __restrict__ meta, int cols, int parity,
-                                       int* __restrict__ status) {
+                                       int wait_all, int* __restrict__ status) {
   const int ws = L.ws, E = L.num_experts, El = E / ws;
   const int* recv_tot = meta + mdt_ep_meta_recv_tot(ws, E);
   const int* recv_off = meta + mdt_ep_meta_recv_off(ws, E);
@@ -201,11 +185,23 @@ __global__ void ep_recv_prepare_kernel(long long my_base, MdtEpLayout L, const i
       for (int i = threadIdx.x; i < vecs; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
     }
   }
+  // the other parity's tile counters were consumed by the previous exchange and are written next by the
+  // following one (which no peer starts before this rank has sent its results of the current one)
+  {
+    unsigned* other = reinterpret_cast<unsigned*>(my_base + L.off_tile_ctr) + (long long)(parity ^ 1) * (L.capacity_rows / 128);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < L.capacity_rows / 128; i += gridDim.x * blockDim.x) other[i] = 0;
+  }
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     unsigned* ctr = reinterpret_cast<unsigned*>(my_base + L.off_arrive_x) + parity;
     const unsigned expected = (unsigned)meta[mdt_ep_meta_scalars(ws, E)];
-    if (!wait_ge(ctr, expected, MDT_PEER_WAIT_LIMIT_NS)) { if (status) atomicCAS(status, 0, ST_TIMEOUT_PEER); }
-    *ctr = 0;   // this parity is next written two exchanges from now
+    if (wait_all) {
+      if (!wait_ge(ctr, expected, MDT_PEER_WAIT_LIMIT_NS)) { if (status) atomicCAS(status, 0, ST_TIMEOUT_PEER); }
+      *ctr = 0;   // this parity is next written two exchanges from now
+    } else {
+      // a consumer waits on the per-tile counters instead; the total counter of the other parity is
+      // idle by the same argument as above
+      reinterpret_cast<unsigned*>(my_base + L.off_arrive_x)[parity ^ 1] = 0;
+    }
   }
 }
 
@@ -248,9 +244,37 @@ __global__ void ep_combine_send_kernel(const bf16* __restrict__ y, const int* __
   }
 }
 
-__global__ void ep_wait_rows_kernel(long long my_base, MdtEpLayout L, const int* __restrict__ meta, int parity, int* __restrict__ status) {
+// For every row of my receive layout: the rank it returns to and its position there (-1 for padding), and for
+// every 128-row tile the number of rows that must arrive before it may be read.
+__global__ void ep_fused_meta_kernel(const int* __restrict__ meta, MdtEpLayout L, int rank, int* __restrict__ row_rank,
+                                     int* __restrict__ row_pos, int* __restrict__ tile_expected) {
+  const int ws = L.ws, E = L.num_experts, El = E / ws;
+  const int* recv_tot = meta + mdt_ep_meta_recv_tot(ws, E);
+  const int* recv_off = meta + mdt_ep_meta_recv_off(ws, E);
+  const int* seg_row = meta + mdt_ep_meta_seg_row(ws, E);
+  const int* seg_pos = meta + mdt_ep_meta_seg_pos(ws, E);
+  const int used = min(recv_off[El], L.capacity_rows);
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < used; r += gridDim.x * blockDim.x) {
+    int le = 0;
+    while (le + 1 < El && recv_off[le + 1] <= r) ++le;
+    int rk = -1, ps = -1;
+    if (r - recv_off[le] < recv_tot[le]) {
+      int s = 0;
+      while (s + 1 < ws && seg_row[le * ws + s + 1] <= r) ++s;
+      // (the last segment starting at or before r is never empty: empty ones share their start with the next)
+      rk = s; ps = seg_pos[le * ws + s] + (r - seg_row[le * ws + s]);
+    }
+    row_rank[r] = rk; row_pos[r] = ps;
+    if ((r & 127) == 0) {
+      const int left = recv_tot[le] - (r - recv_off[le]);
+      tile_expected[r >> 7] = left < 0 ? 0 : (left > 128 ? 128 : left);
+    }
+  }
+}
+
+__global__ void ep_wait_rows_kernel(long long my_base, MdtEpLayout L, const int* __restrict__ meta, int parity, int mult, int* __restrict__ status) {
   unsigned* ctr = reinterpret_cast<unsigned*>(my_base + L.off_arrive_y) + parity;
-  const unsigned expected = (unsigned)meta[mdt_ep_meta_scalars(L.ws, L.num_experts) + 1];
+  const unsigned expected = (unsigned)meta[mdt_ep_meta_scalars(L.ws, L.num_experts) + 1] * (unsigned)mult;
   if (!wait_ge(ctr, expected, MDT_PEER_WAIT_LIMIT_NS)) { if (status) atomicCAS(status, 0, ST_TIMEOUT_PEER); }
   *ctr = 0;
 }
@@ -322,8 +346,8 @@ extern "C" int mdt_ep_dispatch(const void* x, const int* src_slot, const int* ex
   MDT_CM_CHECK();
   return 0;
 }
-extern "C" int mdt_ep_recv_prepare(long long my_base, MdtEpLayout L, const int* meta, int cols, int parity, int* status, cudaStream_t s) {
-  ep_recv_prepare_kernel<<<64, 256, 0, s>>>(my_base, L, meta, cols, parity, status);
+extern "C" int mdt_ep_recv_prepare(long long my_base, MdtEpLayout L, const int* meta, int cols, int parity, int wait_all, int* status, cudaStream_t s) {
+  ep_recv_prepare_kernel<<<64, 256, 0, s>>>(my_base, L, meta, cols, parity, wait_all, status);
   MDT_CM_CHECK();
   return 0;
 }
@@ -336,8 +360,13 @@ extern "C" int mdt_ep_combine_send(const void* y, const int* meta, const long lo
   MDT_CM_CHECK();
   return 0;
 }
-extern "C" int mdt_ep_wait_rows(long long my_base, MdtEpLayout L, const int* meta, int parity, int* status, cudaStream_t s) {
-  ep_wait_rows_kernel<<<1, 1, 0, s>>>(my_base, L, meta, parity, status);
+extern "C" int mdt_ep_fused_meta(const int* meta, MdtEpLayout L, int rank, int* row_rank, int* row_pos, int* tile_expected, cudaStream_t s) {
+  ep_fused_meta_kernel<<<64, 256, 0, s>>>(meta, L, rank, row_rank, row_pos, tile_expected);
+  MDT_CM_CHECK();
+  return 0;
+}
+extern "C" int mdt_ep_wait_rows(long long my_base, MdtEpLayout L, const int* meta, int parity, int mult, int* status, cudaStream_t s) {
+  ep_wait_rows_kernel<<<1, 1, 0, s>>>(my_base, L, meta, parity, mult < 1 ? 1 : mult, status);
   MDT_CM_CHECK();
   return 0;
 }

@@ -17,6 +17,7 @@ typedef struct MdtEpLayout {
   long long off_arrive_y;   // u32   [2]
   long long off_recv_x;     // bf16  [capacity_rows][cols]
   long long off_recv_y;     // bf16  [capacity_slots][cols]
+  long long off_tile_ctr;   // u32   [2][capacity_rows / 128]  rows arrived per 128-row tile of recv_x
 } MdtEpLayout;
 
 // Offsets (in ints) into the per-exchange metadata buffer written by mdt_ep_counts_wait_meta.
@@ -42,10 +43,11 @@ int mdt_ep_counts_send(const int* counts, const long long* peer_base, MdtEpLayou
 int mdt_ep_counts_wait_meta(long long my_base, MdtEpLayout L, int rank, int parity, unsigned epoch, int* meta, int* status, cudaStream_t s);
 int mdt_ep_dispatch(const void* x, const int* src_slot, const int* expert_of_slot, const void* slot_scale, const int* meta,
                     const long long* peer_base, MdtEpLayout L, int num_slots, int top_k, int cols, int parity, cudaStream_t s);
-int mdt_ep_recv_prepare(long long my_base, MdtEpLayout L, const int* meta, int cols, int parity, int* status, cudaStream_t s);
+int mdt_ep_recv_prepare(long long my_base, MdtEpLayout L, const int* meta, int cols, int parity, int wait_all, int* status, cudaStream_t s);
+int mdt_ep_fused_meta(const int* meta, MdtEpLayout L, int rank, int* row_rank, int* row_pos, int* tile_expected, cudaStream_t s);
 int mdt_ep_combine_send(const void* y, const int* meta, const long long* peer_base, MdtEpLayout L, int rank, int max_rows, int cols,
                         int parity, cudaStream_t s);
-int mdt_ep_wait_rows(long long my_base, MdtEpLayout L, const int* meta, int parity, int* status, cudaStream_t s);
+int mdt_ep_wait_rows(long long my_base, MdtEpLayout L, const int* meta, int parity, int mult, int* status, cudaStream_t s);
 int mdt_ag_pull(void* out, const long long* peer_shard, int ws, long long bytes_per_rank, cudaStream_t s);
 int mdt_rs_pull(void* out, const long long* peer_full, int ws, int rank, long long n, int in_fp32, int out_fp32, float scale,
                 int accumulate, cudaStream_t s);

@@ -67,6 +67,32 @@ __device__ __forceinline__ bool wait_parity(uint64_t* bar, uint32_t parity, vola
   }
 }
 
+// ---- system-scope flags and counters (peer GPUs over NVLink) --------------------------------------
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_add_release_sys(unsigned* p, unsigned v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// generic-proxy writes (also those of peers, once acquired) become visible to later async-proxy (TMA) reads
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// spin until *p >= target (acquire); false after the time limit
+__device__ __forceinline__ bool wait_ge(const unsigned* p, unsigned target, unsigned long long limit_ns) {
+  if (ld_acquire_sys(p) >= target) return true;
+  const unsigned long long t0 = global_timer_ns();
+  unsigned spins = 0;
+  while (ld_acquire_sys(p) < target) {
+    if ((++spins & 63u) == 0 && global_timer_ns() - t0 > limit_ns) return false;
+    __nanosleep(64);
+  }
+  return true;
+}
+
 // ---- TMA tiled loads (no cluster-wide forms are used anywhere in this code base) ------------
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile(

@@ -48,7 +48,12 @@ struct GemmParams {
   float alpha;
   int store_gate_up;
   int* status;
+  const unsigned* tile_ready; const int* tile_expected;
+  const int* row_dest_rank; const int* row_dest_row; const long long* peer_out; const long long* peer_arrive; int num_peers;
 };
+#ifndef MDT_GEMM_PEER_WAIT_NS
+#define MDT_GEMM_PEER_WAIT_NS 10000000000ull
+#endif
 
 struct Tile {
   int g, m0, n0, krow0, num_kb, num_kb_l;
@@ -162,6 +167,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     bool ok = true;
     for (int tile = blockIdx.x; ok && (p.dual ? get_tile<BN / 2>(p, tile, t) : get_tile<BN>(p, tile, t)); tile += gridDim.x) {
       const int total_kb = t.num_kb + (t.num_kb > 0 || p.mode != 2 ? t.num_kb_l : 0);
+      if (p.tile_ready != nullptr) {
+        // rows of this tile are stored by peer GPUs: wait for them, then order the TMA reads after the acquire
+        const int ti = t.m0 / BM;
+        if (!wait_ge(p.tile_ready + ti, (unsigned)p.tile_expected[ti], MDT_GEMM_PEER_WAIT_NS)) { fail(ST_TIMEOUT_PEER); ok = false; break; }
+        fence_proxy_async_all();
+      }
       for (int kb = 0; kb < total_kb; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
@@ -255,7 +266,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       const int row = t.m0 + q * 32 + lane;
       const int row_limit = (p.mode == 1) ? p.offsets[p.G] : p.M;
       const bool row_ok = row < row_limit;
-      const long long base = (p.mode == 2 ? (long long)t.g * p.c_group_stride : 0) + (long long)row * p.ldc;
+      long long base = (p.mode == 2 ? (long long)t.g * p.c_group_stride : 0) + (long long)row * p.ldc;
+      void* Cout = p.C;
+      int dest = -1;
+      bool store_ok = row_ok;
+      if (p.row_dest_rank != nullptr) {          // result rows go straight into peers' buffers
+        dest = row_ok ? p.row_dest_rank[row] : -1;
+        store_ok = dest >= 0;
+        if (store_ok) { Cout = reinterpret_cast<void*>(p.peer_out[dest]); base = (long long)p.row_dest_row[row] * p.ldc; }
+      }
       if (total_kb == 0) {
         if (!p.accumulate && row_ok) {
           float z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -302,7 +321,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           uint32_t r[32];
           tmem_ld_32x32(taddr + c, r);
           tmem_ld_wait();
-          if (row_ok) {
+          if (store_ok) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               const int col = t.n0 + c + v * 8;
@@ -310,7 +329,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
                 float o[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(r[v * 8 + i]) * p.alpha;
-                store8(p.C, base + col, o, p.c_fp32, p.accumulate);
+                store8(Cout, base + col, o, p.c_fp32, p.accumulate);
               }
             }
           }
@@ -321,6 +340,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
       ++acc_it;
+      if (p.row_dest_rank != nullptr) {
+        // publish this warp's rows: one count per (row, column tile) and destination
+        __threadfence_system();
+        __syncwarp();
+        for (int d = 0; d < p.num_peers; ++d) {
+          const unsigned m = __ballot_sync(0xffffffffu, dest == d);
+          if (lane == 0 && m != 0) red_add_release_sys(reinterpret_cast<unsigned*>(p.peer_arrive[d]), __popc(m));
+        }
+      }
     }
   }
 
@@ -404,6 +432,10 @@ extern "C" int mdt_gemm(const MdtGemmDesc* d, cudaStream_t stream) {
   p.offsets = d->offsets; p.C = d->C; p.C2 = d->C2; p.C3 = d->C3; p.ldc = d->ldc; p.c_group_stride = d->c_group_stride;
   p.c_fp32 = d->c_fp32; p.accumulate = d->accumulate; p.alpha = d->alpha; p.store_gate_up = d->C2 != nullptr;
   p.status = d->status;
+  p.tile_ready = d->tile_ready; p.tile_expected = d->tile_expected;
+  p.row_dest_rank = d->row_dest_rank; p.row_dest_row = d->row_dest_row; p.peer_out = d->peer_out; p.peer_arrive = d->peer_arrive;
+  p.num_peers = d->num_peers;
+  if (p.row_dest_rank != nullptr && (p.dual || p.c_fp32 || p.accumulate || p.mode == 2)) return -12;
   if (p.N % 8 != 0 || p.ldc % 8 != 0) return -10;
   if (p.dual && (p.b_mn != 0 || p.c_fp32 || p.accumulate)) return -11;
   const int BN = (p.dual || p.N > 128) ? 256 : 128;

@@ -41,9 +41,13 @@ def launch_count() -> int:
 
 
 def _gemm(mode, A, a_mn, B, b_mn, C, M, N, K, G=1, offsets=None, capacity=0, B2=None, A_l=None, a_mn_l=False,
-          B_l=None, B2_l=None, b_mn_l=False, K_l=0, C2=None, C3=None, accumulate=False, alpha=1.0):
+          B_l=None, B2_l=None, b_mn_l=False, K_l=0, C2=None, C3=None, accumulate=False, alpha=1.0, wait=None, scatter=None):
+    """wait = (tile_ready, tile_expected): A rows arrive from peers, tile by tile.  scatter = (row_rank, row_pos,
+    peer_out table, peer_arrive table): result rows are stored into peers' buffers instead of C."""
+    w0, w1 = wait if wait is not None else (None, None)
+    s0, s1, s2, s3 = scatter if scatter is not None else (None, None, None, None)
     ext.gemm(mode, A, a_mn, B, b_mn, C, M, N, K, G, offsets, capacity, B2, A_l, a_mn_l, B_l, B2_l, b_mn_l, K_l,
-             C2, C3, accumulate, alpha, status_tensor(A.device))
+             C2, C3, accumulate, alpha, status_tensor(A.device), w0, w1, s0, s1, s2, s3)
     return C
 
 
@@ -220,13 +224,16 @@ class _GroupedSwiGLUMLP(torch.autograd.Function):
         l3 = lora.get("w3") if lora else None
         kw = {}
         t13 = A13 = B1p = B3p = None
+        # rows still arriving from peer GPUs: the first GEMM that reads xg waits tile by tile
+        wait = getattr(plan, "ep_wait", None)
         if l1 is not None or l3 is not None:
             assert l1 is not None and l3 is not None, "expert LoRA must cover w1 and w3 together"
             (A1, B1, s1), (A3, B3, s3) = l1, l3
             r = A1.shape[2]
             A13 = torch.cat([A1 * s1 if s1 != 1.0 else A1, A3 * s3 if s3 != 1.0 else A3], dim=2).contiguous()  # [E,H,2r], scale folded
             t13 = torch.empty(R, 2 * r, dtype=dt, device=dev)
-            _g(1, xg, False, A13, True, t13, 2 * r, H, plan)
+            _g(1, xg, False, A13, True, t13, 2 * r, H, plan, wait=wait)
+            wait = None
             z = torch.zeros_like(B1)
             B1p, B3p = torch.cat([B1, z], dim=1).contiguous(), torch.cat([z, B3], dim=1).contiguous()  # [E,2r,F]
             kw = dict(A_l=t13, B_l=B1p, B2_l=B3p, b_mn_l=True, K_l=2 * r)
@@ -234,7 +241,9 @@ class _GroupedSwiGLUMLP(torch.autograd.Function):
         g = u = None
         if need_grad:
             g, u = torch.empty_like(h), torch.empty_like(h)
-        _g(1, xg, False, w1, False, h, F, H, plan, B2=w3, C2=g, C3=u, **kw)
+        _g(1, xg, False, w1, False, h, F, H, plan, B2=w3, C2=g, C3=u, wait=wait, **kw)
+        if getattr(plan, "ep_clone_input", False):
+            xg = xg.clone()          # all rows have arrived now; the receive buffer is re-used by later exchanges
         t2 = None
         kw2 = {}
         if l2 is not None:
@@ -243,7 +252,8 @@ class _GroupedSwiGLUMLP(torch.autograd.Function):
             _g(1, h, False, A2, True, t2, A2.shape[2], F, plan, alpha=s2)
             kw2 = dict(A_l=t2, B_l=B2, b_mn_l=True, K_l=A2.shape[2])
         y = torch.empty(R, H, dtype=dt, device=dev)
-        _g(1, h, False, w2, True, y, H, F, plan, **kw2)
+        # with ep_scatter the result rows go straight into the source ranks' buffers (y itself stays unwritten)
+        _g(1, h, False, w2, True, y, H, F, plan, scatter=getattr(plan, "ep_scatter", None), **kw2)
         if need_grad:
             ctx.plan, ctx.lora, ctx.wgrad_scale, ctx.wgrad_out = plan, lora, wgrad_scale, wgrad_out
             ctx.n_lora, ctx.lora_ids = len(lora_tensors), lora_ids
@@ -262,6 +272,9 @@ class _GroupedSwiGLUMLP(torch.autograd.Function):
         l2 = lora.get("w2") if lora else None
         l3 = lora.get("w3") if lora else None
         grads = {}
+        wait = getattr(plan, "ep_wait", None)        # dy rows still arriving from peers (fused exchange)
+        scatter = getattr(plan, "ep_scatter", None) if l1 is None else None
+        plan.ep_scattered = scatter is not None
         # ---- down projection
         kw = {}
         dt2 = None
@@ -269,10 +282,11 @@ class _GroupedSwiGLUMLP(torch.autograd.Function):
             A2, B2, s2 = l2
             r = A2.shape[2]
             dt2 = torch.empty(R, r, dtype=dt, device=dev)
-            _g(1, dy, False, B2, False, dt2, r, H, plan, alpha=s2)             # s * dy B2^T
+            _g(1, dy, False, B2, False, dt2, r, H, plan, alpha=s2, wait=wait)  # s * dy B2^T
+            wait = None
             kw = dict(A_l=dt2, B_l=A2, b_mn_l=False, K_l=r)
         dh = torch.empty(R, F, dtype=dt, device=dev)
-        _g(1, dy, False, w2, False, dh, F, H, plan, **kw)                       # dy W2^T (W2 stored [F,H])
+        _g(1, dy, False, w2, False, dh, F, H, plan, wait=wait, **kw)            # dy W2^T (W2 stored [F,H])
         wg = ctx.wgrad_out
         dw1 = dw2 = dw3 = None
         need_w = ctx.needs_input_grad[1] or ctx.needs_input_grad[2] or ctx.needs_input_grad[3]
@@ -291,7 +305,7 @@ class _GroupedSwiGLUMLP(torch.autograd.Function):
         dg, du = ext.swiglu_bwd(g, u, dh)
         # ---- up projections
         dx = torch.empty(R, H, dtype=dt, device=dev)
-        _g(1, dg, False, w1, True, dx, H, F, plan, A_l=du, B_l=w3, b_mn_l=True, K_l=F)   # dg W1 + du W3
+        _g(1, dg, False, w1, True, dx, H, F, plan, A_l=du, B_l=w3, b_mn_l=True, K_l=F, scatter=scatter)   # dg W1 + du W3
         if need_w:
             if wg is not None:
                 _g(2, dg, True, xg, True, wg[0], H, 0, plan, alpha=ws, accumulate=True)

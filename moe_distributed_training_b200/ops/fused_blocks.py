@@ -8,11 +8,15 @@ bookkeeping in between.  The math is the same as composing the individual ops of
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import cuda_ops as C
 
 ext = C.ext
+# expert GEMMs wait for / deliver rows themselves (tile-wise overlap with the exchange) instead of separate kernels
+GEMM_FUSION = os.environ.get("MDT_EP_GEMM_FUSION", "1") != "0"
 
 
 def _lin_fwd(x2, W, A, B, s):
@@ -191,12 +195,24 @@ class _MoEBlock(torch.autograd.Function):
             eos = idx.reshape(-1).contiguous()
             expert_sorted = eos.index_select(0, plan.src_slot.long()) if grad_mode else None
             par = eng.next_phase()
-            eng.dispatch(xn, plan.src_slot, eos, None, meta_c, k, par)
-            xr = eng.wspace.recv_x()
-            if grad_mode:
-                xr = xr.clone()
-            yg = C._GroupedSwiGLUMLP.forward(mctx, xr, w1, w2, w3, eng.recv_plan(meta_c), lora, float(ws), wgrad_out, ids, *lora_tensors)
-            ys = eng.combine(yg, meta_c, par, n_slots, clone=grad_mode)
+            rplan = eng.recv_plan(meta_c)
+            if GEMM_FUSION:
+                # the expert GEMMs take part in the exchange: the first one waits for its row tiles as they arrive,
+                # the down projection stores its result rows straight into the source ranks' buffers
+                rr, rp, te = eng.fused_meta(meta_c)
+                eng.dispatch(xn, plan.src_slot, eos, None, meta_c, k, par, wait=False)
+                rplan.ep_wait, rplan.ep_scatter = eng.gemm_wait(par, te), eng.gemm_scatter(par, rr, rp)
+                rplan.ep_clone_input, rplan.ep_meta = grad_mode, (rr, rp, te)
+                H = x2.shape[1]
+                C._GroupedSwiGLUMLP.forward(mctx, eng.wspace.recv_x(), w1, w2, w3, rplan, lora, float(ws), wgrad_out, ids, *lora_tensors)
+                ys = eng.wait_rows(meta_c, par, n_slots, (H + 255) // 256 if H > 128 else 1, clone=grad_mode)
+            else:
+                eng.dispatch(xn, plan.src_slot, eos, None, meta_c, k, par)
+                xr = eng.wspace.recv_x()
+                if grad_mode:
+                    xr = xr.clone()
+                yg = C._GroupedSwiGLUMLP.forward(mctx, xr, w1, w2, w3, rplan, lora, float(ws), wgrad_out, ids, *lora_tensors)
+                ys = eng.combine(yg, meta_c, par, n_slots, clone=grad_mode)
             comb = ext.combine_rows(ys, plan.dest_row, wts, k)
         comb.add_(x2)
         if grad_mode:
@@ -219,9 +235,22 @@ class _MoEBlock(torch.autograd.Function):
             dxn = ext.combine_rows(g[0], plan.dest_row, None, k)
         else:
             par = eng.next_phase()
-            eng.dispatch(d_rows, eng.identity(d_rows.shape[0]), expert_sorted, None, meta_c, 1, par)
-            g = C._GroupedSwiGLUMLP.backward(mctx, eng.wspace.recv_x())
-            back = eng.combine(g[0].contiguous(), meta_c, par, plan.dest_row.numel(), clone=False)
+            rplan = mctx.plan
+            n_slots = plan.dest_row.numel()
+            if GEMM_FUSION:
+                rr, rp, te = rplan.ep_meta
+                eng.dispatch(d_rows, eng.identity(d_rows.shape[0]), expert_sorted, None, meta_c, 1, par, wait=False)
+                rplan.ep_wait, rplan.ep_scatter, rplan.ep_clone_input = eng.gemm_wait(par, te), eng.gemm_scatter(par, rr, rp), False
+                g = C._GroupedSwiGLUMLP.backward(mctx, eng.wspace.recv_x())
+                if rplan.ep_scattered:
+                    H = x2.shape[1]
+                    back = eng.wait_rows(meta_c, par, n_slots, (H + 255) // 256 if H > 128 else 1, clone=False)
+                else:
+                    back = eng.combine(g[0].contiguous(), meta_c, par, n_slots, clone=False)
+            else:
+                eng.dispatch(d_rows, eng.identity(d_rows.shape[0]), expert_sorted, None, meta_c, 1, par)
+                g = C._GroupedSwiGLUMLP.backward(mctx, eng.wspace.recv_x())
+                back = eng.combine(g[0].contiguous(), meta_c, par, n_slots, clone=False)
             dxn = ext.combine_rows(back, plan.dest_row, None, k)
         dxr, dWr = ext.router_bwd(xn, Wr.contiguous(), idx, dwts, None, True)
         dxn.add_(dxr)

@@ -126,18 +126,40 @@ class FusedExpertParallel:
         self.ext.ep_counts_wait_meta(w.my_base, w.layout, w.rank, parity, self.count_epoch, meta, self.status())
         return meta
 
-    def dispatch(self, x, src_slot, expert_of_slot, slot_scale, meta, top_k, parity):
+    def dispatch(self, x, src_slot, expert_of_slot, slot_scale, meta, top_k, parity, wait: bool = True):
+        """Send my rows; `wait=False` leaves the waiting to a GEMM that checks the per-tile arrival counters."""
         w = self.wspace
         assert expert_of_slot.numel() <= w.capacity_slots, "more (token, choice) slots than the workspace was sized for"
         self.ext.ep_dispatch(x, src_slot, expert_of_slot, slot_scale, meta, w.peer_base, w.layout, top_k, parity)
-        self.ext.ep_recv_prepare(w.my_base, w.layout, meta, w.cols, parity, self.status())
+        self.ext.ep_recv_prepare(w.my_base, w.layout, meta, w.cols, parity, self.status(), wait)
 
     def combine(self, y, meta, parity, n_slots, clone: bool):
         w = self.wspace
         self.ext.ep_combine_send(y, meta, w.peer_base, w.layout, w.rank, w.capacity_rows, parity)
-        self.ext.ep_wait_rows(w.my_base, w.layout, meta, parity, self.status())
+        return self.wait_rows(meta, parity, n_slots, 1, clone)
+
+    def wait_rows(self, meta, parity, n_slots, mult: int, clone: bool):
+        w = self.wspace
+        self.ext.ep_wait_rows(w.my_base, w.layout, meta, parity, self.status(), mult)
         out = w.recv_y()[:n_slots]
         return out.clone() if clone else out
+
+    # -- pieces for GEMMs that take part in the exchange themselves
+    def fused_meta(self, meta):
+        """(row -> source rank, row -> position at the source, rows expected per 128-row tile) of my receive layout."""
+        w = self.wspace
+        return self.ext.ep_fused_meta(meta, w.layout, w.rank)
+
+    def gemm_wait(self, parity, tile_expected):
+        return (self.wspace.tile_counters(parity), tile_expected)
+
+    def gemm_scatter(self, parity, row_rank, row_pos):
+        w = self.wspace
+        if not hasattr(self, "_peer_out"):
+            self._peer_out = torch.tensor([b + w.layout[9] for b in w.bases], dtype=torch.int64, device=self.device)
+            self._peer_arrive = [torch.tensor([b + w.layout[7] + 4 * par for b in w.bases], dtype=torch.int64, device=self.device)
+                                 for par in (0, 1)]
+        return (row_rank, row_pos, self._peer_out, self._peer_arrive[parity])
 
     def recv_plan(self, meta) -> RoutingPlan:
         w = self.wspace

@@ -42,6 +42,11 @@ class EpWorkspace:
         off = self.layout[8]
         return self.buffer[off:off + self.capacity_rows * self.cols * 2].view(torch.bfloat16).view(self.capacity_rows, self.cols)
 
+    def tile_counters(self, parity: int) -> torch.Tensor:
+        n = self.capacity_rows // 128
+        off = self.layout[10] + parity * n * 4
+        return self.buffer[off:off + n * 4].view(torch.int32)
+
     def recv_y(self) -> torch.Tensor:
         off = self.layout[9]
         return self.buffer[off:off + self.capacity_slots * self.cols * 2].view(torch.bfloat16).view(self.capacity_slots, self.cols)
@@ -55,7 +60,8 @@ def ep_layout(ws: int, num_experts: int, cols: int, capacity_rows: int, capacity
     off_ay = off; off = _align(off + 8)
     off_rx = off; off = _align(off + capacity_rows * cols * 2)
     off_ry = off; off = _align(off + capacity_slots * cols * 2)
-    return [ws, num_experts, capacity_rows, capacity_slots, off_counts, off_flags, off_ax, off_ay, off_rx, off_ry], off
+    off_tc = off; off = _align(off + 2 * (capacity_rows // 128) * 4)
+    return [ws, num_experts, capacity_rows, capacity_slots, off_counts, off_flags, off_ax, off_ay, off_rx, off_ry, off_tc], off
 
 
 def ep_capacities(ws: int, num_experts: int, max_tokens: int, top_k: int, capacity_factor: Optional[float] = None):

@@ -40,7 +40,7 @@ def test_dispatch_and_combine_emulated_ranks(cops, ws, E, k, tokens):
         for r, w in enumerate(spaces):
             ext.ep_dispatch(xs[r], plans[r].src_slot, tops[r].reshape(-1).contiguous(), None, metas[r], w.peer_base, w.layout, k, par)
         for r, w in enumerate(spaces):
-            ext.ep_recv_prepare(w.my_base, w.layout, metas[r], H, par, status)
+            ext.ep_recv_prepare(w.my_base, w.layout, metas[r], H, par, status, True)
         cops.check_status(DEV)
         # oracle of every receive buffer
         for d, w in enumerate(spaces):
@@ -64,7 +64,7 @@ def test_dispatch_and_combine_emulated_ranks(cops, ws, E, k, tokens):
         for r, w in enumerate(spaces):
             ext.ep_combine_send(ys[r], metas[r], w.peer_base, w.layout, r, w.capacity_rows, par)
         for r, w in enumerate(spaces):
-            ext.ep_wait_rows(w.my_base, w.layout, metas[r], par, status)
+            ext.ep_wait_rows(w.my_base, w.layout, metas[r], par, status, 1)
         cops.check_status(DEV)
         for r, w in enumerate(spaces):
             n = tops[r].numel()
@@ -104,3 +104,54 @@ def test_peer_wait_gives_up_with_a_status_code(cops):
     ext.barrier_wait(flags.data_ptr(), 2, 1, status, 200)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("ws,E,tokens", [(2, 4, [300, 77]), (4, 8, [513, 128, 700, 5])])
+def test_gemm_takes_part_in_the_exchange_emulated_ranks(cops, ws, E, tokens):
+    """Grouped GEMM that waits for its row tiles on the arrival counters and stores its result rows straight
+    into the source ranks' buffers, for several ranks emulated on one GPU (all sends before any GEMM)."""
+    from moe_distributed_training_b200.ops.reference import RoutingPlan
+    from moe_distributed_training_b200.parallel import symm
+    ext = cops.ext
+    H, N, k, El = 256, 512, 2, E // ws
+    torch.manual_seed(3)
+    spaces = symm.emulate_ep_workspaces(ws, E, N, max(tokens), k, DEV)   # recv rows have N columns on the way back
+    # the forward buffer holds H-column rows: use a second set of workspaces for the inputs
+    spaces_in = symm.emulate_ep_workspaces(ws, E, H, max(tokens), k, DEV)
+    status = cops.status_tensor(DEV)
+    W = (torch.randn(E, N, H, device=DEV) * 0.05).to(torch.bfloat16)
+    xs = [torch.randn(t, H, device=DEV).to(torch.bfloat16) for t in tokens]
+    tops = [torch.randn(t, E, device=DEV).topk(k, -1).indices.int() for t in tokens]
+    plans = [cops.make_plan(tp, E, 1, tp.numel()) for tp in tops]
+    off = [int(v) for v in ext.ep_meta_offsets(ws, E)]
+    metas = [torch.zeros(off[8], dtype=torch.int32, device=DEV) for _ in range(ws)]
+    for epoch in (1, 2):
+        par = epoch & 1
+        for r, w in enumerate(spaces_in):
+            ext.ep_counts_send(plans[r].tokens_per_expert, w.peer_base, w.layout, r, par, epoch)
+        for r, w in enumerate(spaces_in):
+            ext.ep_counts_wait_meta(w.my_base, w.layout, r, par, epoch, metas[r], status)
+        for r, w in enumerate(spaces_in):
+            ext.ep_dispatch(xs[r], plans[r].src_slot, tops[r].reshape(-1).contiguous(), None, metas[r], w.peer_base, w.layout, k, par)
+        for r, w in enumerate(spaces_in):
+            ext.ep_recv_prepare(w.my_base, w.layout, metas[r], H, par, status, False)
+        for r, (wi, wo) in enumerate(zip(spaces_in, spaces)):
+            rr, rp, te = ext.ep_fused_meta(metas[r], wi.layout, r)
+            m = metas[r]
+            rplan = RoutingPlan(m[off[1]:off[1] + El], m[off[2]:off[2] + El + 1], None, None, 1, El, capacity_rows=wi.capacity_rows)
+            peer_out = torch.tensor([b + wo.layout[9] for b in wo.bases], dtype=torch.int64, device=DEV)
+            peer_arr = torch.tensor([b + wo.layout[7] + 4 * par for b in wo.bases], dtype=torch.int64, device=DEV)
+            dummy = torch.empty(wi.capacity_rows, N, dtype=torch.bfloat16, device=DEV)
+            cops._g(1, wi.recv_x(), False, W[r * El:(r + 1) * El], False, dummy, N, H, rplan,
+                    wait=(wi.tile_counters(par), te), scatter=(rr, rp, peer_out, peer_arr))
+        for r, wo in enumerate(spaces):
+            ext.ep_wait_rows(wo.my_base, wo.layout, metas[r], par, status, (N + 255) // 256)
+        cops.check_status(DEV)
+        for r, wo in enumerate(spaces):
+            n = tops[r].numel()
+            slot = plans[r].src_slot[:n].long()
+            e = tops[r].reshape(-1)[slot].long()
+            want = torch.einsum("nh,nkh->nk", xs[r][slot // k].float(), W[e].float())
+            got = wo.recv_y()[:n].float()
+            err = (got - want).norm() / want.norm()
+            assert err < 2e-2, (r, float(err))
