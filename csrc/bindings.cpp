@@ -311,9 +311,10 @@ void ep_wait_rows(int64_t my_base, std::vector<int64_t> layout, const Tensor& me
 std::vector<Tensor> ep_fused_meta(const Tensor& meta, std::vector<int64_t> layout, int64_t rank) {
   c10::cuda::CUDAGuard guard(meta.device());
   MdtEpLayout L = to_layout(layout);
-  auto rr = torch::full({L.capacity_rows}, -1, meta.options());
-  auto rp = torch::full({L.capacity_rows}, -1, meta.options());
-  auto te = torch::zeros({L.capacity_rows / 128}, meta.options());
+  // the kernel writes every entry a consumer can read (rows / tiles below the padded row count in use)
+  auto rr = torch::empty({L.capacity_rows}, meta.options());
+  auto rp = torch::empty({L.capacity_rows}, meta.options());
+  auto te = torch::empty({L.capacity_rows / 128}, meta.options());
   check(mdt_ep_fused_meta(meta.data_ptr<int>(), L, (int)rank, rr.data_ptr<int>(), rp.data_ptr<int>(), te.data_ptr<int>(), cur_stream()), "ep_fused_meta");
   return {rr, rp, te};
 }
@@ -341,6 +342,276 @@ void barrier_wait(int64_t my_flags, int64_t ws, int64_t epoch, Tensor& status, i
 
 int64_t launch_count() {
   return mdt_gemm_launch_count() + mdt_elementwise_launch_count() + mdt_router_launch_count() + mdt_attention_launch_count() + mdt_comm_launch_count();
+}
+
+
+// =====================================================================================================
+// Whole attention sub-block in one call each way (RMSNorm -> q/k/v (+LoRA) -> RoPE -> attention -> o (+LoRA)
+// -> residual).  Same kernels as the per-op bindings; issuing them from C++ keeps the host ahead of the GPU.
+// =====================================================================================================
+namespace {
+
+struct Lin { Tensor W; OptTensor A, B; double s; };   // y = x W^T + s (x A^T) B^T
+
+void gemm_raw(int mode, const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, Tensor& C, int64_t M, int64_t N, int64_t K,
+              const OptTensor& A_l, const OptTensor& B_l, bool b_mn_l, int64_t K_l, bool accumulate, double alpha, const OptTensor& status) {
+  gemm(mode, A, a_mn, B, b_mn, C, M, N, K, 1, std::nullopt, 0, std::nullopt, A_l, false, B_l, std::nullopt, b_mn_l, K_l, std::nullopt,
+       std::nullopt, accumulate, alpha, status, std::nullopt, std::nullopt, std::nullopt, std::nullopt, std::nullopt, std::nullopt);
+}
+// y = x W^T (+ LoRA); returns (y, t) with t = s x A^T
+std::pair<Tensor, OptTensor> lin_fwd(const Tensor& x, const Lin& l, const OptTensor& status) {
+  const int64_t M = x.size(0), K = x.size(1), N = l.W.size(0);
+  auto y = torch::empty({M, N}, x.options());
+  if (!l.A.has_value()) {
+    gemm_raw(0, x, false, l.W, false, y, M, N, K, std::nullopt, std::nullopt, false, 0, false, 1.0, status);
+    return {y, std::nullopt};
+  }
+  const int64_t r = l.A->size(0);
+  auto t = torch::empty({M, r}, x.options());
+  gemm_raw(0, x, false, *l.A, false, t, M, r, K, std::nullopt, std::nullopt, false, 0, false, l.s, status);
+  gemm_raw(0, x, false, l.W, false, y, M, N, K, t, l.B, false, r, false, 1.0, status);
+  return {y, t};
+}
+// dx (+)= dy W (+ LoRA), and the requested parameter gradients
+struct LinGrads { OptTensor dW, dA, dB; };
+LinGrads lin_bwd(const Tensor& dy, const Tensor& xin, const Lin& l, const OptTensor& t, bool need_w, bool need_a, bool need_b,
+                 Tensor& dx, bool accumulate, const OptTensor& status) {
+  const int64_t M = dy.size(0), N = dy.size(1), K = l.W.size(1);
+  LinGrads g;
+  OptTensor dt;
+  if (l.A.has_value()) {
+    const int64_t r = l.A->size(0);
+    dt = torch::empty({M, r}, dy.options());
+    gemm_raw(0, dy, false, *l.B, true, *dt, M, r, N, std::nullopt, std::nullopt, false, 0, false, l.s, status);      // s dy B
+    gemm_raw(0, dy, false, l.W, true, dx, M, K, N, dt, l.A, true, r, accumulate, 1.0, status);                       // dy W + dt A
+    if (need_a) { g.dA = torch::empty_like(*l.A); gemm_raw(2, *dt, true, xin, true, *g.dA, r, K, M, std::nullopt, std::nullopt, false, 0, false, 1.0, status); }
+    if (need_b) { g.dB = torch::empty_like(*l.B); gemm_raw(2, dy, true, *t, true, *g.dB, N, r, M, std::nullopt, std::nullopt, false, 0, false, 1.0, status); }
+  } else {
+    gemm_raw(0, dy, false, l.W, true, dx, M, K, N, std::nullopt, std::nullopt, false, 0, accumulate, 1.0, status);
+  }
+  if (need_w) { g.dW = torch::empty_like(l.W); gemm_raw(2, dy, true, xin, true, *g.dW, N, K, M, std::nullopt, std::nullopt, false, 0, false, 1.0, status); }
+  return g;
+}
+Lin make_lin(const std::vector<Tensor>& p, size_t& i, double s) {
+  Lin l;
+  l.W = p[i++];
+  l.s = s;
+  if (s >= 0.0) { l.A = p[i++]; l.B = p[i++]; }   // negative scaling = no adapter on this projection
+  return l;
+}
+
+}  // namespace
+
+// params: ln_w, then for q, k, v, o: W [, A, B].  scalings[j] < 0: projection j has no adapter.
+// Returns {out, rstd, xn, qr, kr, v3, o, lse, tq, tk, tv, to} (adapter intermediates are empty tensors when absent).
+std::vector<Tensor> attention_block_fwd(const Tensor& x, const std::vector<Tensor>& params, const std::vector<double>& scalings,
+                                        const Tensor& positions, const Tensor& cu_seqlens, int64_t max_seqlen, double eps, double theta,
+                                        int64_t Hq, int64_t Hkv, int64_t d, const Tensor& status_t) {
+  c10::cuda::CUDAGuard guard(x.device());
+  OptTensor status = status_t;
+  const int64_t T = x.size(0);
+  size_t i = 1;
+  Lin lq = make_lin(params, i, scalings[0]), lk = make_lin(params, i, scalings[1]), lv = make_lin(params, i, scalings[2]),
+      lo = make_lin(params, i, scalings[3]);
+  auto nr = rmsnorm_fwd(x, params[0], eps);
+  Tensor xn = nr[0], rstd = nr[1];
+  auto [q, tq] = lin_fwd(xn, lq, status);
+  auto [k, tk] = lin_fwd(xn, lk, status);
+  auto [v, tv] = lin_fwd(xn, lv, status);
+  Tensor qr = rope(q.view({T, Hq, d}), positions, theta, false);
+  Tensor kr = rope(k.view({T, Hkv, d}), positions, theta, false);
+  Tensor v3 = v.view({T, Hkv, d});
+  auto at = attention_fwd(qr, kr, v3, cu_seqlens, max_seqlen, 1.0 / std::sqrt((double)d));
+  Tensor o = at[0], lse = at[1];
+  auto [out, to] = lin_fwd(o.view({T, Hq * d}), lo, status);
+  out.add_(x);
+  Tensor none = torch::empty({0}, x.options());
+  return {out, rstd, xn, qr, kr, v3, o, lse, tq.value_or(none), tk.value_or(none), tv.value_or(none), to.value_or(none)};
+}
+
+// needs[j] for params[j]; returns {dx, grads of params in order (empty tensor where not needed)}
+std::vector<Tensor> attention_block_bwd(const Tensor& dy, const std::vector<Tensor>& saved, const std::vector<Tensor>& params,
+                                        const std::vector<double>& scalings, const std::vector<bool>& needs, const Tensor& positions,
+                                        const Tensor& cu_seqlens, int64_t max_seqlen, double theta, int64_t Hq, int64_t Hkv, int64_t d,
+                                        const Tensor& status_t) {
+  c10::cuda::CUDAGuard guard(dy.device());
+  OptTensor status = status_t;
+  const Tensor &x = saved[0], &rstd = saved[1], &xn = saved[2], &qr = saved[3], &kr = saved[4], &v3 = saved[5], &o = saved[6], &lse = saved[7];
+  auto opt = [](const Tensor& t) -> OptTensor { return t.numel() ? OptTensor(t) : std::nullopt; };
+  OptTensor tq = opt(saved[8]), tk = opt(saved[9]), tv = opt(saved[10]), to = opt(saved[11]);
+  const int64_t T = x.size(0), H = x.size(1);
+  size_t i = 1;
+  const size_t iq = i; Lin lq = make_lin(params, i, scalings[0]);
+  const size_t ik = i; Lin lk = make_lin(params, i, scalings[1]);
+  const size_t iv = i; Lin lv = make_lin(params, i, scalings[2]);
+  const size_t io = i; Lin lo = make_lin(params, i, scalings[3]);
+  Tensor none = torch::empty({0}, x.options());
+  std::vector<Tensor> grads(params.size(), none);
+  auto put = [&](size_t at, const Lin& l, const LinGrads& g) {
+    if (g.dW.has_value()) grads[at] = *g.dW;
+    if (l.A.has_value()) { if (g.dA.has_value()) grads[at + 1] = *g.dA; if (g.dB.has_value()) grads[at + 2] = *g.dB; }
+  };
+  auto nd = [&](size_t at, int k2) { return at + k2 < needs.size() ? (bool)needs[at + k2] : false; };
+  Tensor dyc = dy.contiguous();
+  Tensor o2 = o.view({T, Hq * d});
+  Tensor d_o = torch::empty({T, Hq * d}, x.options());
+  put(io, lo, lin_bwd(dyc, o2, lo, to, nd(io, 0), lo.A.has_value() && nd(io, 1), lo.A.has_value() && nd(io, 2), d_o, false, status));
+  auto g3 = attention_bwd(qr, kr, v3, o, d_o.view({T, Hq, d}), lse, cu_seqlens, max_seqlen, 1.0 / std::sqrt((double)d));
+  Tensor dq = rope(g3[0], positions, theta, true).view({T, Hq * d});
+  Tensor dk = rope(g3[1], positions, theta, true).view({T, Hkv * d});
+  Tensor dv = g3[2].view({T, Hkv * d});
+  Tensor d_xn = torch::empty({T, H}, x.options());
+  put(iq, lq, lin_bwd(dq, xn, lq, tq, nd(iq, 0), lq.A.has_value() && nd(iq, 1), lq.A.has_value() && nd(iq, 2), d_xn, false, status));
+  put(ik, lk, lin_bwd(dk, xn, lk, tk, nd(ik, 0), lk.A.has_value() && nd(ik, 1), lk.A.has_value() && nd(ik, 2), d_xn, true, status));
+  put(iv, lv, lin_bwd(dv, xn, lv, tv, nd(iv, 0), lv.A.has_value() && nd(iv, 1), lv.A.has_value() && nd(iv, 2), d_xn, true, status));
+  auto rb = rmsnorm_bwd(x, params[0], d_xn, rstd);
+  Tensor dx = rb[0];
+  if (needs[0]) grads[0] = rb[1].sum(0).to(params[0].scalar_type());
+  dx.add_(dyc);
+  std::vector<Tensor> out;
+  out.reserve(1 + grads.size());
+  out.push_back(dx);
+  for (auto& g : grads) out.push_back(g);
+  return out;
+}
+
+// =====================================================================================================
+// Whole MoE sub-block (no expert adapters): RMSNorm -> router -> plan -> [peer exchange] -> grouped SwiGLU MLP
+// -> [exchange back] -> gate-weighted combine -> residual.  `ep` carries the exchange state when the experts are
+// expert-parallel: ints = {my_base, rank, count_epoch, count_parity, data_parity, num_col_tiles}, tensors =
+// {peer_base, peer_out, peer_arrive(parity), tile_counters(parity), recv_x, recv_y, identity}.
+// =====================================================================================================
+namespace {
+void ggemm(int mode, const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, Tensor& C, int64_t M, int64_t N, int64_t K, int64_t G,
+           const Tensor& offs, int64_t cap, const OptTensor& B2, const OptTensor& A_l, const OptTensor& B_l, bool b_mn_l, int64_t K_l,
+           const OptTensor& C2, const OptTensor& C3, bool acc, double alpha, const OptTensor& status, const OptTensor& w0, const OptTensor& w1,
+           const OptTensor& s0, const OptTensor& s1, const OptTensor& s2, const OptTensor& s3) {
+  gemm(mode, A, a_mn, B, b_mn, C, M, N, K, G, offs, cap, B2, A_l, false, B_l, std::nullopt, b_mn_l, K_l, C2, C3, acc, alpha, status, w0, w1, s0, s1, s2, s3);
+}
+const OptTensor NONE = std::nullopt;
+}  // namespace
+
+std::vector<Tensor> moe_block_fwd(const Tensor& x, const Tensor& ln_w, const Tensor& Wr, const Tensor& w1, const Tensor& w2, const Tensor& w3,
+                                  double eps, int64_t top_k, int64_t E, bool grad_mode, const std::vector<int64_t>& layout,
+                                  const std::vector<int64_t>& ep_ints, const std::vector<Tensor>& ep, const Tensor& status_t) {
+  c10::cuda::CUDAGuard guard(x.device());
+  OptTensor status = status_t;
+  Tensor st = status_t;
+  const bool is_ep = !ep.empty();
+  const int64_t T = x.size(0), H = x.size(1), El = w1.size(0), F = w1.size(1);
+  auto nr = rmsnorm_fwd(x, ln_w, eps);
+  Tensor xn = nr[0], rstd = nr[1];
+  auto rt = router_fwd(xn, Wr, top_k, true);
+  Tensor wts = rt[1], idx = rt[2];
+  Tensor none = torch::empty({0}, x.options());
+  Tensor nonei = torch::empty({0}, idx.options());
+  Tensor xg, offs, meta_c = nonei, rr = nonei, rp = nonei, te = nonei, expert_sorted = nonei, ys, out;
+  int64_t cap;
+  std::vector<Tensor> plan;
+  OptTensor w0, w1o, s0, s1, s2, s3;
+  const int64_t n_slots = idx.numel();
+  if (!is_ep) {
+    const int64_t c = std::max<int64_t>(128, ((n_slots + E * 127) / 128) * 128);
+    plan = make_plan(idx.view({-1}), E, 128, c);
+    xg = gather_rows(xn, plan[3], plan[1], E, NONE, top_k);
+    offs = plan[1]; cap = c;
+  } else {
+    plan = make_plan(idx.view({-1}), E, 1, n_slots);
+    const int64_t my_base = ep_ints[0], rank = ep_ints[1], epoch = ep_ints[2], cpar = ep_ints[3], dpar = ep_ints[4];
+    MdtEpLayout L = to_layout(layout);
+    meta_c = torch::empty({mdt_ep_meta_size(L.ws, L.num_experts)}, idx.options());
+    ep_counts_send(plan[0], ep[0], layout, rank, cpar, epoch);
+    ep_counts_wait_meta(my_base, layout, rank, cpar, epoch, meta_c, st);
+    auto fm = ep_fused_meta(meta_c, layout, rank);
+    rr = fm[0]; rp = fm[1]; te = fm[2];
+    Tensor eos = idx.view({-1});
+    if (grad_mode) expert_sorted = eos.index_select(0, plan[3].to(at::kLong));
+    ep_dispatch(xn, plan[3], eos, NONE, meta_c, ep[0], layout, top_k, dpar);
+    ep_recv_prepare(my_base, layout, meta_c, H, dpar, st, false);
+    xg = ep[4];
+    const int o2 = mdt_ep_meta_recv_off(L.ws, L.num_experts);
+    offs = meta_c.narrow(0, o2, El + 1);
+    cap = L.capacity_rows;
+    w0 = ep[3]; w1o = te; s0 = rr; s1 = rp; s2 = ep[1]; s3 = ep[2];
+  }
+  const int64_t R = xg.size(0);
+  Tensor h = torch::empty({R, F}, x.options());
+  OptTensor g, u;
+  if (grad_mode) { g = torch::empty({R, F}, x.options()); u = torch::empty({R, F}, x.options()); }
+  ggemm(1, xg, false, w1, false, h, R, F, H, El, offs, cap, w3, NONE, NONE, false, 0, g, u, false, 1.0, status, w0, w1o, NONE, NONE, NONE, NONE);
+  if (is_ep && grad_mode) xg = xg.clone();
+  Tensor y = torch::empty({R, H}, x.options());
+  ggemm(1, h, false, w2, true, y, R, H, F, El, offs, cap, NONE, NONE, NONE, false, 0, NONE, NONE, false, 1.0, status, NONE, NONE, s0, s1, s2, s3);
+  if (!is_ep) {
+    ys = y;
+  } else {
+    ep_wait_rows(ep_ints[0], layout, meta_c, ep_ints[4], st, ep_ints[5]);
+    ys = ep[5].narrow(0, 0, n_slots);
+    if (grad_mode) ys = ys.clone();
+  }
+  out = combine_rows(ys, plan[2], wts, top_k);
+  out.add_(x);
+  if (!grad_mode) return {out, plan[0]};
+  return {out, plan[0], rstd, xn, wts, idx, ys, plan[1], plan[2], plan[3], meta_c, rr, rp, te, xg, *g, *u, h, expert_sorted, offs};
+}
+
+// state = the forward's return list; wg = {dw1, dw2, dw3} accumulation buffers ([El,F,H]) or empty when the experts are frozen.
+// Returns {dx, d_ln, d_Wr}.
+std::vector<Tensor> moe_block_bwd(const Tensor& dy, const std::vector<Tensor>& state, const Tensor& x, const Tensor& ln_w, const Tensor& Wr,
+                                  const Tensor& w1, const Tensor& w2, const Tensor& w3, const std::vector<Tensor>& wg, double wscale,
+                                  int64_t top_k, int64_t E, const std::vector<int64_t>& layout, const std::vector<int64_t>& ep_ints,
+                                  const std::vector<Tensor>& ep, const Tensor& status_t) {
+  c10::cuda::CUDAGuard guard(dy.device());
+  OptTensor status = status_t;
+  Tensor st = status_t;
+  const bool is_ep = !ep.empty();
+  const Tensor &rstd = state[2], &xn = state[3], &wts = state[4], &idx = state[5], &ys = state[6], &p_offs = state[7], &dest_row = state[8],
+               &src_slot = state[9], &meta_c = state[10], &rr = state[11], &rp = state[12], &te = state[13], &xg = state[14], &g = state[15],
+               &u = state[16], &h = state[17], &expert_sorted = state[18], &offs = state[19];
+  const int64_t H = x.size(1), El = w1.size(0), F = w1.size(1);
+  Tensor dyc = dy.contiguous();
+  Tensor d_rows = gather_rows(dyc, src_slot, p_offs, E, wts.view({-1}), top_k);
+  Tensor dwts = combine_wgrad(ys, dest_row, dyc, top_k);
+  Tensor dyg;
+  int64_t cap;
+  OptTensor w0, w1o, s0, s1, s2, s3;
+  const int64_t n_slots = dest_row.numel();
+  if (!is_ep) {
+    dyg = d_rows; cap = src_slot.numel();
+  } else {
+    const int64_t my_base = ep_ints[0], dpar = ep_ints[4];
+    MdtEpLayout L = to_layout(layout);
+    ep_dispatch(d_rows, ep[6].narrow(0, 0, n_slots), expert_sorted, NONE, meta_c, ep[0], layout, 1, dpar);
+    ep_recv_prepare(my_base, layout, meta_c, H, dpar, st, false);
+    dyg = ep[4]; cap = L.capacity_rows;
+    w0 = ep[3]; w1o = te; s0 = rr; s1 = rp; s2 = ep[1]; s3 = ep[2];
+  }
+  const int64_t R = dyg.size(0);
+  Tensor dh = torch::empty({R, F}, x.options());
+  ggemm(1, dyg, false, w2, false, dh, R, F, H, El, offs, cap, NONE, NONE, NONE, false, 0, NONE, NONE, false, 1.0, status, w0, w1o, NONE, NONE, NONE, NONE);
+  if (!wg.empty()) { Tensor c = wg[1]; ggemm(2, h, true, dyg, true, c, F, H, 0, El, offs, cap, NONE, NONE, NONE, false, 0, NONE, NONE, true, wscale, status, NONE, NONE, NONE, NONE, NONE, NONE); }
+  auto gu = swiglu_bwd(g, u, dh);
+  Tensor dxg = torch::empty({R, H}, x.options());
+  ggemm(1, gu[0], false, w1, true, dxg, R, H, F, El, offs, cap, NONE, gu[1], w3, true, F, NONE, NONE, false, 1.0, status, NONE, NONE, s0, s1, s2, s3);
+  if (!wg.empty()) {
+    Tensor c1 = wg[0], c3 = wg[2];
+    ggemm(2, gu[0], true, xg, true, c1, F, H, 0, El, offs, cap, NONE, NONE, NONE, false, 0, NONE, NONE, true, wscale, status, NONE, NONE, NONE, NONE, NONE, NONE);
+    ggemm(2, gu[1], true, xg, true, c3, F, H, 0, El, offs, cap, NONE, NONE, NONE, false, 0, NONE, NONE, true, wscale, status, NONE, NONE, NONE, NONE, NONE, NONE);
+  }
+  Tensor back;
+  if (!is_ep) {
+    back = dxg;
+  } else {
+    ep_wait_rows(ep_ints[0], layout, meta_c, ep_ints[4], st, ep_ints[5]);
+    back = ep[5].narrow(0, 0, n_slots);
+  }
+  Tensor dxn = combine_rows(back, dest_row, NONE, top_k);
+  auto rb = router_bwd(xn, Wr, idx, dwts, NONE, true);
+  dxn.add_(rb[0]);
+  auto nb = rmsnorm_bwd(x, ln_w, dxn, rstd);
+  Tensor dx = nb[0];
+  dx.add_(dyc);
+  return {dx, nb[1].sum(0).to(ln_w.scalar_type()), rb[1].to(Wr.scalar_type())};
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -376,5 +647,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rs_pull", &rs_pull);
   m.def("barrier_arrive", &barrier_arrive);
   m.def("barrier_wait", &barrier_wait);
+  m.def("attention_block_fwd", &attention_block_fwd);
+  m.def("attention_block_bwd", &attention_block_bwd);
+  m.def("moe_block_fwd", &moe_block_fwd);
+  m.def("moe_block_bwd", &moe_block_bwd);
   m.def("launch_count", &launch_count);
 }

@@ -65,7 +65,10 @@ class SparseMLPv2(nn.Module):
         """(w1, w2, w3 views, LoRA dict, weight-gradient scale, direct-accumulation buffers) for one call."""
         w1, w2, w3 = self.weight_views()
         wgrad_out = None
-        if xg.is_cuda and ops.get_backend() == "native" and torch.is_grad_enabled() and self.w1.requires_grad:
+        # (only for weights this module owns: when the experts are sharded like dense parameters the
+        #  attributes are views of a gathered buffer and their gradients go through the flat reduction)
+        if (xg.is_cuda and ops.get_backend() == "native" and torch.is_grad_enabled() and self.w1.requires_grad
+                and isinstance(self.w1, nn.Parameter)):
             E, Fr, H = self.experts_per_rank, self.features_per_rank, self.args.hidden_size
             for w in (self.w1, self.w2, self.w3):
                 if w.grad is None:
@@ -75,15 +78,5 @@ class SparseMLPv2(nn.Module):
 
     def forward(self, xg: torch.Tensor, plan) -> torch.Tensor:
         """xg: block-padded expert-grouped rows [R, hidden]; returns rows of the same layout."""
-        w1, w2, w3 = self.weight_views()
-        wgrad_out = None
-        if xg.is_cuda and ops.get_backend() == "native" and torch.is_grad_enabled() and self.w1.requires_grad:
-            # the weight-gradient GEMMs add straight into .grad (scaled), so no per-micro-batch
-            # gradient tensors of the size of the expert weights are created
-            E, Fr, H = self.experts_per_rank, self.features_per_rank, self.args.hidden_size
-            for w in (self.w1, self.w2, self.w3):
-                if w.grad is None:
-                    w.grad = torch.zeros_like(w)
-            wgrad_out = tuple(w.grad.view(E, Fr, H) for w in (self.w1, self.w2, self.w3))
-        return ops.grouped_swiglu_mlp(xg, w1, w2, w3, plan, self.lora_views(),
-                                      wgrad_scale=self.gradient_scale or 1.0, wgrad_out=wgrad_out)
+        w1, w2, w3, lora, scale, wgrad_out = self.call_args(xg)
+        return ops.grouped_swiglu_mlp(xg, w1, w2, w3, plan, lora, wgrad_scale=scale, wgrad_out=wgrad_out)

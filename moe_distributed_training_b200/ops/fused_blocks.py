@@ -35,6 +35,35 @@ def _lin_bwd(dy2, xin, W, A, B, s, t, need_w, need_a, need_b, dx_out=None, accum
     return dx, dW, dA, dB
 
 
+class _AttentionBlockNative(torch.autograd.Function):
+    """Same sub-block with the kernel sequence issued from C++ (one binding call per direction)."""
+
+    @staticmethod
+    def forward(ctx, x, meta, *params):
+        eps, theta, Hq, Hkv, d, positions, cu, max_seqlen, scalings = meta
+        sc = [-1.0 if s is None else float(s) for s in scalings]
+        res = ext.attention_block_fwd(x.contiguous(), list(params), sc, positions, cu, max_seqlen, eps, theta, Hq, Hkv, d,
+                                      C.status_tensor(x.device))
+        if any(ctx.needs_input_grad):
+            ctx.meta, ctx.sc, ctx.n_params = meta, sc, len(params)
+            ctx.save_for_backward(x, *res[1:], *params)
+        return res[0]
+
+    @staticmethod
+    def backward(ctx, dy):
+        eps, theta, Hq, Hkv, d, positions, cu, max_seqlen, scalings = ctx.meta
+        saved = ctx.saved_tensors
+        state, params = list(saved[:12]), list(saved[12:])
+        needs = [bool(n) for n in ctx.needs_input_grad[2:]]
+        res = ext.attention_block_bwd(dy, state, params, ctx.sc, needs, positions, cu, max_seqlen, theta, Hq, Hkv, d,
+                                      C.status_tensor(dy.device))
+        grads = tuple(g if (g.numel() and need) else None for g, need in zip(res[1:], needs))
+        return (res[0], None) + grads
+
+
+NATIVE_ISSUE = os.environ.get("MDT_NATIVE_BLOCKS", "1") != "0"
+
+
 class _AttentionBlock(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, meta, *params):
@@ -122,7 +151,7 @@ def attention_block(layer, x, batch):
             scalings.append(None)
     meta = (layer.input_layernorm.eps, float(attn.cfg.rope_theta), attn.num_heads, attn.num_kv_heads, attn.head_dim,
             batch.positions, batch.cu_seqlens, int(batch.max_seqlen), tuple(scalings))
-    return _AttentionBlock.apply(x, meta, *params)
+    return (_AttentionBlockNative if NATIVE_ISSUE else _AttentionBlock).apply(x, meta, *params)
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -267,6 +296,71 @@ class _MoEBlock(torch.autograd.Function):
         return (dx, None) + tuple(grads)
 
 
+class _MoEBlockNative(torch.autograd.Function):
+    """MoE sub-block without expert adapters, kernel sequence issued from C++ (local or fused expert-parallel)."""
+
+    @staticmethod
+    def _ep_args(eng, parity, H):
+        w = eng.wspace
+        eng.gemm_scatter(parity, None, None)      # makes sure the address tables exist
+        ints = [w.my_base, w.rank, eng.count_epoch, eng.count_epoch & 1, parity, (H + 255) // 256 if H > 128 else 1]
+        tens = [w.peer_base, eng._peer_out, eng._peer_arrive[parity], w.tile_counters(parity), w.recv_x(), w.recv_y(),
+                eng.identity(w.capacity_slots)]
+        return w.layout, ints, tens
+
+    @staticmethod
+    def forward(ctx, x, layer, *params):
+        moe = layer.block_sparse_moe
+        ex, mlp, a = moe.experts, moe.experts.mlp, moe.args
+        ln_w, Wr = params[0], params[1]
+        x2 = x.contiguous()
+        grad_mode = any(ctx.needs_input_grad)
+        with torch.set_grad_enabled(grad_mode):
+            w1, w2, w3, _, ws, wgrad_out = mlp.call_args(x2)
+        eng, layout, ints, tens = None, [], [], []
+        if ex.ep_group is not None and ex.ep_size > 1:
+            if ex._fused is None:
+                from ..parallel.fused_ep import FusedExpertParallel
+                ex._fused = FusedExpertParallel.for_group(ex.ep_group, a, x2.device)
+            eng = ex._fused
+            assert x2.shape[0] * a.moe_top_k <= eng.wspace.capacity_slots, "more (token, choice) slots than the workspace was sized for"
+            eng.count_epoch += 1
+            layout, ints, tens = _MoEBlockNative._ep_args(eng, eng.next_phase(), x2.shape[1])
+        res = ext.moe_block_fwd(x2, ln_w, Wr.contiguous(), w1, w2, w3, layer.post_attention_layernorm.eps, a.moe_top_k,
+                                a.moe_num_experts, grad_mode, layout, ints, tens, C.status_tensor(x2.device))
+        ex.last_tokens_per_expert = res[1]
+        if grad_mode:
+            ctx.layer, ctx.eng, ctx.ws, ctx.wgrad_out = layer, eng, float(ws), wgrad_out
+            ctx.views = (w1, w2, w3)
+            ctx.save_for_backward(x2, ln_w, Wr, *res)
+        return res[0]
+
+    @staticmethod
+    def backward(ctx, dy):
+        layer, eng = ctx.layer, ctx.eng
+        a = layer.block_sparse_moe.args
+        saved = ctx.saved_tensors
+        x2, ln_w, Wr, state = saved[0], saved[1], saved[2], list(saved[3:])
+        w1, w2, w3 = ctx.views
+        layout, ints, tens = [], [], []
+        if eng is not None:
+            layout, ints, tens = _MoEBlockNative._ep_args(eng, eng.next_phase(), x2.shape[1])
+        wg = list(ctx.wgrad_out) if ctx.wgrad_out is not None else []
+        dx, dln, dWr = ext.moe_block_bwd(dy, state, x2, ln_w, Wr.contiguous(), w1, w2, w3, wg, ctx.ws, a.moe_top_k, a.moe_num_experts,
+                                         layout, ints, tens, C.status_tensor(dy.device))
+        need = ctx.needs_input_grad
+        return dx, None, (dln if need[2] else None), (dWr if need[3] else None), None, None, None
+
+
+def _native_moe_ok(layer) -> bool:
+    """No expert adapters, and expert weights either frozen or owned by the module (direct gradient accumulation)."""
+    ex = layer.block_sparse_moe.experts
+    if getattr(ex, "lora", None) is not None:
+        return False
+    w = ex.mlp.w1
+    return (not w.requires_grad) or isinstance(w, torch.nn.Parameter)
+
+
 def moe_block(layer, x):
     """x + block_sparse_moe(post_attention_layernorm(x)) as one autograd node (local or fused-EP experts)."""
     moe = layer.block_sparse_moe
@@ -277,4 +371,6 @@ def moe_block(layer, x):
         for name in ("w1", "w2", "w3"):
             if name in lora.lora_A:
                 params += [lora.lora_A[name], lora.lora_B[name]]
+    if NATIVE_ISSUE and GEMM_FUSION and _native_moe_ok(layer):
+        return _MoEBlockNative.apply(x, layer, *params[:5])
     return _MoEBlock.apply(x, layer, *params)

@@ -161,6 +161,7 @@ class FusedExpertParallel:
                                  for par in (0, 1)]
         return (row_rank, row_pos, self._peer_out, self._peer_arrive[parity])
 
+
     def recv_plan(self, meta) -> RoutingPlan:
         w = self.wspace
         El = w.num_experts // w.ws

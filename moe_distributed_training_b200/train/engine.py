@@ -72,6 +72,7 @@ class Engine:
     shard_group: object = None
     ep_group: object = None
     max_grad_norm: Optional[float] = None
+    sort_microbatches: bool = True
     step_count: int = 0
     last: dict = field(default_factory=dict)
 
@@ -91,6 +92,11 @@ class Engine:
 
     def train_step(self, microbatches: List[dict]) -> dict:
         ga = len(microbatches)
+        if self.world_size > 1 and self.sort_microbatches:
+            # Expert-parallel ranks meet at every MoE layer, so a micro-batch costs every rank the time of the
+            # longest sequence among them.  Gradient accumulation does not depend on the order, so each rank runs
+            # its micro-batches longest first: ranks then work on sequences of similar length at the same time.
+            microbatches = sorted(microbatches, key=lambda mb: -int(mb["input_ids"].numel()))
         loss_sum = None
         for mb in microbatches:
             l = self.forward_backward(mb, 1.0 / ga)
@@ -185,6 +191,10 @@ def build_engine(cfg: MixtralConfig, *, dtype: torch.dtype = torch.bfloat16, dev
                 ep_group = shard_group
             else:
                 shard_experts = True  # no expert parallelism: experts are sharded like everything else
+    if shard_experts and targets is None and not sync_each_batch:
+        # full fine-tuning with the experts sharded like everything else: a full-size local gradient
+        # accumulator would be 4 bytes x 46.7 G parameters, so gradients are reduce-scattered every micro-batch
+        sync_each_batch = True
     runner = ShardedMixtral(model, shard_group, replicate_group, expert_dp_group, world_group,
                             shard_experts=shard_experts, sync_each_batch=sync_each_batch)
     params = [p for p in model.parameters() if p.requires_grad]

@@ -26,8 +26,16 @@ def main():
     mbs = [collate_packed([ex]) for ex in ds.examples]
     result = {}
     for impl in ("nccl", "fused"):
-        eng = build_engine(cfg, dtype=torch.bfloat16, device_type="cuda", ep_size=world, use_lora=use_lora, learning_rate=1e-3,
-                           seed=0, dispatch_impl=impl, ep_max_tokens=512, lr_scheduler_type="constant")
+        if mode.startswith("fsdp"):
+            # no expert parallelism: everything, experts included, is sharded; compare NCCL collectives with the
+            # peer-memory all-gather / reduce-scatter kernels
+            os.environ["MDT_PEER_COLLECTIVES"] = "0" if impl == "nccl" else "1"
+            eng = build_engine(cfg, dtype=torch.bfloat16, device_type="cuda", ep_size=1, use_lora="attn-only" if mode == "fsdp-lora" else "none",
+                               learning_rate=1e-3, seed=0, lr_scheduler_type="constant")
+        else:
+            os.environ["MDT_PEER_COLLECTIVES"] = "0" if impl == "nccl" else "1"
+            eng = build_engine(cfg, dtype=torch.bfloat16, device_type="cuda", ep_size=world, use_lora=use_lora, learning_rate=1e-3,
+                               seed=0, dispatch_impl=impl, ep_max_tokens=512, lr_scheduler_type="constant")
         losses = [float(eng.train_step(mbs[2 * s:2 * s + 2])["loss"]) for s in range(3)]
         from moe_distributed_training_b200.ops import cuda_ops
         cuda_ops.check_status(eng.device)

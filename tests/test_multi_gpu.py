@@ -22,13 +22,13 @@ def _run(n, mode, tmp_path, port):
     return json.load(open(out))
 
 
-@pytest.mark.parametrize("mode", ["full", "lora"])
+@pytest.mark.parametrize("mode", ["full", "lora", "fsdp", "fsdp-lora"])
 def test_fused_exchange_matches_nccl_exchange(tmp_path, mode):
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least two GPUs")
     n = 4 if n >= 4 else 2
-    res = _run(n, mode, tmp_path, 29610 + (mode == "lora"))
+    res = _run(n, mode, tmp_path, 29610 + ["full", "lora", "fsdp", "fsdp-lora"].index(mode))
     for rank_res in res:
         a, b = rank_res["nccl"], rank_res["fused"]
         for la, lb in zip(a["losses"], b["losses"]):
