@@ -23,6 +23,8 @@
 #include <stdio.h>
 
 #include <map>
+#include <unordered_map>
+#include <string.h>
 #include <mutex>
 #include <tuple>
 
@@ -378,8 +380,36 @@ static EncodeTiledFn encode_fn() {
 }
 
 // bf16 tensor [d2][d1][d0] (d0 contiguous), strides in elements; box = {b0, b1, 1}
+// Encoded maps are cached per host thread: a training step re-uses the same (pointer, shape, box) combinations
+// (weights, pooled gather buffers, allocator-recycled activations) thousands of times.
+struct MapKey {
+  uint64_t v[8];
+  bool operator==(const MapKey& o) const { return memcmp(v, o.v, sizeof(v)) == 0; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = 1469598103934665603ull;
+    for (int i = 0; i < 8; ++i) { h ^= k.v[i]; h *= 1099511628211ull; }
+    return (size_t)h;
+  }
+};
+static int make_map_uncached(CUtensorMap* m, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1, uint64_t s2,
+                             uint32_t b0, uint32_t b1, int rank);
 static int make_map(CUtensorMap* m, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1, uint64_t s2,
                     uint32_t b0, uint32_t b1, int rank) {
+  static thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey k{{(uint64_t)reinterpret_cast<uintptr_t>(ptr), d0, d1, d2, s1, s2, ((uint64_t)b0 << 32) | b1, (uint64_t)rank}};
+  auto it = cache.find(k);
+  if (it != cache.end()) { *m = it->second; return 0; }
+  int rc = make_map_uncached(m, ptr, d0, d1, d2, s1, s2, b0, b1, rank);
+  if (rc == 0) {
+    if (cache.size() > 65536) cache.clear();
+    cache.emplace(k, *m);
+  }
+  return rc;
+}
+static int make_map_uncached(CUtensorMap* m, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1, uint64_t s2,
+                             uint32_t b0, uint32_t b1, int rank) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return -1;
   cuuint64_t dims[3] = {d0, d1, d2};

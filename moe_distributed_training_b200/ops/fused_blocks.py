@@ -290,7 +290,8 @@ class _MoEBlock(torch.autograd.Function):
             grads[0] = dwp.sum(0).to(ln_w.dtype)
         if need[3]:
             grads[1] = dWr.to(Wr.dtype)
-        grads[2], grads[3], grads[4] = g[1], g[2], g[3]
+        # the MLP works on [E, F, H] views of the [E*F, H] parameters
+        grads[2], grads[3], grads[4] = (t.reshape(-1, t.shape[-1]) if t is not None else None for t in (g[1], g[2], g[3]))
         for i, gl in enumerate(g[9:]):
             grads[5 + i] = gl
         return (dx, None) + tuple(grads)
