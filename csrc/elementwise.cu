@@ -247,55 +247,100 @@ template <typename T> __device__ __forceinline__ void stf(T* p, long long i, flo
 template <> __device__ __forceinline__ void stf<float>(float* p, long long i, float v) { p[i] = v; }
 template <> __device__ __forceinline__ void stf<bf16>(bf16* p, long long i, float v) { p[i] = __float2bfloat16(v); }
 
-__global__ void adamw_kernel(const MdtAdamTensor* __restrict__ tensors, float lr, float b1, float b2, float eps, float wd,
-                             float bc1, float bc2, float gscale) {
+__device__ __forceinline__ void adam_update(float& p, float g, float& m, float& v, float lr, float b1, float b2, float eps,
+                                            float wd, float bc1, float bc2, float gscale) {
+  const float gg = g * gscale;
+  m = b1 * m + (1.f - b1) * gg;
+  v = b2 * v + (1.f - b2) * gg * gg;
+  const float denom = sqrtf(v / bc2) + eps;
+  p = p * (1.f - lr * wd) - lr * (m / bc1) / denom;
+}
+__device__ __forceinline__ bool aligned16(const void* a, const void* b, const void* c, const void* d) {
+  return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) |
+           reinterpret_cast<uintptr_t>(d)) & 15) == 0;
+}
+
+// One launch for all tensors (blockIdx.y = tensor).  All-bf16, 16-byte aligned tensors go eight elements
+// per thread through 128-bit loads, two vectors in flight; everything else, and the tail, element by element.
+__global__ void __launch_bounds__(256, 2) adamw_kernel(const MdtAdamTensor* __restrict__ tensors, float lr, float b1, float b2,
+                                                    float eps, float wd, float bc1, float bc2, float gscale) {
   const MdtAdamTensor t = tensors[blockIdx.y];
-  const long long stride = (long long)gridDim.x * blockDim.x * 8;
-  for (long long base = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; base < t.n; base += stride) {
-    const int cnt = (t.n - base) < 8 ? (int)(t.n - base) : 8;
-    float p[8], g[8], m[8], v[8];
-    const bool vec = cnt == 8 && !t.p_fp32 && !t.g_fp32 && !t.s_fp32;
-    if (vec) {
-      unpack8(*reinterpret_cast<const uint4*>((const bf16*)t.p + base), p);
-      unpack8(*reinterpret_cast<const uint4*>((const bf16*)t.g + base), g);
-      unpack8(*reinterpret_cast<const uint4*>((const bf16*)t.m + base), m);
-      unpack8(*reinterpret_cast<const uint4*>((const bf16*)t.v + base), v);
-    } else {
-      for (int j = 0; j < cnt; ++j) {
-        p[j] = t.p_fp32 ? ldf((const float*)t.p, base + j) : ldf((const bf16*)t.p, base + j);
-        g[j] = t.g_fp32 ? ldf((const float*)t.g, base + j) : ldf((const bf16*)t.g, base + j);
-        m[j] = t.s_fp32 ? ldf((const float*)t.m, base + j) : ldf((const bf16*)t.m, base + j);
-        v[j] = t.s_fp32 ? ldf((const float*)t.v, base + j) : ldf((const bf16*)t.v, base + j);
-      }
-    }
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  long long done = 0;
+  if (!t.p_fp32 && !t.g_fp32 && !t.s_fp32 && aligned16(t.p, t.g, t.m, t.v)) {
+    const long long nv = t.n / 8;
+    uint4* __restrict__ pp = reinterpret_cast<uint4*>(t.p);
+    const uint4* __restrict__ gp = reinterpret_cast<const uint4*>(t.g);
+    uint4* __restrict__ mp = reinterpret_cast<uint4*>(t.m);
+    uint4* __restrict__ vp = reinterpret_cast<uint4*>(t.v);
+    for (long long i = tid; i < nv; i += 2 * nthreads) {
+      const long long i2 = i + nthreads;
+      const bool two = i2 < nv;
+      uint4 P0 = pp[i], G0 = __ldcs(gp + i), M0 = mp[i], V0 = vp[i];
+      uint4 P1 = P0, G1 = G0, M1 = M0, V1 = V0;
+      if (two) { P1 = pp[i2]; G1 = __ldcs(gp + i2); M1 = mp[i2]; V1 = vp[i2]; }
+      bf162* ph = reinterpret_cast<bf162*>(&P0); const bf162* gh = reinterpret_cast<const bf162*>(&G0);
+      bf162* mh = reinterpret_cast<bf162*>(&M0); bf162* vh = reinterpret_cast<bf162*>(&V0);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (j < cnt) {
-        const float gg = g[j] * gscale;
-        m[j] = b1 * m[j] + (1.f - b1) * gg;
-        v[j] = b2 * v[j] + (1.f - b2) * gg * gg;
-        const float denom = sqrtf(v[j] / bc2) + eps;
-        p[j] = p[j] * (1.f - lr * wd) - lr * (m[j] / bc1) / denom;
+      for (int j = 0; j < 4; ++j) {
+        float2 p = __bfloat1622float2(ph[j]), g = __bfloat1622float2(gh[j]), m = __bfloat1622float2(mh[j]), v = __bfloat1622float2(vh[j]);
+        adam_update(p.x, g.x, m.x, v.x, lr, b1, b2, eps, wd, bc1, bc2, gscale);
+        adam_update(p.y, g.y, m.y, v.y, lr, b1, b2, eps, wd, bc1, bc2, gscale);
+        ph[j] = __floats2bfloat162_rn(p.x, p.y); mh[j] = __floats2bfloat162_rn(m.x, m.y); vh[j] = __floats2bfloat162_rn(v.x, v.y);
+      }
+      pp[i] = P0; mp[i] = M0; vp[i] = V0;
+      if (two) {
+        ph = reinterpret_cast<bf162*>(&P1); gh = reinterpret_cast<const bf162*>(&G1);
+        mh = reinterpret_cast<bf162*>(&M1); vh = reinterpret_cast<bf162*>(&V1);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 p = __bfloat1622float2(ph[j]), g = __bfloat1622float2(gh[j]), m = __bfloat1622float2(mh[j]), v = __bfloat1622float2(vh[j]);
+          adam_update(p.x, g.x, m.x, v.x, lr, b1, b2, eps, wd, bc1, bc2, gscale);
+          adam_update(p.y, g.y, m.y, v.y, lr, b1, b2, eps, wd, bc1, bc2, gscale);
+          ph[j] = __floats2bfloat162_rn(p.x, p.y); mh[j] = __floats2bfloat162_rn(m.x, m.y); vh[j] = __floats2bfloat162_rn(v.x, v.y);
+        }
+        pp[i2] = P1; mp[i2] = M1; vp[i2] = V1;
       }
     }
-    if (vec) {
-      *reinterpret_cast<uint4*>((bf16*)t.p + base) = pack8(p);
-      *reinterpret_cast<uint4*>((bf16*)t.m + base) = pack8(m);
-      *reinterpret_cast<uint4*>((bf16*)t.v + base) = pack8(v);
-    } else {
-      for (int j = 0; j < cnt; ++j) {
-        if (t.p_fp32) stf((float*)t.p, base + j, p[j]); else stf((bf16*)t.p, base + j, p[j]);
-        if (t.s_fp32) { stf((float*)t.m, base + j, m[j]); stf((float*)t.v, base + j, v[j]); }
-        else { stf((bf16*)t.m, base + j, m[j]); stf((bf16*)t.v, base + j, v[j]); }
-      }
-    }
+    done = nv * 8;
+  }
+  for (long long i = done + tid; i < t.n; i += nthreads) {
+    float p = t.p_fp32 ? ldf((const float*)t.p, i) : ldf((const bf16*)t.p, i);
+    const float g = t.g_fp32 ? ldf((const float*)t.g, i) : ldf((const bf16*)t.g, i);
+    float m = t.s_fp32 ? ldf((const float*)t.m, i) : ldf((const bf16*)t.m, i);
+    float v = t.s_fp32 ? ldf((const float*)t.v, i) : ldf((const bf16*)t.v, i);
+    adam_update(p, g, m, v, lr, b1, b2, eps, wd, bc1, bc2, gscale);
+    if (t.p_fp32) stf((float*)t.p, i, p); else stf((bf16*)t.p, i, p);
+    if (t.s_fp32) { stf((float*)t.m, i, m); stf((float*)t.v, i, v); }
+    else { stf((bf16*)t.m, i, m); stf((bf16*)t.v, i, v); }
   }
 }
 
-__global__ void sumsq_kernel(const void* __restrict__ x, long long n, int fp32, float* __restrict__ out) {
+__global__ void __launch_bounds__(256) sumsq_kernel(const void* __restrict__ x, long long n, int fp32, float* __restrict__ out) {
   __shared__ float red[32];
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
   float s = 0.f;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+  long long done = 0;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    const uint4* __restrict__ xv = reinterpret_cast<const uint4*>(x);
+    const int per = fp32 ? 4 : 8;
+    const long long nv = n / per;
+    for (long long i = tid; i < nv; i += nthreads) {
+      const uint4 u = xv[i];
+      if (fp32) {
+        const float4 f = *reinterpret_cast<const float4*>(&u);
+        s += f.x * f.x + f.y * f.y + f.z * f.z + f.w * f.w;
+      } else {
+        const bf162* h = reinterpret_cast<const bf162*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); s += f.x * f.x + f.y * f.y; }
+      }
+    }
+    done = nv * per;
+  }
+  for (long long i = done + tid; i < n; i += nthreads) {
     const float v = fp32 ? ((const float*)x)[i] : __bfloat162float(((const bf16*)x)[i]);
     s += v * v;
   }
@@ -304,8 +349,29 @@ __global__ void sumsq_kernel(const void* __restrict__ x, long long n, int fp32, 
 }
 
 // y = a*y + b*x
-__global__ void axpby_kernel(void* __restrict__ y, const void* __restrict__ x, long long n, float a, float b, int y_fp32, int x_fp32) {
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+__global__ void __launch_bounds__(256) axpby_kernel(void* __restrict__ y, const void* __restrict__ x, long long n, float a, float b,
+                                                    int y_fp32, int x_fp32) {
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  long long done = 0;
+  if (!y_fp32 && !x_fp32 && ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(x)) & 15) == 0) {
+    const long long nv = n / 8;
+    uint4* __restrict__ yv = reinterpret_cast<uint4*>(y);
+    const uint4* __restrict__ xv = reinterpret_cast<const uint4*>(x);
+    for (long long i = tid; i < nv; i += nthreads) {
+      const uint4 X = xv[i];
+      uint4 Y = a == 0.f ? make_uint4(0, 0, 0, 0) : yv[i];
+      bf162* yh = reinterpret_cast<bf162*>(&Y); const bf162* xh = reinterpret_cast<const bf162*>(&X);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 yf = __bfloat1622float2(yh[j]), xf = __bfloat1622float2(xh[j]);
+        yh[j] = __floats2bfloat162_rn(a * yf.x + b * xf.x, a * yf.y + b * xf.y);
+      }
+      yv[i] = Y;
+    }
+    done = nv * 8;
+  }
+  for (long long i = done + tid; i < n; i += nthreads) {
     const float xv = x_fp32 ? ((const float*)x)[i] : __bfloat162float(((const bf16*)x)[i]);
     const float yv = a == 0.f ? 0.f : a * (y_fp32 ? ((float*)y)[i] : __bfloat162float(((bf16*)y)[i]));
     const float r = yv + b * xv;
@@ -392,7 +458,7 @@ extern "C" int mdt_cross_entropy(void* logits, const long long* labels, float* l
 extern "C" int mdt_adamw(const MdtAdamTensor* tensors_device, int num_tensors, long long max_n, float lr, float beta1, float beta2,
                          float eps, float weight_decay, float bc1, float bc2, float grad_scale, cudaStream_t s) {
   if (num_tensors == 0) return 0;
-  dim3 grid(grid_for((max_n + 7) / 8, 256, 148 * 8), num_tensors);
+  dim3 grid(grid_for((max_n + 15) / 16, 256, 148 * 8), num_tensors);
   adamw_kernel<<<grid, 256, 0, s>>>(tensors_device, lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale);
   MDT_CHECK_LAUNCH();
   return 0;

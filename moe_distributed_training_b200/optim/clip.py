@@ -19,16 +19,18 @@ def global_grad_norm(model, shard_group=None, ep_group=None) -> torch.Tensor:
     dev = next(model.parameters()).device
     sq = torch.zeros(3, dtype=torch.float32, device=dev)  # dense shards, experts, replicated
     flat_ids = {id(p) for p in getattr(model, "_flat_shards", [])}
+    from .. import ops
+    native = dev.type == "cuda" and ops.get_backend() == "native"
     for p in model.parameters():
         if p.grad is None:
             continue
-        n2 = p.grad.float().pow(2).sum()
-        if id(p) in flat_ids:
-            sq[0] += n2
-        elif getattr(p, "_is_expert_param", False):
-            sq[1] += n2
+        slot = 0 if id(p) in flat_ids else (1 if getattr(p, "_is_expert_param", False) else 2)
+        g = p.grad
+        if native and g.is_contiguous() and g.dtype in (torch.bfloat16, torch.float32):
+            # one vectorised pass that adds the sum of squares into the slot; no fp32 copy of the gradient
+            ops._cuda().ext.sumsq(g, sq[slot:slot + 1])
         else:
-            sq[2] += n2
+            sq[slot] += g.float().pow(2).sum()
     if coll.group_size(shard_group) > 1:
         t = sq[0:1].clone(); dist.all_reduce(t, group=shard_group); sq[0] = t[0]
     if coll.group_size(ep_group) > 1:

@@ -268,6 +268,40 @@ def test_adamw(ops):
         _close(p, pr, 1e-2, "adamw param")
 
 
+def test_adamw_tails_and_fp32_states(ops):
+    """Sizes that are not multiples of 8, misaligned views and fp32 moments take the element-wise path."""
+    from moe_distributed_training_b200.ops import reference
+    torch.manual_seed(12)
+    base = _rand(8 * 1024 + 13)
+    edge = base.clone()
+    ps = [base[3:8 * 1024 + 5], _rand(100003), _rand(77)]
+    gs = [_rand(p.numel(), scale=0.1) for p in ps]
+    ms = [torch.zeros(p.numel(), device=DEV, dtype=torch.float32 if i == 1 else torch.bfloat16) for i, p in enumerate(ps)]
+    vs = [torch.zeros_like(m) for m in ms]
+    ref = [[t.clone().float() for t in group] for group in (ps, gs, ms, vs)]
+    for step in (1, 2):
+        ops.adamw_multi(ps, gs, ms, vs, 1e-2, 0.9, 0.999, 1e-8, 0.01, step, 1.0)
+        for p, g, m, v in zip(*ref):
+            reference.adamw_step(p, g, m, v, 1e-2, 0.9, 0.999, 1e-8, 0.01, step, 1.0)
+    for p, pr in zip(ps, ref[0]):
+        _close(p, pr, 1e-2, "adamw param (tail)")
+    assert torch.equal(base[:3], edge[:3]) and torch.equal(base[8 * 1024 + 5:], edge[8 * 1024 + 5:])  # neighbours untouched
+
+
+def test_sumsq_and_axpby(ops):
+    torch.manual_seed(13)
+    for n, dt in ((100003, torch.bfloat16), (8 * 4096, torch.bfloat16), (50001, torch.float32)):
+        x = torch.randn(n, device=DEV, dtype=dt)
+        out = torch.zeros(1, device=DEV, dtype=torch.float32)
+        ops.ext.sumsq(x, out)
+        ref = x.double().pow(2).sum().item()
+        assert abs(out.item() - ref) <= 1e-3 * ref, (n, dt, out.item(), ref)
+    y, x = _rand(100003), _rand(100003)
+    want = (0.5 * y.float() + 2.0 * x.float())
+    ops.ext.axpby(y, x, 0.5, 2.0)
+    _close(y, want, 1e-2, "axpby")
+
+
 def test_end_to_end_matches_reference_path(ops):
     """One training step of a small bf16 model: CUDA kernels vs the PyTorch statement of every op."""
     from moe_distributed_training_b200 import MixtralConfig
