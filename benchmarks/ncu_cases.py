@@ -1,6 +1,6 @@
 """Small single-GPU cases for profiler captures: one kernel family per case, a handful of launches.
 
-    python benchmarks/ncu_cases.py gemm|expert_mlp|attention|dispatch
+    python benchmarks/ncu_cases.py gemm|gemm_pair|expert_mlp|attention|dispatch
 
 Sizes keep the working set above the 126 MB L2 where DRAM figures matter, but far below a GB of launches.
 """
@@ -17,10 +17,11 @@ def main():
     from moe_distributed_training_b200.ops import cuda_ops as C
     dev, bf = "cuda", torch.bfloat16
     torch.manual_seed(0)
-    if case == "gemm":
+    if case in ("gemm", "gemm_pair"):
         x = torch.randn(8192, 4096, device=dev, dtype=bf)
         w = torch.randn(8192, 4096, device=dev, dtype=bf)
         out = torch.empty(8192, 8192, device=dev, dtype=bf)
+        C.ext.gemm_set_pair_policy(2 if case == "gemm_pair" else 0)   # CTA-pair kernel or single-CTA kernel
         for _ in range(4):
             C.mm_nt(x, w, out=out)
     elif case == "expert_mlp":

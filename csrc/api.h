@@ -42,6 +42,17 @@ typedef struct MdtGemmDesc {
 
 int mdt_gemm(const MdtGemmDesc* desc, cudaStream_t stream);
 long long mdt_gemm_launch_count(void);
+long long mdt_skinny_launch_count(void);
+// y[M, r] = alpha * x[M, K] * op(A), r <= 32: a_is_kr = 0 -> A is [r, K] (row stride lda), 1 -> A is [K, r]
+int mdt_skinny_mm(const void* x, const void* A, void* y, int M, int K, int r, long long ldx, long long lda,
+                  int a_is_kr, float alpha, cudaStream_t s);
+// CTA-pair (cta_group::2) kernel selection: 0 never, 1 where the shape fills 256-row pair tiles, 2 whenever the
+// tile is 256 wide; returns the previous policy (policy < 0 only reads it).
+int mdt_gemm_set_pair_policy(int policy);
+// CTA pairs resident at once on this device (0 until the pair kernel has been launched)
+int mdt_gemm_max_pairs(void);
+// upper bound on the pair kernel's grid, in pairs (0 = the resident maximum); for scaling measurements
+void mdt_gemm_set_pair_cap(int pairs);
 
 // ---- element-wise / normalisation / loss / optimizer (elementwise.cu) --------------------------
 int mdt_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps, cudaStream_t s);
@@ -49,7 +60,9 @@ int mdt_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* r
                     int rows, int cols, int n_partial, cudaStream_t s);
 int mdt_rope(const void* x, void* y, const int* positions, int tokens, int heads, int head_dim, float theta,
              int inverse, cudaStream_t s);
-int mdt_swiglu_bwd(const void* g, const void* u, const void* dh, void* dg, void* du, long long n, cudaStream_t s);
+// rows_used (optional, device): number of leading rows of `cols` elements that hold data; the rest is left untouched
+int mdt_swiglu_bwd(const void* g, const void* u, const void* dh, void* dg, void* du, long long n,
+                   const int* rows_used, long long cols, cudaStream_t s);
 int mdt_swiglu_fwd(const void* g, const void* u, void* h, long long n, cudaStream_t s);
 int mdt_embedding(const void* table, const long long* ids, void* out, int tokens, int cols, cudaStream_t s);
 int mdt_embedding_bwd(const void* dout, const long long* ids, float* dtable, int tokens, int cols, cudaStream_t s);

@@ -114,10 +114,17 @@ Tensor swiglu_fwd(const Tensor& g, const Tensor& u) {
   check(mdt_swiglu_fwd(g.data_ptr(), u.data_ptr(), h.data_ptr(), g.numel(), cur_stream()), "swiglu_fwd");
   return h;
 }
-std::vector<Tensor> swiglu_bwd(const Tensor& g, const Tensor& u, const Tensor& dh) {
+// `offsets` (optional, int32 [G+1]): row-group offsets of block-padded buffers; rows past offsets[G] are not touched
+std::vector<Tensor> swiglu_bwd(const Tensor& g, const Tensor& u, const Tensor& dh, const OptTensor& offsets) {
   c10::cuda::CUDAGuard guard(g.device());
   auto dg = torch::empty_like(g), du = torch::empty_like(u);
-  check(mdt_swiglu_bwd(g.data_ptr(), u.data_ptr(), dh.data_ptr(), dg.data_ptr(), du.data_ptr(), g.numel(), cur_stream()), "swiglu_bwd");
+  const int* rows_used = nullptr;
+  if (offsets.has_value() && offsets->defined()) {
+    TORCH_CHECK(offsets->scalar_type() == at::kInt && offsets->is_contiguous() && g.dim() == 2);
+    rows_used = offsets->data_ptr<int>() + (offsets->numel() - 1);
+  }
+  check(mdt_swiglu_bwd(g.data_ptr(), u.data_ptr(), dh.data_ptr(), dg.data_ptr(), du.data_ptr(), g.numel(), rows_used,
+                       g.size(-1), cur_stream()), "swiglu_bwd");
   return {dg, du};
 }
 Tensor embedding(const Tensor& table, const Tensor& ids) {
@@ -341,7 +348,7 @@ void barrier_wait(int64_t my_flags, int64_t ws, int64_t epoch, Tensor& status, i
 }
 
 int64_t launch_count() {
-  return mdt_gemm_launch_count() + mdt_elementwise_launch_count() + mdt_router_launch_count() + mdt_attention_launch_count() + mdt_comm_launch_count();
+  return mdt_gemm_launch_count() + mdt_skinny_launch_count() + mdt_elementwise_launch_count() + mdt_router_launch_count() + mdt_attention_launch_count() + mdt_comm_launch_count();
 }
 
 
@@ -349,6 +356,23 @@ int64_t launch_count() {
 // Whole attention sub-block in one call each way (RMSNorm -> q/k/v (+LoRA) -> RoPE -> attention -> o (+LoRA)
 // -> residual).  Same kernels as the per-op bindings; issuing them from C++ keeps the host ahead of the GPU.
 // =====================================================================================================
+// y[M, r] = alpha * x[M, K] * A^T (A [r, K]) or alpha * x * A (A [K, r], a_is_kr): CUDA-core kernel for r <= 32
+bool skinny_ok(const Tensor& x, const Tensor& A, bool a_is_kr) {
+  const int64_t K = x.size(1), r = a_is_kr ? A.size(1) : A.size(0);
+  return x.scalar_type() == at::kBFloat16 && A.scalar_type() == at::kBFloat16 && x.dim() == 2 && A.dim() == 2 && r >= 1 && r <= 32 &&
+         K % 8 == 0 && x.stride(1) == 1 && x.stride(0) % 8 == 0 && A.stride(1) == 1 &&
+         (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0 && (a_is_kr ? A.size(0) : A.size(1)) == K;
+}
+Tensor skinny_mm(const Tensor& x, const Tensor& A, bool a_is_kr, double alpha) {
+  TORCH_CHECK(skinny_ok(x, A, a_is_kr), "skinny_mm: unsupported operands");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t M = x.size(0), K = x.size(1), r = a_is_kr ? A.size(1) : A.size(0);
+  auto y = torch::empty({M, r}, x.options());
+  check(mdt_skinny_mm(x.data_ptr(), A.data_ptr(), y.data_ptr(), (int)M, (int)K, (int)r, x.stride(0), A.stride(0), a_is_kr ? 1 : 0,
+                      (float)alpha, cur_stream()), "skinny_mm");
+  return y;
+}
+
 namespace {
 
 struct Lin { Tensor W; OptTensor A, B; double s; };   // y = x W^T + s (x A^T) B^T
@@ -367,8 +391,13 @@ std::pair<Tensor, OptTensor> lin_fwd(const Tensor& x, const Lin& l, const OptTen
     return {y, std::nullopt};
   }
   const int64_t r = l.A->size(0);
-  auto t = torch::empty({M, r}, x.options());
-  gemm_raw(0, x, false, *l.A, false, t, M, r, K, std::nullopt, std::nullopt, false, 0, false, l.s, status);
+  Tensor t;
+  if (skinny_ok(x, *l.A, false)) {
+    t = skinny_mm(x, *l.A, false, l.s);
+  } else {
+    t = torch::empty({M, r}, x.options());
+    gemm_raw(0, x, false, *l.A, false, t, M, r, K, std::nullopt, std::nullopt, false, 0, false, l.s, status);
+  }
   gemm_raw(0, x, false, l.W, false, y, M, N, K, t, l.B, false, r, false, 1.0, status);
   return {y, t};
 }
@@ -381,8 +410,12 @@ LinGrads lin_bwd(const Tensor& dy, const Tensor& xin, const Lin& l, const OptTen
   OptTensor dt;
   if (l.A.has_value()) {
     const int64_t r = l.A->size(0);
-    dt = torch::empty({M, r}, dy.options());
-    gemm_raw(0, dy, false, *l.B, true, *dt, M, r, N, std::nullopt, std::nullopt, false, 0, false, l.s, status);      // s dy B
+    if (skinny_ok(dy, *l.B, true)) {
+      dt = skinny_mm(dy, *l.B, true, l.s);                                                                           // s dy B
+    } else {
+      dt = torch::empty({M, r}, dy.options());
+      gemm_raw(0, dy, false, *l.B, true, *dt, M, r, N, std::nullopt, std::nullopt, false, 0, false, l.s, status);
+    }
     gemm_raw(0, dy, false, l.W, true, dx, M, K, N, dt, l.A, true, r, accumulate, 1.0, status);                       // dy W + dt A
     if (need_a) { g.dA = torch::empty_like(*l.A); gemm_raw(2, *dt, true, xin, true, *g.dA, r, K, M, std::nullopt, std::nullopt, false, 0, false, 1.0, status); }
     if (need_b) { g.dB = torch::empty_like(*l.B); gemm_raw(2, dy, true, *t, true, *g.dB, N, r, M, std::nullopt, std::nullopt, false, 0, false, 1.0, status); }
@@ -590,7 +623,7 @@ std::vector<Tensor> moe_block_bwd(const Tensor& dy, const std::vector<Tensor>& s
   Tensor dh = torch::empty({R, F}, x.options());
   ggemm(1, dyg, false, w2, false, dh, R, F, H, El, offs, cap, NONE, NONE, NONE, false, 0, NONE, NONE, false, 1.0, status, w0, w1o, NONE, NONE, NONE, NONE);
   if (!wg.empty()) { Tensor c = wg[1]; ggemm(2, h, true, dyg, true, c, F, H, 0, El, offs, cap, NONE, NONE, NONE, false, 0, NONE, NONE, true, wscale, status, NONE, NONE, NONE, NONE, NONE, NONE); }
-  auto gu = swiglu_bwd(g, u, dh);
+  auto gu = swiglu_bwd(g, u, dh, offs);
   Tensor dxg = torch::empty({R, H}, x.options());
   ggemm(1, gu[0], false, w1, true, dxg, R, H, F, El, offs, cap, NONE, gu[1], w3, true, F, NONE, NONE, false, 1.0, status, NONE, NONE, s0, s1, s2, s3);
   if (!wg.empty()) {
@@ -620,10 +653,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("rope", &rope);
   m.def("swiglu_fwd", &swiglu_fwd);
-  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("swiglu_bwd", &swiglu_bwd, py::arg("g"), py::arg("u"), py::arg("dh"), py::arg("offsets") = py::none());
   m.def("embedding", &embedding);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("cross_entropy", &cross_entropy);
+  m.def("gemm_set_pair_policy", [](int64_t policy) { return (int64_t)mdt_gemm_set_pair_policy((int)policy); });
+  m.def("gemm_set_pair_cap", [](int64_t n) { mdt_gemm_set_pair_cap((int)n); });
+  m.def("gemm_max_pairs", []() { return (int64_t)mdt_gemm_max_pairs(); });
+  m.def("skinny_mm", &skinny_mm);
   m.def("adamw", &adamw);
   m.def("sumsq", &sumsq);
   m.def("axpby", &axpby);

@@ -155,7 +155,10 @@ __global__ void swiglu_fwd_kernel(const uint4* __restrict__ g, const uint4* __re
   }
 }
 __global__ void swiglu_bwd_kernel(const uint4* __restrict__ g, const uint4* __restrict__ u, const uint4* __restrict__ dh,
-                                  uint4* __restrict__ dg, uint4* __restrict__ du, long long nv) {
+                                  uint4* __restrict__ dg, uint4* __restrict__ du, long long nv,
+                                  const int* __restrict__ rows_used, long long vecs_per_row) {
+  // buffers sized for a capacity carry their row count in device memory: only that many rows are touched
+  if (rows_used != nullptr) { const long long lim = (long long)rows_used[0] * vecs_per_row; nv = lim < nv ? lim : nv; }
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv; i += (long long)gridDim.x * blockDim.x) {
     float a[8], b[8], d[8], og[8], ou[8]; unpack8(g[i], a); unpack8(u[i], b); unpack8(dh[i], d);
 #pragma unroll
@@ -419,10 +422,11 @@ extern "C" int mdt_swiglu_fwd(const void* g, const void* u, void* h, long long n
   MDT_CHECK_LAUNCH();
   return 0;
 }
-extern "C" int mdt_swiglu_bwd(const void* g, const void* u, const void* dh, void* dg, void* du, long long n, cudaStream_t s) {
+extern "C" int mdt_swiglu_bwd(const void* g, const void* u, const void* dh, void* dg, void* du, long long n,
+                              const int* rows_used, long long cols, cudaStream_t s) {
   if (n % 8 != 0) return -1;
   if (n == 0) return 0;
-  swiglu_bwd_kernel<<<grid_for(n / 8, 256), 256, 0, s>>>((const uint4*)g, (const uint4*)u, (const uint4*)dh, (uint4*)dg, (uint4*)du, n / 8);
+  swiglu_bwd_kernel<<<grid_for(n / 8, 256), 256, 0, s>>>((const uint4*)g, (const uint4*)u, (const uint4*)dh, (uint4*)dg, (uint4*)du, n / 8, rows_used, cols / 8);
   MDT_CHECK_LAUNCH();
   return 0;
 }

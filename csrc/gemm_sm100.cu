@@ -21,6 +21,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <map>
 #include <unordered_map>
@@ -360,6 +361,304 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
 }
 
 // ---------------------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2).  Two CTAs of a cluster share one 256 x 256 MMA tile: each CTA loads its own
+// 128 rows of A and half of B's 256 columns (in the dual mode: the leader the gate matrix, its peer the up
+// matrix), the leader's MMA thread reads both CTAs' shared memory, and each CTA's TMEM receives the accumulators
+// of its own 128 rows.  Per CTA and 64-deep k block that is 32 KB of operands instead of 48 KB, which is what
+// bounds the single-CTA kernel, and the ring holds 7 stages instead of 4.
+//   full_bar[s]   (leader's is used): 2 arrivals (one producer per CTA) + both CTAs' TMA bytes
+//   empty_bar[s]  (one per CTA)     : arrives by the leader's commit, delivered to both CTAs
+//   tfull_bar[b]  (one per CTA)     : same, when a tile's accumulators are complete
+//   tempty_bar[b] (leader's is used): 8 arrivals, the 4 epilogue warps of each CTA
+// Every load lands in the shared memory of the CTA that issued it.
+// ---------------------------------------------------------------------------------------------
+constexpr int PAIR_BN = 256;
+constexpr int PAIR_STAGES = 7;
+constexpr int PAIR_B_BYTES = 128 * BK * 2;
+constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;
+
+struct PairTile {
+  int g, m0, n0, krow0, num_kb, num_kb_l, second_ok;
+};
+
+// Pair tiles cover 256 rows.  In the grouped-rows mode a pair never straddles two groups: a group with an odd
+// number of 128-row blocks ends with a pair whose second half is idle (second_ok = 0).
+template <int BN_OUT>
+__device__ __forceinline__ bool get_pair_tile(const GemmParams& p, int t, PairTile& o) {
+  const int n_blocks = (p.N + BN_OUT - 1) / BN_OUT;
+  o.num_kb_l = (p.K_l + BK - 1) / BK;
+  o.second_ok = 1;
+  if (p.mode == 2) {
+    const int m_pairs = (p.M + 2 * BM - 1) / (2 * BM);
+    const int per_group = m_pairs * n_blocks;
+    if (t >= per_group * p.G) return false;
+    o.g = t / per_group;
+    const int r = t - o.g * per_group;
+    o.m0 = (r % m_pairs) * 2 * BM;
+    o.n0 = (r / m_pairs) * BN_OUT;
+    int k_begin = 0, k_end = p.K;
+    if (p.offsets != nullptr) { k_begin = p.offsets[o.g]; k_end = p.offsets[o.g + 1]; }
+    o.krow0 = k_begin;
+    o.num_kb = (k_end - k_begin + BK - 1) / BK;
+    return true;
+  }
+  o.krow0 = 0;
+  o.num_kb = (p.K + BK - 1) / BK;
+  if (p.mode == 0) {
+    const int m_pairs = (p.M + 2 * BM - 1) / (2 * BM);
+    if (t >= m_pairs * n_blocks) return false;
+    o.g = 0;
+    o.m0 = (t % m_pairs) * 2 * BM;
+    o.n0 = (t / m_pairs) * BN_OUT;
+    return true;
+  }
+  int total = 0;
+  for (int g = 0; g < p.G; ++g) total += ((p.offsets[g + 1] - p.offsets[g]) / BM + 1) / 2;
+  if (total == 0 || t >= total * n_blocks) return false;
+  int mp = t % total;
+  o.n0 = (t / total) * BN_OUT;
+  for (int g = 0; g < p.G; ++g) {
+    const int begin = p.offsets[g], end = p.offsets[g + 1];
+    const int pairs = ((end - begin) / BM + 1) / 2;
+    if (mp < pairs) {
+      o.g = g;
+      o.m0 = begin + mp * 2 * BM;
+      o.second_ok = (o.m0 + BM < end) ? 1 : 0;
+      return true;
+    }
+    mp -= pairs;
+  }
+  return false;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_pair_kernel(const __grid_constant__ GemmParams p) {
+  constexpr int STAGES = PAIR_STAGES;
+  constexpr int BN = PAIR_BN;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  // the dynamic shared memory starts at the same offset in both CTAs, so the aligned tile addresses match too
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * PAIR_STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();          // 0 = leader
+  const int pair_id = (int)cluster_id_x(), num_pairs = (int)num_clusters_x();
+  const int BN_OUT = p.dual ? BN / 2 : BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 2); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 8); }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc_pair(tmem_slot, TMEM_COLS); tmem_relinquish_pair(); }
+  tc_fence_before();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto fail = [&](int code) {
+    *abort_flag = 1;
+    if (p.status != nullptr) atomicCAS(p.status, 0, code);
+  };
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------------ TMA producer (one per CTA)
+    prefetch_tensormap(&p.tmA); prefetch_tensormap(&p.tmB);
+    uint32_t it = 0;
+    PairTile t;
+    bool ok = true;
+    for (int tile = pair_id; ok && (p.dual ? get_pair_tile<BN / 2>(p, tile, t) : get_pair_tile<BN>(p, tile, t)); tile += num_pairs) {
+      const int total_kb = t.num_kb + (t.num_kb > 0 || p.mode != 2 ? t.num_kb_l : 0);
+      const int my_m0 = t.m0 + (int)cta_rank * BM;
+      const bool half_ok = cta_rank == 0 || t.second_ok;
+      if (p.tile_ready != nullptr && half_ok && total_kb > 0) {
+        const int ti = my_m0 / BM;
+        if (!wait_ge(p.tile_ready + ti, (unsigned)p.tile_expected[ti], MDT_GEMM_PEER_WAIT_NS)) { fail(ST_TIMEOUT_PEER); ok = false; break; }
+        fence_proxy_async_all();
+      }
+      for (int kb = 0; kb < total_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!wait_parity(&empty_bar[s], ph ^ 1, abort_flag)) { fail(ST_TIMEOUT_EMPTY); ok = false; break; }
+        uint8_t* sA = smem + s * PAIR_STAGE_BYTES;
+        uint8_t* sB = sA + A_BYTES;
+        const uint32_t bar = mapa_shared(smem_u32(&full_bar[s]), 0);
+        mbar_expect_tx_cluster(bar, PAIR_STAGE_BYTES);
+        const bool lora = kb >= t.num_kb;
+        const int kk = (lora ? kb - t.num_kb : kb) * BK;
+        const CUtensorMap* mA = lora ? &p.tmA_l : &p.tmA;
+        const CUtensorMap* mB = lora ? &p.tmB_l : &p.tmB;
+        const int a_mn = lora ? p.a_mn_l : p.a_mn, b_mn = lora ? p.b_mn_l : p.b_mn;
+        const int krow = (lora ? 0 : t.krow0) + kk;
+        if (a_mn == 0) {
+          tma_load_2d_pair(sA, mA, bar, kk, my_m0);
+        } else {
+          tma_load_2d_pair(sA, mA, bar, my_m0, krow);
+          tma_load_2d_pair(sA + 8192, mA, bar, my_m0 + 64, krow);
+        }
+        const int zB = (p.mode == 2) ? 0 : t.g;
+        // this CTA's half of B: columns n0 + 128*rank, or in the dual mode the gate (leader) / up (peer) matrix
+        if (p.dual && cta_rank == 1) mB = lora ? &p.tmB2_l : &p.tmB2;
+        const int my_n0 = p.dual ? t.n0 : t.n0 + (int)cta_rank * 128;
+        if (b_mn == 0) {
+          tma_load_3d_pair(sB, mB, bar, kk, my_n0, zB);
+        } else {
+          tma_load_3d_pair(sB, mB, bar, my_n0, krow, zB);
+          tma_load_3d_pair(sB + 8192, mB, bar, my_n0 + 64, krow, zB);
+        }
+      }
+    }
+    if (!ok) {  // give this CTA's copies already in flight a bounded time to land before it leaves
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 2000000ull) {}
+    }
+  } else if (warp == 1 && lane == 0 && cta_rank == 0) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    uint32_t it = 0, acc_it = 0;
+    PairTile t;
+    bool ok = true;
+    for (int tile = pair_id; ok && (p.dual ? get_pair_tile<BN / 2>(p, tile, t) : get_pair_tile<BN>(p, tile, t)); tile += num_pairs) {
+      const int total_kb = t.num_kb + (t.num_kb > 0 || p.mode != 2 ? t.num_kb_l : 0);
+      if (total_kb == 0) continue;
+      const int buf = acc_it & 1;
+      const uint32_t aph = (acc_it >> 1) & 1;
+      if (!wait_parity(&tempty_bar[buf], aph ^ 1, abort_flag)) { fail(ST_TIMEOUT_TMEM_EMPTY); break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      for (int kb = 0; kb < total_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!wait_parity(&full_bar[s], ph, abort_flag)) { fail(ST_TIMEOUT_FULL); ok = false; break; }
+        tc_fence_after();
+        const bool lora = kb >= t.num_kb;
+        const int a_mn = lora ? p.a_mn_l : p.a_mn, b_mn = lora ? p.b_mn_l : p.b_mn;
+        const uint32_t idesc = make_idesc_bf16(2 * BM, BN, a_mn, b_mn);
+        const uint32_t sA = smem_u32(smem + s * PAIR_STAGE_BYTES);
+        const uint32_t sB = sA + A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {
+          const uint64_t da = a_mn ? make_smem_desc(sA + k * 2048, 8192, 1024) : make_smem_desc(sA + k * 32, 16, 1024);
+          const uint64_t db = b_mn ? make_smem_desc(sB + k * 2048, 8192, 1024) : make_smem_desc(sB + k * 32, 16, 1024);
+          umma_bf16_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit_pair(&empty_bar[s], 3);   // frees the stage in both CTAs
+      }
+      if (!ok) break;
+      umma_commit_pair(&tfull_bar[buf], 3);   // accumulators complete, in both CTAs
+      ++acc_it;
+    }
+  } else if (warp >= 2) {
+    // ------------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    const int q = warp & 3;
+    uint32_t acc_it = 0;
+    PairTile t;
+    for (int tile = pair_id; (p.dual ? get_pair_tile<BN / 2>(p, tile, t) : get_pair_tile<BN>(p, tile, t)); tile += num_pairs) {
+      const int total_kb = t.num_kb + (t.num_kb > 0 || p.mode != 2 ? t.num_kb_l : 0);
+      const bool half_ok = cta_rank == 0 || t.second_ok;
+      const int row = t.m0 + (int)cta_rank * BM + q * 32 + lane;
+      const int row_limit = (p.mode == 1) ? p.offsets[p.G] : p.M;
+      const bool row_ok = half_ok && row < row_limit;
+      long long base = (p.mode == 2 ? (long long)t.g * p.c_group_stride : 0) + (long long)row * p.ldc;
+      void* Cout = p.C;
+      int dest = -1;
+      bool store_ok = row_ok;
+      if (p.row_dest_rank != nullptr) {          // result rows go straight into peers' buffers
+        dest = row_ok ? p.row_dest_rank[row] : -1;
+        store_ok = dest >= 0;
+        if (store_ok) { Cout = reinterpret_cast<void*>(p.peer_out[dest]); base = (long long)p.row_dest_row[row] * p.ldc; }
+      }
+      if (total_kb == 0) {
+        if (!p.accumulate && row_ok) {
+          float z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          for (int c = 0; c < BN_OUT; c += 8)
+            if (t.n0 + c < p.N) store8(p.C, base + t.n0 + c, z, p.c_fp32, 0);
+        }
+        continue;
+      }
+      const int buf = acc_it & 1;
+      const uint32_t aph = (acc_it >> 1) & 1;
+      if (!wait_parity(&tfull_bar[buf], aph, abort_flag)) { fail(ST_TIMEOUT_TMEM_FULL); break; }
+      __syncwarp();   // lanes may leave the wait loop at different times; the TMEM loads below are warp-aligned
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
+      if (p.dual) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 2; c += 32) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(taddr + c, rg);
+          tmem_ld_32x32(taddr + BN / 2 + c, ru);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = t.n0 + c + v * 8;
+              if (col < p.N) {
+                float h[8], gg[8], uu[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  gg[i] = __uint_as_float(rg[v * 8 + i]);
+                  uu[i] = __uint_as_float(ru[v * 8 + i]);
+                  h[i] = gg[i] / (1.0f + __expf(-gg[i])) * uu[i];
+                }
+                store8(p.C, base + col, h, 0, 0);
+                if (p.store_gate_up) { store8(p.C2, base + col, gg, 0, 0); store8(p.C3, base + col, uu, 0, 0); }
+              }
+            }
+          }
+          __syncwarp();   // the next TMEM load is warp-aligned
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tmem_ld_wait();
+          if (store_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = t.n0 + c + v * 8;
+              if (col < p.N) {
+                float o[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(r[v * 8 + i]) * p.alpha;
+                store8(Cout, base + col, o, p.c_fp32, p.accumulate);
+              }
+            }
+          }
+          __syncwarp();   // the next TMEM load is warp-aligned
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[buf]), 0));
+      ++acc_it;
+      if (p.row_dest_rank != nullptr) {
+        // publish this warp's rows: one count per (row, column tile) and destination
+        __threadfence_system();
+        __syncwarp();
+        for (int d = 0; d < p.num_peers; ++d) {
+          const unsigned m = __ballot_sync(0xffffffffu, dest == d);
+          if (lane == 0 && m != 0) red_add_release_sys(reinterpret_cast<unsigned*>(p.peer_arrive[d]), __popc(m));
+        }
+      }
+    }
+  }
+
+  // Neither CTA may leave while its partner can still read its shared memory or arrive on its barriers.
+  __syncwarp();
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc_pair(tmem_base, TMEM_COLS); }
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -440,9 +739,57 @@ static cudaError_t launch(const GemmParams& p, int grid, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+// Number of CTA pairs that can be resident at once (pairs never span GPCs, so this can be below SMs / 2); the
+// persistent grid is sized to it because tiles are assigned to pairs statically.
+static int g_max_pairs = 0;
+static int g_pair_cap = 0;   // optional upper bound set through mdt_gemm_set_pair_cap (0 = none)
+
+static cudaError_t launch_pair(const GemmParams& p, int pairs_wanted, cudaStream_t stream) {
+  constexpr int smem = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_sm100_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)(g_num_sms & ~1)); cfg.blockDim = dim3(GEMM_THREADS); cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_sm100_pair_kernel, &cfg) != cudaSuccess || n < 1) { cudaGetLastError(); n = g_num_sms / 2; }
+    g_max_pairs = n < g_num_sms / 2 ? n : g_num_sms / 2;
+    configured = true;
+  }
+  const int limit = (g_pair_cap > 0 && g_pair_cap < g_max_pairs) ? g_pair_cap : g_max_pairs;
+  const int grid = 2 * (pairs_wanted < limit ? pairs_wanted : limit);
+  gemm_sm100_pair_kernel<<<grid, GEMM_THREADS, smem, stream>>>(p);
+  ++g_launches;
+  return cudaGetLastError();
+}
+
+// 0 = never (default), 1 = where the shape fills pair tiles, 2 = whenever the tile is 256 wide (tests).
+// Initial value from MDT_GEMM_PAIR; mdt_gemm_set_pair_policy() changes it.
+static int g_pair_policy = -1;
+static int pair_policy() {
+  if (g_pair_policy < 0) {
+    const char* e = getenv("MDT_GEMM_PAIR");
+    g_pair_policy = (e != nullptr && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 0;
+  }
+  return g_pair_policy;
+}
+
 }  // namespace mdt
 
 extern "C" long long mdt_gemm_launch_count() { return mdt::g_launches; }
+extern "C" int mdt_gemm_max_pairs() { return mdt::g_max_pairs; }
+extern "C" void mdt_gemm_set_pair_cap(int pairs) { mdt::g_pair_cap = pairs; }
+extern "C" int mdt_gemm_set_pair_policy(int policy) {
+  const int old = mdt::pair_policy();
+  if (policy >= 0 && policy <= 2) mdt::g_pair_policy = policy;
+  return old;
+}
 
 extern "C" int mdt_gemm(const MdtGemmDesc* d, cudaStream_t stream) {
   using namespace mdt;
@@ -470,16 +817,22 @@ extern "C" int mdt_gemm(const MdtGemmDesc* d, cudaStream_t stream) {
   if (p.dual && (p.b_mn != 0 || p.c_fp32 || p.accumulate)) return -11;
   const int BN = (p.dual || p.N > 128) ? 256 : 128;
   const int bn_out = p.dual ? BN / 2 : BN;
+  // The CTA-pair kernel needs 256-row pair tiles that are mostly full: dense and depth-grouped products with
+  // M >= 256, and row-grouped products whose groups average at least four 128-row blocks.
+  const long long rows_hint = (p.mode == 1) ? d->capacity_rows : p.M;
+  const int policy = pair_policy();
+  const bool pair = BN == 256 && (policy == 2 || (policy == 1 && rows_hint >= 2 * BM &&
+                                                  (p.mode != 1 || rows_hint >= (long long)p.G * 4 * BM)));
   int rc = 0;
   // A: [a_rows, a_cols] row-major, a_cols contiguous.  K-major: rows = M, cols = K.  MN-major: rows = depth, cols = M.
   rc |= make_map(&p.tmA, d->A, d->a_cols, d->a_rows, 1, d->lda, 0, 64, d->a_mn ? 64 : BM, 2);
   // B: [G, b_rows, b_cols].  K-major: rows = N, cols = K.  MN-major: rows = depth, cols = N.
-  const uint32_t b_box_rows = d->b_mn ? 64 : bn_out;
+  const uint32_t b_box_rows = d->b_mn ? 64 : (pair ? 128 : bn_out);
   rc |= make_map(&p.tmB, d->B, d->b_cols, d->b_rows, p.mode == 2 ? 1 : p.G, d->ldb, d->b_group_stride, 64, b_box_rows, 3);
   if (p.dual) rc |= make_map(&p.tmB2, d->B2, d->b_cols, d->b_rows, p.G, d->ldb, d->b_group_stride, 64, b_box_rows, 3);
   if (p.K_l > 0) {
     rc |= make_map(&p.tmA_l, d->A_l, d->al_cols, d->al_rows, 1, d->lda_l, 0, 64, d->a_mn_l ? 64 : BM, 2);
-    const uint32_t bl_box_rows = d->b_mn_l ? 64 : bn_out;
+    const uint32_t bl_box_rows = d->b_mn_l ? 64 : (pair ? 128 : bn_out);
     rc |= make_map(&p.tmB_l, d->B_l, d->bl_cols, d->bl_rows, p.G, d->ldb_l, d->bl_group_stride, 64, bl_box_rows, 3);
     if (p.dual) rc |= make_map(&p.tmB2_l, d->B2_l, d->bl_cols, d->bl_rows, p.G, d->ldb_l, d->bl_group_stride, 64, bl_box_rows, 3);
   }
@@ -488,6 +841,12 @@ extern "C" int mdt_gemm(const MdtGemmDesc* d, cudaStream_t stream) {
   long long rows = (p.mode == 1) ? d->capacity_rows : p.M;
   long long tiles = ((rows + BM - 1) / BM) * ((p.N + bn_out - 1) / bn_out) * (p.mode == 2 ? p.G : 1);
   int grid = (int)(tiles < g_num_sms ? (tiles < 1 ? 1 : tiles) : g_num_sms);
+  if (pair) {
+    long long pairs = ((rows + 2 * BM - 1) / (2 * BM) + (p.mode == 1 ? p.G : 0)) * ((p.N + bn_out - 1) / bn_out) * (p.mode == 2 ? p.G : 1);
+    const int np = (int)(pairs < 1 ? 1 : (pairs > g_num_sms ? g_num_sms : pairs));
+    cudaError_t e2 = launch_pair(p, np, stream);
+    return e2 == cudaSuccess ? 0 : -100 - (int)e2;
+  }
   cudaError_t e = (BN == 256) ? launch<256, 4>(p, grid, stream) : launch<128, 6>(p, grid, stream);
   return e == cudaSuccess ? 0 : -100 - (int)e;
 }

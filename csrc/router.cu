@@ -4,6 +4,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <map>
+#include <mutex>
+
 #include "api.h"
 
 namespace mdt {
@@ -32,26 +35,49 @@ __device__ __forceinline__ float wsum(float v) {
   return v;
 }
 
-// logits[e] = <x[t,:], w[e,:]> for one token per warp; every lane ends with all E logits
+// logits[e] = <x[t,:], w[e,:]> for one token per warp; every lane ends with all E logits.
+// `w` may point to shared memory (see stage_router_weights).  Four 16-byte loads of x are in flight per lane.
 template <int E_T>
-__device__ __forceinline__ void token_logits(const bf16* __restrict__ x, const bf16* __restrict__ w, int hidden, int experts,
+__device__ __forceinline__ void token_logits(const bf16* __restrict__ x, const bf16* w, int hidden, int experts,
                                              int lane, float (&logit)[E_T]) {
 #pragma unroll
   for (int e = 0; e < E_T; ++e) logit[e] = 0.f;
   const uint4* xr = reinterpret_cast<const uint4*>(x);
-  for (int i = lane; i < hidden / 8; i += 32) {
-    float xf[8]; unpack8r(xr[i], xf);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  const int nv = hidden / 8;
+  for (int i0 = lane; i0 < nv; i0 += 128) {
+    uint4 xv[4];
 #pragma unroll
-    for (int e = 0; e < E_T; ++e) {
-      if (e < experts) {
-        float wf[8]; unpack8r(reinterpret_cast<const uint4*>(w + (long long)e * hidden)[i], wf);
+    for (int u = 0; u < 4; ++u) xv[u] = (i0 + 32 * u < nv) ? xr[i0 + 32 * u] : make_uint4(0, 0, 0, 0);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) logit[e] += xf[j] * wf[j];
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + 32 * u;
+      if (i < nv) {
+        float xf[8]; unpack8r(xv[u], xf);
+#pragma unroll
+        for (int e = 0; e < E_T; ++e) {
+          if (e < experts) {
+            float wf[8]; unpack8r(wr[(long long)e * nv + i], wf);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) logit[e] += xf[j] * wf[j];
+          }
+        }
       }
     }
   }
 #pragma unroll
   for (int e = 0; e < E_T; ++e) logit[e] = wsum(logit[e]);
+}
+
+// Copies the router matrix into shared memory once per CTA when the launch provided room for it.
+__device__ __forceinline__ const bf16* stage_router_weights(const bf16* __restrict__ w, int experts, int hidden, int staged) {
+  extern __shared__ uint4 router_w_smem[];
+  if (!staged) return w;
+  const int nv = experts * (hidden / 8);
+  const uint4* src = reinterpret_cast<const uint4*>(w);
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) router_w_smem[i] = src[i];
+  __syncthreads();
+  return reinterpret_cast<const bf16*>(router_w_smem);
 }
 
 template <int E_T>
@@ -82,13 +108,14 @@ __device__ __forceinline__ void softmax_topk(const float (&logit)[E_T], int expe
 template <int E_T>
 __global__ void router_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ scores,
                                   bf16* __restrict__ weights, int* __restrict__ idx, int tokens, int hidden, int experts,
-                                  int top_k, int normalize) {
+                                  int top_k, int normalize, int w_staged) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
+  const bf16* wp = stage_router_weights(w, experts, hidden, w_staged);
   for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < tokens; t += gridDim.x * warps_per_block) {
     float logit[E_T], prob[E_T], wsel[MAX_K], denom;
     int sel[MAX_K];
-    token_logits<E_T>(x + (long long)t * hidden, w, hidden, experts, lane, logit);
+    token_logits<E_T>(x + (long long)t * hidden, wp, hidden, experts, lane, logit);
     softmax_topk<E_T>(logit, experts, top_k, normalize, prob, sel, wsel, denom);
     if (lane == 0) {
 #pragma unroll
@@ -107,13 +134,14 @@ template <int E_T>
 __global__ void router_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const int* __restrict__ idx,
                                   const bf16* __restrict__ dweights, const bf16* __restrict__ dscores, bf16* __restrict__ dx,
                                   float* __restrict__ dlogits, int tokens, int hidden, int experts, int top_k, int normalize,
-                                  int accumulate_dx) {
+                                  int accumulate_dx, int w_staged) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
+  const bf16* wp = stage_router_weights(w, experts, hidden, w_staged);
   for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < tokens; t += gridDim.x * warps_per_block) {
     float logit[E_T], prob[E_T], ds[E_T], wsel[MAX_K], denom;
     int sel[MAX_K];
-    token_logits<E_T>(x + (long long)t * hidden, w, hidden, experts, lane, logit);
+    token_logits<E_T>(x + (long long)t * hidden, wp, hidden, experts, lane, logit);
     softmax_topk<E_T>(logit, experts, top_k, normalize, prob, sel, wsel, denom);
     // the forward's selection is authoritative (ties): take the saved indices
     for (int c = 0; c < top_k; ++c) sel[c] = idx[(long long)t * top_k + c];
@@ -156,7 +184,7 @@ __global__ void router_bwd_kernel(const bf16* __restrict__ x, const bf16* __rest
 #pragma unroll
       for (int e = 0; e < E_T; ++e) {
         if (e < experts) {
-          float wf[8]; unpack8r(reinterpret_cast<const uint4*>(w + (long long)e * hidden)[i], wf);
+          float wf[8]; unpack8r(reinterpret_cast<const uint4*>(wp + (long long)e * hidden)[i], wf);
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc[j] += dl[e] * wf[j];
         }
@@ -331,17 +359,39 @@ using namespace mdt;
 
 extern "C" long long mdt_router_launch_count() { return g_rt_launches; }
 
+// One warp per token, four tokens per CTA in flight; enough CTAs to fill the GPU, each staging the router matrix once.
+static int router_grid(int tokens) {
+  const int g = (tokens + 3) / 4;
+  return g < 1 ? 1 : (g > 148 * 3 ? 148 * 3 : g);
+}
+// The router matrix is staged in shared memory when it fits (E x H bf16 <= 96 KB); opt in above 48 KB once per kernel.
+static int router_smem_ok(const void* kernel, size_t bytes) {
+  if (bytes > 96 * 1024) return 0;
+  if (bytes <= 48 * 1024) return 1;
+  static std::map<const void*, int> done;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = done.find(kernel);
+  if (it != done.end()) return it->second;
+  const int ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) == cudaSuccess ? 1 : 0;
+  done[kernel] = ok;
+  return ok;
+}
+
 extern "C" int mdt_router_fwd(const void* x, const void* w, void* scores, void* weights, int* idx, int tokens, int hidden,
                               int experts, int top_k, int normalize, cudaStream_t s) {
   if (hidden % 8 != 0 || experts > MAX_E || top_k > MAX_K || top_k > experts) return -1;
   if (tokens == 0) return 0;
-  const int grid = (tokens + 3) / 4;
-  if (experts <= 8)
-    router_fwd_kernel<8><<<grid, 128, 0, s>>>((const bf16*)x, (const bf16*)w, (bf16*)scores, (bf16*)weights, idx, tokens, hidden, experts, top_k, normalize);
-  else if (experts <= 16)
-    router_fwd_kernel<16><<<grid, 128, 0, s>>>((const bf16*)x, (const bf16*)w, (bf16*)scores, (bf16*)weights, idx, tokens, hidden, experts, top_k, normalize);
-  else
-    router_fwd_kernel<MAX_E><<<grid, 128, 0, s>>>((const bf16*)x, (const bf16*)w, (bf16*)scores, (bf16*)weights, idx, tokens, hidden, experts, top_k, normalize);
+  const int grid = router_grid(tokens);
+  const size_t wbytes = (size_t)experts * hidden * 2;
+#define RT_FWD(ET)                                                                                                             \
+  {                                                                                                                            \
+    const int staged = router_smem_ok((const void*)router_fwd_kernel<ET>, wbytes);                                             \
+    router_fwd_kernel<ET><<<grid, 128, staged ? wbytes : 0, s>>>((const bf16*)x, (const bf16*)w, (bf16*)scores, (bf16*)weights, \
+                                                                 idx, tokens, hidden, experts, top_k, normalize, staged);      \
+  }
+  if (experts <= 8) RT_FWD(8) else if (experts <= 16) RT_FWD(16) else RT_FWD(MAX_E)
+#undef RT_FWD
   MDT_RT_CHECK();
   return 0;
 }
@@ -353,11 +403,16 @@ extern "C" int mdt_router_bwd(const void* x, const void* w, const void* scores, 
   if (hidden % 8 != 0 || experts > MAX_E || top_k > MAX_K) return -1;
   if (tokens == 0) return 0;
   float* dlogits = dw + (long long)experts * hidden;
-  const int grid = (tokens + 3) / 4;
+  const int grid = router_grid(tokens);
+  const size_t wbytes = (size_t)experts * hidden * 2;
   dim3 g2((hidden + 127) / 128, 16);
 #define RT_BWD(ET)                                                                                                          \
-  router_bwd_kernel<ET><<<grid, 128, 0, s>>>((const bf16*)x, (const bf16*)w, idx, (const bf16*)dweights, (const bf16*)dscores, \
-                                             (bf16*)dx, dlogits, tokens, hidden, experts, top_k, normalize, accumulate_dx);    \
+  {                                                                                                                         \
+    const int staged = router_smem_ok((const void*)router_bwd_kernel<ET>, wbytes);                                          \
+    router_bwd_kernel<ET><<<grid, 128, staged ? wbytes : 0, s>>>((const bf16*)x, (const bf16*)w, idx, (const bf16*)dweights,  \
+                                                                 (const bf16*)dscores, (bf16*)dx, dlogits, tokens, hidden,  \
+                                                                 experts, top_k, normalize, accumulate_dx, staged);         \
+  }                                                                                                                         \
   MDT_RT_CHECK();                                                                                                           \
   router_dw_kernel<ET><<<g2, 128, 0, s>>>((const bf16*)x, dlogits, dw, tokens, hidden, experts);                             \
   MDT_RT_CHECK();

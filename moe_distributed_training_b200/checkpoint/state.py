@@ -179,6 +179,8 @@ def load_training_state(engine, in_dir: str) -> int:
             p.copy_(saved.to(p.device))
             if st:
                 engine.optimizer.state[p] = {k: (v.to(p.device) if torch.is_tensor(v) else v) for k, v in st.items()}
+    if hasattr(engine.runner, "invalidate_gathered"):
+        engine.runner.invalidate_gathered()
     engine.scheduler.load_state_dict(state["scheduler"])
     for g, lr in zip(engine.optimizer.param_groups, state.get("lrs", [])):
         g["lr"] = lr
@@ -200,4 +202,6 @@ def load_adapter(engine, in_dir: str):
                 named[name].copy_(t.to(named[name].dtype))
         else:
             missing.append(key)
+    if hasattr(engine.runner, "invalidate_gathered"):
+        engine.runner.invalidate_gathered()
     return missing

@@ -16,7 +16,7 @@ CSRC = os.path.join(_ROOT, "csrc")
 EXT_DIR = os.path.join(_PKG, "_ext")
 EXT_NAME = "mdt_ext"
 
-SOURCES = ["bindings.cpp", "gemm_sm100.cu", "elementwise.cu", "router.cu", "attention.cu", "comm.cu"]
+SOURCES = ["bindings.cpp", "gemm_sm100.cu", "skinny.cu", "elementwise.cu", "router.cu", "attention.cu", "comm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 

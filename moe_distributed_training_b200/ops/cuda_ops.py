@@ -83,6 +83,14 @@ def mm_tn(a, b, out=None, alpha=1.0, accumulate=False, out_dtype=None):
 
 
 # ----------------------------------------------------------------------------------------------- dense linear
+def _skinny(x, A, a_is_kr, alpha):
+    """x A^T (A [r, K]) or x A (A [K, r]) for a LoRA rank r: CUDA-core kernel for r <= 32, else the GEMM."""
+    r = A.shape[1] if a_is_kr else A.shape[0]
+    if r <= 32 and x.shape[1] % 8 == 0 and A.is_contiguous() and x.dtype == torch.bfloat16 and A.dtype == torch.bfloat16:
+        return ext.skinny_mm(x, A, a_is_kr, float(alpha))
+    return mm_nn(x, A, alpha=alpha) if a_is_kr else mm_nt(x, A, alpha=alpha)
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, A, B, scaling):
@@ -92,7 +100,7 @@ class _Linear(torch.autograd.Function):
             x2 = x2.contiguous()
         t = None
         if A is not None:
-            t = mm_nt(x2, A, alpha=scaling)           # [M, r] = s * x A^T
+            t = _skinny(x2, A, False, scaling)        # [M, r] = s * x A^T
             y = mm_nt(x2, w, lora=(t, B))
         else:
             y = mm_nt(x2, w)
@@ -109,7 +117,7 @@ class _Linear(torch.autograd.Function):
         dx = dw = dA = dB = None
         dt = None
         if A is not None:
-            dt = mm_nn(dy2, B, alpha=ctx.scaling)      # [M, r] = s * dy B
+            dt = _skinny(dy2, B, True, ctx.scaling)    # [M, r] = s * dy B
         if ctx.needs_input_grad[0]:
             dx = mm_nn(dy2, w, lora=(dt, A) if A is not None else None).view(ctx.shape)
         if ctx.needs_input_grad[1]:
@@ -302,7 +310,7 @@ class _GroupedSwiGLUMLP(torch.autograd.Function):
             dB2 = torch.empty_like(B2); _g(2, t2, True, dy, True, dB2, H, 0, plan, alpha=ws)
             grads[id(A2)], grads[id(B2)] = dA2, dB2
         # ---- SwiGLU
-        dg, du = ext.swiglu_bwd(g, u, dh)
+        dg, du = ext.swiglu_bwd(g, u, dh, plan.padded_offsets)
         # ---- up projections
         dx = torch.empty(R, H, dtype=dt, device=dev)
         _g(1, dg, False, w1, True, dx, H, F, plan, A_l=du, B_l=w3, b_mn_l=True, K_l=F, scatter=scatter)   # dg W1 + du W3

@@ -213,7 +213,8 @@ class ShardedMixtral:
 
     def __init__(self, model: MixtralForCausalLM, shard_group=None, replicate_group=None,
                  expert_dp_group=None, world_group=None, shard_experts: bool = False,
-                 sync_each_batch: bool = False, pool_slots: int = 3):
+                 sync_each_batch: bool = False, pool_slots: int = 3, resident_params: Optional[bool] = None,
+                 resident_limit_bytes: int = 16 << 30):
         self.model = model
         self.shard_group, self.replicate_group = shard_group, replicate_group
         self.expert_dp_group, self.world_group = expert_dp_group, world_group
@@ -238,7 +239,19 @@ class ShardedMixtral:
         self.is_cuda = dev.type == "cuda"
         self.comm_stream = torch.cuda.Stream(device=dev) if (self.is_cuda and self.ws > 1) else None
         self.pool = None
-        if self.ws > 1:
+        # With 180 GB per GPU the gathered dense parameters of a Mixtral-8x7B (3.2 GB in bf16) can simply stay
+        # resident: every rank keeps a full copy next to its shard and re-reads from its peers only the groups an
+        # optimizer step has changed (ZeRO-2 style).  Frozen groups are gathered once per run instead of twice per
+        # block per micro-batch.  Default: on when the full copies fit in `resident_limit_bytes`.
+        full_bytes = sum(g.padded * g.shard.element_size() for u in self.units + [self.root] for g in u.groups)
+        if resident_params is None:
+            resident_params = os.environ.get("MDT_RESIDENT_PARAMS", "1") != "0" and full_bytes <= resident_limit_bytes
+        self.resident = bool(resident_params) and self.ws > 1
+        self._param_version = 1
+        self._frozen_version = 1
+        if self.ws > 1 and self.resident:
+            self.root_buffers = None
+        elif self.ws > 1:
             n_groups = max(len(u.groups) for u in self.units)
             sizes = [max((u.groups[j].padded for u in self.units if len(u.groups) > j), default=0) for j in range(n_groups)]
             dts = self.units[0].groups[0].dtype
@@ -294,8 +307,17 @@ class ShardedMixtral:
         self._ext.barrier_arrive(self._flag_table, p.ws, p.rank, p.epoch)
         self._ext.barrier_wait(p.bases[p.rank] + self._flag_off, p.ws, p.epoch, self._status, 0)
 
+    def invalidate_gathered(self):
+        """Call after writing parameter shards by hand (checkpoint load): every resident copy is re-read."""
+        self._param_version += 1
+        self._frozen_version += 1
+        if self.peers is not None:
+            self.peer_barrier()
+
     def after_optimizer_step(self):
-        """Peers must not gather a shard that its owner is still updating."""
+        """Peers must not gather a shard that its owner is still updating; resident copies of trainable groups
+        are stale from here on."""
+        self._param_version += 1
         self.peer_barrier()
 
     # ------------------------------------------------------------------ buffers
@@ -314,6 +336,10 @@ class ShardedMixtral:
         if self.ws == 1:
             unit.buffers = [g.shard.data for g in unit.groups]
             return
+        if self.resident:
+            self._refresh_resident(unit, side_stream=True)
+            unit.buffers = unit.resident
+            return
         slot = self.pool.acquire(idx)
         self._slot[idx] = slot
         bufs = self.pool.slots[slot][:len(unit.groups)]
@@ -330,6 +356,35 @@ class ShardedMixtral:
         else:
             self._gather_into(unit, bufs)
         unit.buffers = bufs
+
+    def _refresh_resident(self, unit: FsdpUnit, side_stream: bool):
+        """Bring the unit's resident full copies up to date: groups changed since their last gather are re-read."""
+        if getattr(unit, "resident", None) is None:
+            unit.resident = [torch.empty(g.padded, dtype=g.dtype, device=self.device) for g in unit.groups]
+            unit.resident_version = [0] * len(unit.groups)
+        want = [self._param_version if g.trainable else self._frozen_version for g in unit.groups]
+        stale = [j for j in range(len(unit.groups)) if unit.resident_version[j] != want[j]]
+        if not stale:
+            return
+
+        def gather():
+            for j in stale:
+                g, buf = unit.groups[j], unit.resident[j]
+                if self.peers is not None:
+                    self._ext.ag_pull(buf[:g.padded], g.shard_table, g.ws, g.shard_numel * g.shard.element_size())
+                else:
+                    coll.all_gather_flat(buf[:g.padded], g.shard.data, g.group)
+                unit.resident_version[j] = want[j]
+        if side_stream and self.comm_stream is not None:
+            # the shards may have just been written by the optimizer on the compute stream, and earlier work on
+            # the compute stream may still read the copies that are about to be replaced
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.comm_stream):
+                gather()
+                unit.ready_event = torch.cuda.Event()
+                unit.ready_event.record(self.comm_stream)
+        else:
+            gather()
 
     def _acquire(self, idx: int, backward: bool = False):
         unit = self.units[idx]
@@ -349,6 +404,9 @@ class ShardedMixtral:
         unit = self.units[idx]
         if self.ws == 1 or unit.buffers is None:
             unit.buffers = None if self.ws > 1 else unit.buffers
+            return
+        if self.resident:
+            unit.buffers = None
             return
         ev = None
         if self.is_cuda:
@@ -437,6 +495,9 @@ class ShardedMixtral:
         root = self.root
         if self.ws == 1:
             bufs = [g.shard.data for g in root.groups]
+        elif self.resident:
+            self._refresh_resident(root, side_stream=False)
+            bufs = root.resident
         else:
             bufs = self.root_buffers
             self._gather_into(root, bufs)

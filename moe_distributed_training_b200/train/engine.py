@@ -17,6 +17,8 @@ gradients of all micro-batches are kept and clipping acts before the update.
 """
 from __future__ import annotations
 
+import gc
+
 import os
 from dataclasses import dataclass, field
 from typing import List, Optional
@@ -73,6 +75,8 @@ class Engine:
     ep_group: object = None
     max_grad_norm: Optional[float] = None
     sort_microbatches: bool = True
+    manage_gc: bool = True
+    gc_every: int = 50
     step_count: int = 0
     last: dict = field(default_factory=dict)
 
@@ -91,6 +95,20 @@ class Engine:
         return out.loss.detach()
 
     def train_step(self, microbatches: List[dict]) -> dict:
+        # A cyclic-garbage collection that starts in the middle of a step on one rank stalls every expert-parallel
+        # peer at the next MoE layer.  Collection is therefore switched off while a step runs and done between
+        # steps (generation 0 every step, a full collection every `gc_every` steps).
+        gc_was_on = gc.isenabled()
+        if self.manage_gc and gc_was_on:
+            gc.disable()
+        try:
+            return self._train_step(microbatches)
+        finally:
+            if self.manage_gc and gc_was_on:
+                gc.enable()
+                gc.collect(2 if self.step_count % self.gc_every == 0 else 0)
+
+    def _train_step(self, microbatches: List[dict]) -> dict:
         ga = len(microbatches)
         if self.world_size > 1 and self.sort_microbatches:
             # Expert-parallel ranks meet at every MoE layer, so a micro-batch costs every rank the time of the

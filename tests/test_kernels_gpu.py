@@ -154,7 +154,88 @@ def test_grouped_swiglu_mlp(ops, T, E, H, F, lora):
     ops.check_status(DEV)
 
 
+def _under_pair_policy(ops, policy, fn):
+    prev = ops.ext.gemm_set_pair_policy(policy)
+    try:
+        return fn()
+    finally:
+        ops.ext.gemm_set_pair_policy(prev)
+
+
+def test_gemm_pair_kernel_matches_single_cta_kernel(ops):
+    """The CTA-pair (cta_group::2) kernel, forced for every 256-wide tile, against the single-CTA kernel."""
+    torch.manual_seed(21)
+    cases = []
+    for M, N, K in [(300, 520, 200), (1024, 4096, 4096), (77, 264, 4096), (512, 256, 64)]:
+        x, w = _rand(M, K), _rand(N, K, scale=0.05)
+        cases.append((f"nt {M}x{N}x{K}", lambda x=x, w=w: ops.mm_nt(x, w), x.float() @ w.float().t()))
+    x, w = _rand(300, 200), _rand(200, 520, scale=0.05)
+    cases.append(("nn", lambda x=x, w=w: ops.mm_nn(x, w), x.float() @ w.float()))
+    for R, M, N in [(1000, 1024, 4096), (200, 136, 264)]:
+        a, b = _rand(R, M), _rand(R, N, scale=0.05)
+        cases.append((f"tn {R}x{M}x{N}", lambda a=a, b=b: ops.mm_tn(a, b), a.float().t() @ b.float()))
+
+        def acc(a=a, b=b):
+            out = torch.ones(a.shape[1], b.shape[1], device=DEV)
+            ops.mm_tn(a, b, out=out, alpha=0.5, accumulate=True)
+            return out
+        cases.append((f"tn accumulate {R}x{M}x{N}", acc, 1.0 + 0.5 * (a.float().t() @ b.float())))
+    for name, fn, want in cases:
+        single = _under_pair_policy(ops, 0, fn)
+        pair = _under_pair_policy(ops, 2, fn)
+        ops.check_status(DEV)
+        _close(pair, want, 2e-2, f"pair kernel {name} vs fp32")
+        _close(pair, single, 1e-3, f"pair kernel {name} vs single-CTA kernel")
+
+
+@pytest.mark.parametrize("T,E,H,F,lora", [(600, 4, 256, 512, True), (1500, 8, 1024, 2048, False), (333, 3, 512, 1024, False)])
+def test_grouped_mlp_pair_kernel_matches_single_cta_kernel(ops, T, E, H, F, lora):
+    """Row groups with odd and even numbers of 128-row blocks (idle second halves), forward and backward."""
+    torch.manual_seed(22)
+    k, r = 2, 16
+    top, plan = _plan(ops, T, k, E)
+    x = _rand(T, H)
+    ws = [_rand(E, F, H, scale=0.05) for _ in range(3)]
+    lo_t = None
+    if lora:
+        lo_t = {}
+        for name in ("w1", "w2", "w3"):
+            fin, fout = (F, H) if name == "w2" else (H, F)
+            lo_t[name] = (_rand(E, fin, r, scale=0.05), _rand(E, r, fout, scale=0.05), 2.0)
+    n_used = int(plan.padded_offsets[-1])
+    valid = (plan.src_slot[:n_used] >= 0)
+    go = torch.zeros(plan.capacity, H, device=DEV, dtype=torch.bfloat16)
+    go[:n_used][valid] = _rand(int(valid.sum()), H)
+
+    def run():
+        w = [t.clone().requires_grad_(True) for t in ws]
+        lo = None if lo_t is None else {n: (A.clone().requires_grad_(True), B.clone().requires_grad_(True), sc) for n, (A, B, sc) in lo_t.items()}
+        xg = ops.gather_rows(x, plan).detach().requires_grad_(True)
+        y = ops.grouped_swiglu_mlp(xg, w[0], w[1], w[2], plan, lo, 0.5)
+        y.backward(go[:y.shape[0]])
+        outs = [y.detach()[:n_used][valid], xg.grad[:n_used][valid]] + [t.grad for t in w]
+        if lo is not None:
+            for n in ("w1", "w2", "w3"):
+                outs += [lo[n][0].grad, lo[n][1].grad]
+        return outs
+    single = _under_pair_policy(ops, 0, run)
+    pair = _under_pair_policy(ops, 2, run)
+    ops.check_status(DEV)
+    for i, (a, b) in enumerate(zip(pair, single)):
+        _close(a, b, 2e-3, f"grouped mlp output {i}: pair vs single-CTA kernel")
+
+
 # ------------------------------------------------------------------------------------------ small ops
+@pytest.mark.parametrize("M,K,r", [(576, 4096, 16), (77, 1024, 8), (1000, 4096, 32), (5, 264, 12)])
+def test_skinny_mm(ops, M, K, r):
+    torch.manual_seed(30)
+    x, A, B = _rand(M, K), _rand(r, K, scale=0.05), _rand(K, r, scale=0.05)
+    _close(ops.ext.skinny_mm(x, A, False, 0.5), 0.5 * (x.float() @ A.float().t()), 1e-2, "skinny x A^T")
+    _close(ops.ext.skinny_mm(x, B, True, 2.0), 2.0 * (x.float() @ B.float()), 1e-2, "skinny x B")
+    xs = _rand(M, K + 64)[:, :K]          # row stride larger than K
+    _close(ops.ext.skinny_mm(xs, A, False, 1.0), xs.float() @ A.float().t(), 1e-2, "skinny strided x")
+
+
 def test_linear_lora_backward(ops):
     from moe_distributed_training_b200.ops import reference
     torch.manual_seed(6)
