@@ -366,7 +366,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
 // matrix), the leader's MMA thread reads both CTAs' shared memory, and each CTA's TMEM receives the accumulators
 // of its own 128 rows.  Per CTA and 64-deep k block that is 32 KB of operands instead of 48 KB, which is what
 // bounds the single-CTA kernel, and the ring holds 7 stages instead of 4.
-//   full_bar[s]   (leader's is used): 2 arrivals (one producer per CTA) + both CTAs' TMA bytes
+//   full_bar[s]   (leader's is used): the leader's producer arrives and announces both CTAs' TMA bytes
 //   empty_bar[s]  (one per CTA)     : arrives by the leader's commit, delivered to both CTAs
 //   tfull_bar[b]  (one per CTA)     : same, when a tile's accumulators are complete
 //   tempty_bar[b] (leader's is used): 8 arrivals, the 4 epilogue warps of each CTA
@@ -452,7 +452,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1) gem
   const int BN_OUT = p.dual ? BN / 2 : BN;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 2); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 8); }
     *abort_flag = 0;
     fence_barrier_init();
@@ -489,8 +489,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1) gem
         if (!wait_parity(&empty_bar[s], ph ^ 1, abort_flag)) { fail(ST_TIMEOUT_EMPTY); ok = false; break; }
         uint8_t* sA = smem + s * PAIR_STAGE_BYTES;
         uint8_t* sB = sA + A_BYTES;
+        // Only the leader arrives, announcing both CTAs' bytes: a cluster-scope arrive from the peer would put a
+        // memory barrier into every stage of its producer loop.  The peer's bytes may be counted before the
+        // leader's announcement (the transaction count goes negative for a moment; the phase cannot complete
+        // before the leader's arrival).
         const uint32_t bar = mapa_shared(smem_u32(&full_bar[s]), 0);
-        mbar_expect_tx_cluster(bar, PAIR_STAGE_BYTES);
+        if (cta_rank == 0) mbar_expect_tx(&full_bar[s], 2 * PAIR_STAGE_BYTES);
         const bool lora = kb >= t.num_kb;
         const int kk = (lora ? kb - t.num_kb : kb) * BK;
         const CUtensorMap* mA = lora ? &p.tmA_l : &p.tmA;
