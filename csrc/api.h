@@ -46,11 +46,15 @@ long long mdt_skinny_launch_count(void);
 // y[M, r] = alpha * x[M, K] * op(A), r <= 32: a_is_kr = 0 -> A is [r, K] (row stride lda), 1 -> A is [K, r]
 int mdt_skinny_mm(const void* x, const void* A, void* y, int M, int K, int r, long long ldx, long long lda,
                   int a_is_kr, float alpha, cudaStream_t s);
-// CTA-pair (cta_group::2) kernel selection: 0 never, 1 where the shape fills 256-row pair tiles, 2 whenever the
-// tile is 256 wide; returns the previous policy (policy < 0 only reads it).
+// Kernel for 256-wide tiles: 0 the 128-row kernel, 1 / 2 the CTA-pair (cta_group::2) kernel where the shape fills
+// 256-row tiles / always, 3 / 4 the tall single-CTA 256 x 256 kernel where it fills / always; returns the previous
+// policy (policy < 0 only reads it).
 int mdt_gemm_set_pair_policy(int policy);
 // CTA pairs resident at once on this device (0 until the pair kernel has been launched)
 int mdt_gemm_max_pairs(void);
+// Expected total rows of the row-grouped (mode 1) products this host thread issues next, for buffers sized to a
+// capacity; 0 = unknown.  Only guides the choice of tile shape.
+void mdt_gemm_rows_hint(long long rows);
 // upper bound on the pair kernel's grid, in pairs (0 = the resident maximum); for scaling measurements
 void mdt_gemm_set_pair_cap(int pairs);
 

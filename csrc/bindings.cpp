@@ -524,6 +524,12 @@ void ggemm(int mode, const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, Ten
 const OptTensor NONE = std::nullopt;
 }  // namespace
 
+// Tells the GEMM's tile-shape choice how many rows to expect in buffers that are sized for a capacity.
+struct RowsHint {
+  explicit RowsHint(int64_t rows) { mdt_gemm_rows_hint((long long)rows); }
+  ~RowsHint() { mdt_gemm_rows_hint(0); }
+};
+
 std::vector<Tensor> moe_block_fwd(const Tensor& x, const Tensor& ln_w, const Tensor& Wr, const Tensor& w1, const Tensor& w2, const Tensor& w3,
                                   double eps, int64_t top_k, int64_t E, bool grad_mode, const std::vector<int64_t>& layout,
                                   const std::vector<int64_t>& ep_ints, const std::vector<Tensor>& ep, const Tensor& status_t) {
@@ -532,6 +538,7 @@ std::vector<Tensor> moe_block_fwd(const Tensor& x, const Tensor& ln_w, const Ten
   Tensor st = status_t;
   const bool is_ep = !ep.empty();
   const int64_t T = x.size(0), H = x.size(1), El = w1.size(0), F = w1.size(1);
+  RowsHint rows_hint(is_ep ? T * top_k : 0);   // balanced routing: a rank receives about as many rows as it sends
   auto nr = rmsnorm_fwd(x, ln_w, eps);
   Tensor xn = nr[0], rstd = nr[1];
   auto rt = router_fwd(xn, Wr, top_k, true);
@@ -602,6 +609,7 @@ std::vector<Tensor> moe_block_bwd(const Tensor& dy, const std::vector<Tensor>& s
                &src_slot = state[9], &meta_c = state[10], &rr = state[11], &rp = state[12], &te = state[13], &xg = state[14], &g = state[15],
                &u = state[16], &h = state[17], &expert_sorted = state[18], &offs = state[19];
   const int64_t H = x.size(1), El = w1.size(0), F = w1.size(1);
+  RowsHint rows_hint(is_ep ? x.size(0) * top_k : 0);
   Tensor dyc = dy.contiguous();
   Tensor d_rows = gather_rows(dyc, src_slot, p_offs, E, wts.view({-1}), top_k);
   Tensor dwts = combine_wgrad(ys, dest_row, dyc, top_k);
@@ -659,6 +667,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cross_entropy", &cross_entropy);
   m.def("gemm_set_pair_policy", [](int64_t policy) { return (int64_t)mdt_gemm_set_pair_policy((int)policy); });
   m.def("gemm_set_pair_cap", [](int64_t n) { mdt_gemm_set_pair_cap((int)n); });
+  m.def("gemm_rows_hint", [](int64_t rows) { mdt_gemm_rows_hint((long long)rows); });
   m.def("gemm_max_pairs", []() { return (int64_t)mdt_gemm_max_pairs(); });
   m.def("skinny_mm", &skinny_mm);
   m.def("adamw", &adamw);

@@ -20,6 +20,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <math.h>
 #include <stdio.h>
 #include <stdlib.h>
 
@@ -663,6 +664,329 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1) gem
 }
 
 // ---------------------------------------------------------------------------------------------
+// Tall variant: one CTA computes a 256 x 256 tile as two 128-row MMAs that share the B operand.  Per 64-deep
+// k block the CTA takes in 64 KB for 256 x 256 x 64 MACs, i.e. 32 KB per 128 x 256 x 64, against 48 KB in the
+// 128 x 256 kernel, whose k blocks arrive more slowly than its MMAs retire them.  The two accumulators fill
+// all 512 TMEM columns, so the epilogue of a tile does not overlap the next tile's MMAs (its loads do); eight
+// epilogue warps (two per TMEM lane quarter, one per 128-row half) keep that phase short.
+// Roles of the 320 threads: warp 0 = TMA producer, warp 1 = MMA issuer (owns TMEM), warps 2-9 = epilogue.
+// ---------------------------------------------------------------------------------------------
+// Coalesced bf16 store of one 32-row x 32-column block held as one row per lane: the warp transposes it through a
+// 2 KB shared-memory stage (16-byte slots, XOR-swizzled so that both passes are conflict-free) and then writes
+// 64 contiguous bytes per row, eight rows per instruction, instead of 16 bytes to each of 32 rows.
+// row_ptr[i] / bit i of ok_mask describe row i*8 + lane/4, the row this lane stores in pass i.
+__device__ __forceinline__ void store32_coalesced(uint8_t* stage, const float (&v)[32], int lane, const unsigned long long (&row_ptr)[4],
+                                                  unsigned ok_mask, int col0, int N) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 out;
+    __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = __floats2bfloat162_rn(v[j * 8 + 2 * i], v[j * 8 + 2 * i + 1]);
+    *reinterpret_cast<uint4*>(stage + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = out;
+  }
+  __syncwarp();
+  const int j = lane & 3;
+  const int col = col0 + j * 8;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = i * 8 + (lane >> 2);
+    const uint4 val = *reinterpret_cast<const uint4*>(stage + row * 64 + ((j ^ ((row >> 1) & 3)) << 4));
+    if (((ok_mask >> i) & 1u) && col < N)
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(row_ptr[i]) + col) = val;
+  }
+  __syncwarp();
+}
+
+constexpr int TALL_THREADS = 320;
+constexpr int TALL_STAGES = 3;
+constexpr int TALL_BN = 256;
+constexpr int TALL_STAGE_BYTES = 2 * A_BYTES + TALL_BN * BK * 2;
+
+__global__ void __launch_bounds__(TALL_THREADS, 1) gemm_sm100_tall_kernel(const __grid_constant__ GemmParams p) {
+  constexpr int STAGES = TALL_STAGES;
+  constexpr int BN = TALL_BN;
+  constexpr int B_BYTES = BN * BK * 2;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * TALL_STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* store_stage = smem + STAGES * TALL_STAGE_BYTES + 256;   // 8 epilogue warps x 2 KB
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int BN_OUT = p.dual ? BN / 2 : BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(tfull_bar, 1);
+    mbar_init(tempty_bar, 8);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto fail = [&](int code) {
+    *abort_flag = 1;
+    if (p.status != nullptr) atomicCAS(p.status, 0, code);
+  };
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    prefetch_tensormap(&p.tmA); prefetch_tensormap(&p.tmB);
+    uint32_t it = 0;
+    PairTile t;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && (p.dual ? get_pair_tile<BN / 2>(p, tile, t) : get_pair_tile<BN>(p, tile, t)); tile += gridDim.x) {
+      const int total_kb = t.num_kb + (t.num_kb > 0 || p.mode != 2 ? t.num_kb_l : 0);
+      if (p.tile_ready != nullptr && total_kb > 0) {
+        for (int h = 0; h < (t.second_ok ? 2 : 1) && ok; ++h) {
+          const int ti = t.m0 / BM + h;
+          if (!wait_ge(p.tile_ready + ti, (unsigned)p.tile_expected[ti], MDT_GEMM_PEER_WAIT_NS)) { fail(ST_TIMEOUT_PEER); ok = false; }
+        }
+        if (!ok) break;
+        fence_proxy_async_all();
+      }
+      for (int kb = 0; kb < total_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!wait_parity(&empty_bar[s], ph ^ 1, abort_flag)) { fail(ST_TIMEOUT_EMPTY); ok = false; break; }
+        uint8_t* sA = smem + s * TALL_STAGE_BYTES;
+        uint8_t* sB = sA + 2 * A_BYTES;
+        mbar_expect_tx(&full_bar[s], TALL_STAGE_BYTES);
+        const bool lora = kb >= t.num_kb;
+        const int kk = (lora ? kb - t.num_kb : kb) * BK;
+        const CUtensorMap* mA = lora ? &p.tmA_l : &p.tmA;
+        const CUtensorMap* mB = lora ? &p.tmB_l : &p.tmB;
+        const CUtensorMap* mB2 = lora ? &p.tmB2_l : &p.tmB2;
+        const int a_mn = lora ? p.a_mn_l : p.a_mn, b_mn = lora ? p.b_mn_l : p.b_mn;
+        const int krow = (lora ? 0 : t.krow0) + kk;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int m0 = t.m0 + h * BM;
+          if (a_mn == 0) {
+            tma_load_2d(sA + h * A_BYTES, mA, &full_bar[s], kk, m0);
+          } else {
+            tma_load_2d(sA + h * A_BYTES, mA, &full_bar[s], m0, krow);
+            tma_load_2d(sA + h * A_BYTES + 8192, mA, &full_bar[s], m0 + 64, krow);
+          }
+        }
+        const int zB = (p.mode == 2) ? 0 : t.g;
+        if (b_mn == 0) {
+          if (p.dual) {
+            tma_load_3d(sB, mB, &full_bar[s], kk, t.n0, zB);
+            tma_load_3d(sB + B_BYTES / 2, mB2, &full_bar[s], kk, t.n0, zB);
+          } else {
+            tma_load_3d(sB, mB, &full_bar[s], kk, t.n0, zB);
+            tma_load_3d(sB + B_BYTES / 2, mB, &full_bar[s], kk, t.n0 + 128, zB);
+          }
+        } else {
+          if (p.dual) {
+#pragma unroll
+            for (int c = 0; c < BN / 128; ++c) {
+              tma_load_3d(sB + c * 8192, mB, &full_bar[s], t.n0 + 64 * c, krow, zB);
+              tma_load_3d(sB + B_BYTES / 2 + c * 8192, mB2, &full_bar[s], t.n0 + 64 * c, krow, zB);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_3d(sB + c * 8192, mB, &full_bar[s], t.n0 + 64 * c, krow, zB);
+          }
+        }
+      }
+    }
+    if (!ok) {  // give copies already in flight a bounded time to land before the CTA exits
+      for (int s = 0; s < STAGES; ++s) {
+        uint64_t t0 = global_timer_ns();
+        while (!mbar_try_wait(&full_bar[s], 0) && !mbar_try_wait(&full_bar[s], 1) && global_timer_ns() - t0 < 1000000ull) {}
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer
+    uint32_t it = 0, acc_it = 0;
+    PairTile t;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && (p.dual ? get_pair_tile<BN / 2>(p, tile, t) : get_pair_tile<BN>(p, tile, t)); tile += gridDim.x) {
+      const int total_kb = t.num_kb + (t.num_kb > 0 || p.mode != 2 ? t.num_kb_l : 0);
+      if (total_kb == 0) continue;
+      if (!wait_parity(tempty_bar, (acc_it & 1) ^ 1, abort_flag)) { fail(ST_TIMEOUT_TMEM_EMPTY); break; }
+      tc_fence_after();
+      for (int kb = 0; kb < total_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!wait_parity(&full_bar[s], ph, abort_flag)) { fail(ST_TIMEOUT_FULL); ok = false; break; }
+        tc_fence_after();
+        const bool lora = kb >= t.num_kb;
+        const int a_mn = lora ? p.a_mn_l : p.a_mn, b_mn = lora ? p.b_mn_l : p.b_mn;
+        const uint32_t idesc = make_idesc_bf16(BM, BN, a_mn, b_mn);
+        const uint32_t sA = smem_u32(smem + s * TALL_STAGE_BYTES);
+        const uint32_t sB = sA + 2 * A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {
+          const uint64_t db = b_mn ? make_smem_desc(sB + k * 2048, 8192, 1024) : make_smem_desc(sB + k * 32, 16, 1024);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t a0 = sA + h * A_BYTES;
+            const uint64_t da = a_mn ? make_smem_desc(a0 + k * 2048, 8192, 1024) : make_smem_desc(a0 + k * 32, 16, 1024);
+            umma_bf16(tmem_base + h * BN, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(&empty_bar[s]);   // frees the stage when these MMAs have read it
+      }
+      if (!ok) break;
+      umma_commit(tfull_bar);         // both accumulators complete
+      ++acc_it;
+    }
+  } else if (warp >= 2) {
+    // ------------------------------------------------------------------ epilogue: warp -> (lane quarter, row half)
+    const int q = warp & 3;
+    const int h = (warp - 2) >> 2;
+    uint32_t acc_it = 0;
+    PairTile t;
+    for (int tile = blockIdx.x; (p.dual ? get_pair_tile<BN / 2>(p, tile, t) : get_pair_tile<BN>(p, tile, t)); tile += gridDim.x) {
+      const int total_kb = t.num_kb + (t.num_kb > 0 || p.mode != 2 ? t.num_kb_l : 0);
+      const bool half_ok = h == 0 || t.second_ok;
+      const int row = t.m0 + h * BM + q * 32 + lane;
+      const int row_limit = (p.mode == 1) ? p.offsets[p.G] : p.M;
+      const bool row_ok = half_ok && row < row_limit;
+      long long base = (p.mode == 2 ? (long long)t.g * p.c_group_stride : 0) + (long long)row * p.ldc;
+      void* Cout = p.C;
+      int dest = -1;
+      bool store_ok = row_ok;
+      if (p.row_dest_rank != nullptr) {          // result rows go straight into peers' buffers
+        dest = row_ok ? p.row_dest_rank[row] : -1;
+        store_ok = dest >= 0;
+        if (store_ok) { Cout = reinterpret_cast<void*>(p.peer_out[dest]); base = (long long)p.row_dest_row[row] * p.ldc; }
+      }
+      if (total_kb == 0) {
+        if (!p.accumulate && row_ok) {
+          float z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          for (int c = 0; c < BN_OUT; c += 8)
+            if (t.n0 + c < p.N) store8(p.C, base + t.n0 + c, z, p.c_fp32, 0);
+        }
+        continue;
+      }
+      if (!wait_parity(tfull_bar, acc_it & 1, abort_flag)) { fail(ST_TIMEOUT_TMEM_FULL); break; }
+      __syncwarp();   // lanes may leave the wait loop at different times; the TMEM loads below are warp-aligned
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + h * BN + ((uint32_t)(q * 32) << 16);
+      // bf16 results without accumulation go out through the coalescing stage; the row this lane stores in pass i
+      // is row i*8 + lane/4 of the warp's 32, whose address and validity come from the lane that owns it
+      const bool fast = !p.c_fp32 && !p.accumulate;
+      uint8_t* stage = store_stage + (warp - 2) * 2048;
+      unsigned long long rptr[4] = {0, 0, 0, 0};
+      unsigned okm = 0;
+      if (fast) {
+        const unsigned long long mine = reinterpret_cast<unsigned long long>(reinterpret_cast<__nv_bfloat16*>(Cout) + base);
+        const int okv = (p.dual ? row_ok : store_ok) ? 1 : 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int src = i * 8 + (lane >> 2);
+          rptr[i] = __shfl_sync(0xffffffffu, mine, src);
+          okm |= (unsigned)(__shfl_sync(0xffffffffu, okv, src) & 1) << i;
+        }
+      }
+      if (p.dual) {
+        const long long d2 = reinterpret_cast<const char*>(p.C2) - reinterpret_cast<const char*>(p.C);
+        const long long d3 = reinterpret_cast<const char*>(p.C3) - reinterpret_cast<const char*>(p.C);
+#pragma unroll 1
+        for (int c = 0; c < BN / 2; c += 32) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(taddr + c, rg);
+          tmem_ld_32x32(taddr + BN / 2 + c, ru);
+          tmem_ld_wait();
+          if (fast) {
+            float hh[32], gg[32], uu[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              gg[i] = __uint_as_float(rg[i]);
+              uu[i] = __uint_as_float(ru[i]);
+              hh[i] = gg[i] / (1.0f + __expf(-gg[i])) * uu[i];
+            }
+            store32_coalesced(stage, hh, lane, rptr, okm, t.n0 + c, p.N);
+            if (p.store_gate_up) {
+              unsigned long long r2[4], r3[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) { r2[i] = rptr[i] + d2; r3[i] = rptr[i] + d3; }
+              store32_coalesced(stage, gg, lane, r2, okm, t.n0 + c, p.N);
+              store32_coalesced(stage, uu, lane, r3, okm, t.n0 + c, p.N);
+            }
+          } else if (row_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = t.n0 + c + v * 8;
+              if (col < p.N) {
+                float hh[8], gg[8], uu[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  gg[i] = __uint_as_float(rg[v * 8 + i]);
+                  uu[i] = __uint_as_float(ru[v * 8 + i]);
+                  hh[i] = gg[i] / (1.0f + __expf(-gg[i])) * uu[i];
+                }
+                store8(p.C, base + col, hh, 0, 0);
+                if (p.store_gate_up) { store8(p.C2, base + col, gg, 0, 0); store8(p.C3, base + col, uu, 0, 0); }
+              }
+            }
+          }
+          __syncwarp();   // the next TMEM load is warp-aligned
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tmem_ld_wait();
+          if (fast) {
+            float o[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(r[i]) * p.alpha;
+            store32_coalesced(stage, o, lane, rptr, okm, t.n0 + c, p.N);
+          } else if (store_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = t.n0 + c + v * 8;
+              if (col < p.N) {
+                float o[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(r[v * 8 + i]) * p.alpha;
+                store8(Cout, base + col, o, p.c_fp32, p.accumulate);
+              }
+            }
+          }
+          __syncwarp();   // the next TMEM load is warp-aligned
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar);
+      ++acc_it;
+      if (p.row_dest_rank != nullptr) {
+        // publish this warp's rows: one count per (row, column tile) and destination
+        __threadfence_system();
+        __syncwarp();
+        for (int d = 0; d < p.num_peers; ++d) {
+          const unsigned m = __ballot_sync(0xffffffffu, dest == d);
+          if (lane == 0 && m != 0) red_add_release_sys(reinterpret_cast<unsigned*>(p.peer_arrive[d]), __popc(m));
+        }
+      }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -743,6 +1067,19 @@ static cudaError_t launch(const GemmParams& p, int grid, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+static cudaError_t launch_tall(const GemmParams& p, int grid, cudaStream_t stream) {
+  constexpr int smem = TALL_STAGES * TALL_STAGE_BYTES + 1024 + 256 + 8 * 2048;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_sm100_tall_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  gemm_sm100_tall_kernel<<<grid, TALL_THREADS, smem, stream>>>(p);
+  ++g_launches;
+  return cudaGetLastError();
+}
+
 // Number of CTA pairs that can be resident at once (pairs never span GPCs, so this can be below SMs / 2); the
 // persistent grid is sized to it because tiles are assigned to pairs statically.
 static int g_max_pairs = 0;
@@ -773,13 +1110,18 @@ static cudaError_t launch_pair(const GemmParams& p, int pairs_wanted, cudaStream
   return cudaGetLastError();
 }
 
-// 0 = never (default), 1 = where the shape fills pair tiles, 2 = whenever the tile is 256 wide (tests).
-// Initial value from MDT_GEMM_PAIR; mdt_gemm_set_pair_policy() changes it.
+// Expected number of rows of the row-grouped products issued by this thread (0 = unknown); see mdt_gemm_rows_hint.
+static thread_local long long t_rows_hint = 0;
+
+// Which kernel takes the 256-wide tiles: 0 = the 128-row kernel always, 1 = the CTA-pair kernel where the shape
+// fills 256-row tiles, 2 = the CTA-pair kernel always (tests), 3 = the tall kernel where the shape fills
+// several waves of 256-row tiles (default), 4 = the tall kernel always (tests).  Initial value from MDT_GEMM_PAIR;
+// mdt_gemm_set_pair_policy() changes it.
 static int g_pair_policy = -1;
 static int pair_policy() {
   if (g_pair_policy < 0) {
     const char* e = getenv("MDT_GEMM_PAIR");
-    g_pair_policy = (e != nullptr && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 0;
+    g_pair_policy = (e != nullptr && e[0] >= '0' && e[0] <= '4') ? e[0] - '0' : 3;
   }
   return g_pair_policy;
 }
@@ -787,11 +1129,12 @@ static int pair_policy() {
 }  // namespace mdt
 
 extern "C" long long mdt_gemm_launch_count() { return mdt::g_launches; }
+extern "C" void mdt_gemm_rows_hint(long long rows) { mdt::t_rows_hint = rows; }
 extern "C" int mdt_gemm_max_pairs() { return mdt::g_max_pairs; }
 extern "C" void mdt_gemm_set_pair_cap(int pairs) { mdt::g_pair_cap = pairs; }
 extern "C" int mdt_gemm_set_pair_policy(int policy) {
   const int old = mdt::pair_policy();
-  if (policy >= 0 && policy <= 2) mdt::g_pair_policy = policy;
+  if (policy >= 0 && policy <= 4) mdt::g_pair_policy = policy;
   return old;
 }
 
@@ -825,18 +1168,37 @@ extern "C" int mdt_gemm(const MdtGemmDesc* d, cudaStream_t stream) {
   // M >= 256, and row-grouped products whose groups average at least four 128-row blocks.
   const long long rows_hint = (p.mode == 1) ? d->capacity_rows : p.M;
   const int policy = pair_policy();
-  const bool pair = BN == 256 && (policy == 2 || (policy == 1 && rows_hint >= 2 * BM &&
-                                                  (p.mode != 1 || rows_hint >= (long long)p.G * 4 * BM)));
+  const bool fills = rows_hint >= 2 * BM && (p.mode != 1 || rows_hint >= (long long)p.G * 4 * BM);
+  const bool pair = BN == 256 && (policy == 2 || (policy == 1 && fills));
+  bool tall = BN == 256 && policy == 4;
+  if (BN == 256 && policy == 3) {
+    // The tall kernel retires k blocks faster (0.70 us per 256 x 256 x 64 against 0.47 us per 128 x 256 x 64, i.e.
+    // 1.3x per flop) but exposes its epilogue and halves the number of tiles.  It is taken where neither matters:
+    // at least 2048 rows (a ragged last 256-row tile is then a small share; at ~1150 rows, the size of one
+    // micro-batch's expert input, the two tilings measured equal), at least three full waves of 128-row tiles (so
+    // that halving the tile count does not idle SMs in the last wave) and a depth of at least 32 k blocks.  Row-grouped products use the expected row count when the
+    // caller gave one (their buffers are sized for a capacity) and count half a padding block per group.
+    long long r = rows_hint;
+    if (p.mode == 1 && t_rows_hint > 0 && t_rows_hint < r) r = t_rows_hint;
+    long long grouped_depth = d->capacity_rows;          // mode 2 over row groups: the depth is the group's rows
+    if (t_rows_hint > 0 && t_rows_hint < grouped_depth) grouped_depth = t_rows_hint;
+    const double blocks = (double)r / BM + (p.mode == 1 ? 0.5 * p.G : 0.0);
+    const double nb = (double)((p.N + bn_out - 1) / bn_out) * (p.mode == 2 ? p.G : 1);
+    const double depth = (p.mode == 2 && d->offsets != nullptr) ? (double)grouped_depth / p.G : (double)p.K;
+    const double kb = ceil(depth / BK) + ceil((double)p.K_l / BK);
+    tall = r >= 16 * BM && ceil(blocks) * nb >= 3.0 * g_num_sms && kb >= 32.0;
+  }
+  const bool half_box = pair || tall;   // these kernels load B in 128-row boxes
   int rc = 0;
   // A: [a_rows, a_cols] row-major, a_cols contiguous.  K-major: rows = M, cols = K.  MN-major: rows = depth, cols = M.
   rc |= make_map(&p.tmA, d->A, d->a_cols, d->a_rows, 1, d->lda, 0, 64, d->a_mn ? 64 : BM, 2);
   // B: [G, b_rows, b_cols].  K-major: rows = N, cols = K.  MN-major: rows = depth, cols = N.
-  const uint32_t b_box_rows = d->b_mn ? 64 : (pair ? 128 : bn_out);
+  const uint32_t b_box_rows = d->b_mn ? 64 : (half_box ? 128 : bn_out);
   rc |= make_map(&p.tmB, d->B, d->b_cols, d->b_rows, p.mode == 2 ? 1 : p.G, d->ldb, d->b_group_stride, 64, b_box_rows, 3);
   if (p.dual) rc |= make_map(&p.tmB2, d->B2, d->b_cols, d->b_rows, p.G, d->ldb, d->b_group_stride, 64, b_box_rows, 3);
   if (p.K_l > 0) {
     rc |= make_map(&p.tmA_l, d->A_l, d->al_cols, d->al_rows, 1, d->lda_l, 0, 64, d->a_mn_l ? 64 : BM, 2);
-    const uint32_t bl_box_rows = d->b_mn_l ? 64 : (pair ? 128 : bn_out);
+    const uint32_t bl_box_rows = d->b_mn_l ? 64 : (half_box ? 128 : bn_out);
     rc |= make_map(&p.tmB_l, d->B_l, d->bl_cols, d->bl_rows, p.G, d->ldb_l, d->bl_group_stride, 64, bl_box_rows, 3);
     if (p.dual) rc |= make_map(&p.tmB2_l, d->B2_l, d->bl_cols, d->bl_rows, p.G, d->ldb_l, d->bl_group_stride, 64, bl_box_rows, 3);
   }
@@ -845,6 +1207,12 @@ extern "C" int mdt_gemm(const MdtGemmDesc* d, cudaStream_t stream) {
   long long rows = (p.mode == 1) ? d->capacity_rows : p.M;
   long long tiles = ((rows + BM - 1) / BM) * ((p.N + bn_out - 1) / bn_out) * (p.mode == 2 ? p.G : 1);
   int grid = (int)(tiles < g_num_sms ? (tiles < 1 ? 1 : tiles) : g_num_sms);
+  if (tall) {
+    long long t256 = ((rows + 2 * BM - 1) / (2 * BM) + (p.mode == 1 ? p.G : 0)) * ((p.N + bn_out - 1) / bn_out) * (p.mode == 2 ? p.G : 1);
+    const int g = (int)(t256 < 1 ? 1 : (t256 > g_num_sms ? g_num_sms : t256));
+    cudaError_t e3 = launch_tall(p, g, stream);
+    return e3 == cudaSuccess ? 0 : -100 - (int)e3;
+  }
   if (pair) {
     long long pairs = ((rows + 2 * BM - 1) / (2 * BM) + (p.mode == 1 ? p.G : 0)) * ((p.N + bn_out - 1) / bn_out) * (p.mode == 2 ? p.G : 1);
     const int np = (int)(pairs < 1 ? 1 : (pairs > g_num_sms ? g_num_sms : pairs));

@@ -225,6 +225,7 @@ class _MoEBlock(torch.autograd.Function):
             expert_sorted = eos.index_select(0, plan.src_slot.long()) if grad_mode else None
             par = eng.next_phase()
             rplan = eng.recv_plan(meta_c)
+            ext.gemm_rows_hint(n_slots)      # the receive buffers are sized for a capacity; expect about what was sent
             if GEMM_FUSION:
                 # the expert GEMMs take part in the exchange: the first one waits for its row tiles as they arrive,
                 # the down projection stores its result rows straight into the source ranks' buffers
@@ -242,6 +243,7 @@ class _MoEBlock(torch.autograd.Function):
                     xr = xr.clone()
                 yg = C._GroupedSwiGLUMLP.forward(mctx, xr, w1, w2, w3, rplan, lora, float(ws), wgrad_out, ids, *lora_tensors)
                 ys = eng.combine(yg, meta_c, par, n_slots, clone=grad_mode)
+            ext.gemm_rows_hint(0)
             comb = ext.combine_rows(ys, plan.dest_row, wts, k)
         comb.add_(x2)
         if grad_mode:
@@ -266,6 +268,7 @@ class _MoEBlock(torch.autograd.Function):
             par = eng.next_phase()
             rplan = mctx.plan
             n_slots = plan.dest_row.numel()
+            ext.gemm_rows_hint(n_slots)
             if GEMM_FUSION:
                 rr, rp, te = rplan.ep_meta
                 eng.dispatch(d_rows, eng.identity(d_rows.shape[0]), expert_sorted, None, meta_c, 1, par, wait=False)
@@ -280,6 +283,7 @@ class _MoEBlock(torch.autograd.Function):
                 eng.dispatch(d_rows, eng.identity(d_rows.shape[0]), expert_sorted, None, meta_c, 1, par)
                 g = C._GroupedSwiGLUMLP.backward(mctx, eng.wspace.recv_x())
                 back = eng.combine(g[0].contiguous(), meta_c, par, n_slots, clone=False)
+            ext.gemm_rows_hint(0)
             dxn = ext.combine_rows(back, plan.dest_row, None, k)
         dxr, dWr = ext.router_bwd(xn, Wr.contiguous(), idx, dwts, None, True)
         dxn.add_(dxr)

@@ -162,8 +162,10 @@ def _under_pair_policy(ops, policy, fn):
         ops.ext.gemm_set_pair_policy(prev)
 
 
-def test_gemm_pair_kernel_matches_single_cta_kernel(ops):
-    """The CTA-pair (cta_group::2) kernel, forced for every 256-wide tile, against the single-CTA kernel."""
+@pytest.mark.parametrize("policy", [2, 4], ids=["pair", "tall"])
+def test_gemm_pair_kernel_matches_single_cta_kernel(ops, policy):
+    """The CTA-pair (cta_group::2) kernel and the tall 256 x 256 kernel, forced for every 256-wide tile, against
+    the 128-row kernel."""
     torch.manual_seed(21)
     cases = []
     for M, N, K in [(300, 520, 200), (1024, 4096, 4096), (77, 264, 4096), (512, 256, 64)]:
@@ -182,14 +184,15 @@ def test_gemm_pair_kernel_matches_single_cta_kernel(ops):
         cases.append((f"tn accumulate {R}x{M}x{N}", acc, 1.0 + 0.5 * (a.float().t() @ b.float())))
     for name, fn, want in cases:
         single = _under_pair_policy(ops, 0, fn)
-        pair = _under_pair_policy(ops, 2, fn)
+        pair = _under_pair_policy(ops, policy, fn)
         ops.check_status(DEV)
         _close(pair, want, 2e-2, f"pair kernel {name} vs fp32")
         _close(pair, single, 1e-3, f"pair kernel {name} vs single-CTA kernel")
 
 
+@pytest.mark.parametrize("policy", [2, 4], ids=["pair", "tall"])
 @pytest.mark.parametrize("T,E,H,F,lora", [(600, 4, 256, 512, True), (1500, 8, 1024, 2048, False), (333, 3, 512, 1024, False)])
-def test_grouped_mlp_pair_kernel_matches_single_cta_kernel(ops, T, E, H, F, lora):
+def test_grouped_mlp_pair_kernel_matches_single_cta_kernel(ops, T, E, H, F, lora, policy):
     """Row groups with odd and even numbers of 128-row blocks (idle second halves), forward and backward."""
     torch.manual_seed(22)
     k, r = 2, 16
@@ -219,7 +222,7 @@ def test_grouped_mlp_pair_kernel_matches_single_cta_kernel(ops, T, E, H, F, lora
                 outs += [lo[n][0].grad, lo[n][1].grad]
         return outs
     single = _under_pair_policy(ops, 0, run)
-    pair = _under_pair_policy(ops, 2, run)
+    pair = _under_pair_policy(ops, policy, run)
     ops.check_status(DEV)
     for i, (a, b) in enumerate(zip(pair, single)):
         _close(a, b, 2e-3, f"grouped mlp output {i}: pair vs single-CTA kernel")
