@@ -81,6 +81,13 @@ def _load_text_dataset(path: str, tokenizer_path: str, max_seq_length: int) -> O
     return out
 
 
+def _sync_each_batch(flag: bool) -> bool:
+    """The launcher passes `gradient_accumulation_kwargs.sync_each_batch` of an accelerator config
+    (accelerator_config.json:1-4) through MDT_SYNC_EACH_BATCH; it overrides the script's default."""
+    env = os.environ.get("MDT_SYNC_EACH_BATCH")
+    return flag if env is None else env == "1"
+
+
 def run_training(
     max_seq_length: int = 4096,
     load_model_dtype: str = "bfloat16",
@@ -145,7 +152,7 @@ def run_training(
         learning_rate=learning_rate, lr_scheduler_type=lr_scheduler_type, num_warmup_steps=num_warmup_steps,
         num_training_steps=max(total_steps, 1), max_grad_norm=max_grad_norm, checkpoint=ckpt, seed=seed,
         mlp_impl="scattermoe" if use_scattermoe else "sparse", dispatch_impl=dispatch_impl,
-        sync_each_batch=sync_each_batch)
+        sync_each_batch=_sync_each_batch(sync_each_batch))
     start_step = 0
     if resume_from:
         from ..checkpoint.state import load_training_state

@@ -140,3 +140,27 @@ def test_parallel_linear_lora_matches_expert_model():
     xs = X.detach()[sorted_scattered_idxs]
     dA, dB = group_bwd_AB(go[sorted_scattered_idxs], xs, A.detach(), B.detach(), alpha / r, torch.tensor([4, 10]), 2)
     assert torch.allclose(dA, Ar.grad, atol=1e-5) and torch.allclose(dB, Br.grad, atol=1e-5)
+
+
+def test_launcher_translates_an_accelerate_config(tmp_path):
+    """accelerate.yaml + accelerator_config.json -> torchrun command line and environment."""
+    import json, os, subprocess, sys
+    import pytest
+    from moe_distributed_training_b200 import launch
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = launch._load_yaml(os.path.join(root, "accelerate.yaml"))
+    accel = json.load(open(os.path.join(root, "accelerator_config.json")))
+    plan = launch.plan_launch(cfg, ["train_fsdp1.py", "--use_megablocks_sharding"], num_processes=4, accelerator_config=accel)
+    assert "--nproc-per-node=4" in plan.command and "--nnodes=1" in plan.command
+    assert plan.command[-2:] == ["train_fsdp1.py", "--use_megablocks_sharding"]
+    assert plan.command[plan.command.index("--master-addr") + 1] == "127.0.0.1"
+    assert plan.env == {"MDT_RESIDENT_PARAMS": "0", "MDT_SYNC_EACH_BATCH": "1"}
+    cfg2 = dict(cfg, fsdp_config=dict(cfg["fsdp_config"], fsdp_sharding_strategy="SHARD_GRAD_OP"))
+    assert launch.plan_launch(cfg2, ["x.py"]).env["MDT_RESIDENT_PARAMS"] == "1"
+    for bad in ({"fsdp_sharding_strategy": 3}, {"fsdp_offload_params": True}):
+        with pytest.raises(ValueError):
+            launch.plan_launch(dict(cfg, fsdp_config=dict(cfg["fsdp_config"], **bad)), ["x.py"])
+    out = subprocess.run([sys.executable, "-m", "moe_distributed_training_b200.launch", "--config_file",
+                          os.path.join(root, "accelerate.yaml"), "--num_processes", "2", "--dry_run", "train_fsdp1.py"],
+                         capture_output=True, text=True, cwd=root, check=True)
+    assert "--nproc-per-node=2" in json.loads(out.stdout)["command"]
