@@ -1,5 +1,7 @@
 // Python bindings: torch tensors in, C launch interface (api.h) out.  No math happens here.
 #include <ATen/cuda/CUDAContext.h>
+#include <ATen/cuda/CUDAEvent.h>
+#include <c10/cuda/CUDACachingAllocator.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
@@ -448,11 +450,44 @@ std::vector<Tensor> attention_block_fwd(const Tensor& x, const std::vector<Tenso
       lo = make_lin(params, i, scalings[3]);
   auto nr = rmsnorm_fwd(x, params[0], eps);
   Tensor xn = nr[0], rstd = nr[1];
-  auto [q, tq] = lin_fwd(xn, lq, status);
-  auto [k, tk] = lin_fwd(xn, lk, status);
-  auto [v, tv] = lin_fwd(xn, lv, status);
-  Tensor qr = rope(q.view({T, Hq, d}), positions, theta, false);
-  Tensor kr = rope(k.view({T, Hkv, d}), positions, theta, false);
+  // The k and v projections have 1024 output columns: for one micro-batch that is ~20 tiles walking the whole
+  // depth, a latency-bound launch that fills a seventh of the GPU.  They run on two side streams beside the q
+  // projection (80 tiles); the three kernels fit on the 148 SMs together.
+  Tensor q, k, v, qr, kr;
+  OptTensor tq, tk, tv;
+  static const bool side_streams = []() { const char* e = getenv("MDT_QKV_STREAMS"); return !(e != nullptr && e[0] == '0'); }();
+  if (side_streams) {
+    auto main_stream = at::cuda::getCurrentCUDAStream();
+    auto s1 = at::cuda::getStreamFromPool(false, x.device().index()), s2 = at::cuda::getStreamFromPool(false, x.device().index());
+    at::cuda::CUDAEvent ready, done1, done2;
+    ready.record(main_stream);
+    auto keep = [&](const Tensor& t) { c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), main_stream); };
+    {
+      c10::cuda::CUDAStreamGuard g1(s1);
+      ready.block(s1);
+      std::tie(k, tk) = lin_fwd(xn, lk, status);
+      kr = rope(k.view({T, Hkv, d}), positions, theta, false);
+      keep(k); keep(kr); if (tk.has_value()) keep(*tk);
+      done1.record(s1);
+    }
+    {
+      c10::cuda::CUDAStreamGuard g2(s2);
+      ready.block(s2);
+      std::tie(v, tv) = lin_fwd(xn, lv, status);
+      keep(v); if (tv.has_value()) keep(*tv);
+      done2.record(s2);
+    }
+    std::tie(q, tq) = lin_fwd(xn, lq, status);
+    qr = rope(q.view({T, Hq, d}), positions, theta, false);
+    done1.block(main_stream);
+    done2.block(main_stream);
+  } else {
+    std::tie(q, tq) = lin_fwd(xn, lq, status);
+    std::tie(k, tk) = lin_fwd(xn, lk, status);
+    std::tie(v, tv) = lin_fwd(xn, lv, status);
+    qr = rope(q.view({T, Hq, d}), positions, theta, false);
+    kr = rope(k.view({T, Hkv, d}), positions, theta, false);
+  }
   Tensor v3 = v.view({T, Hkv, d});
   auto at = attention_fwd(qr, kr, v3, cu_seqlens, max_seqlen, 1.0 / std::sqrt((double)d));
   Tensor o = at[0], lse = at[1];

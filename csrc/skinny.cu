@@ -44,51 +44,77 @@ __global__ void __launch_bounds__(SK_WARPS * 32) skinny_kernel(const bf16* __res
     for (int j = 0; j < R; ++j) acc[i][j] = 0.f;
 
   for (int k = warp * 256 + lane * 8; k < K; k += SK_WARPS * 256) {
-    float xf[SK_ROWS][8];
+    // all loads of an iteration are issued before any is used: the op is latency bound (two L2 round trips per
+    // lane for K = 4096), so nothing may wait for one load at a time
+    uint4 xv[SK_ROWS];
 #pragma unroll
-    for (int i = 0; i < SK_ROWS; ++i) {
-      const uint4 v = (row0 + i < M) ? *reinterpret_cast<const uint4*>(x + (long long)(row0 + i) * ldx + k) : make_uint4(0, 0, 0, 0);
-      sk_unpack(v, xf[i]);
-    }
+    for (int i = 0; i < SK_ROWS; ++i)
+      xv[i] = (row0 + i < M) ? *reinterpret_cast<const uint4*>(x + (long long)(row0 + i) * ldx + k) : make_uint4(0, 0, 0, 0);
     if (!TRANS) {
 #pragma unroll
-      for (int j = 0; j < R; ++j) {
-        float af[8];
-        if (j < r) {
-          if (a_vec) {
-            sk_unpack(*reinterpret_cast<const uint4*>(A + (long long)j * lda + k), af);
-          } else {
-#pragma unroll
-            for (int q = 0; q < 8; ++q) af[q] = __bfloat162float(A[(long long)j * lda + k + q]);
-          }
-#pragma unroll
-          for (int i = 0; i < SK_ROWS; ++i)
-#pragma unroll
-            for (int q = 0; q < 8; ++q) acc[i][j] += xf[i][q] * af[q];
-        }
-      }
-    } else {
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        float ar[R];
-        const bf16* src = A + (long long)(k + q) * lda;
+      for (int j0 = 0; j0 < R; j0 += 16) {
+        uint4 av[16];
         if (a_vec) {
 #pragma unroll
-          for (int jv = 0; jv < R / 8; ++jv) {
-            if (jv * 8 < r) sk_unpack(*reinterpret_cast<const uint4*>(src + jv * 8), ar + jv * 8);
-            else {
-#pragma unroll
-              for (int t = 0; t < 8; ++t) ar[jv * 8 + t] = 0.f;
-            }
+          for (int j = 0; j < 16; ++j) {
+            const int jj = (j0 + j < r) ? j0 + j : r - 1;      // rows past r repeat the last one; their sums are dropped
+            av[j] = *reinterpret_cast<const uint4*>(A + (long long)jj * lda + k);
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < R; ++j) ar[j] = j < r ? __bfloat162float(src[j]) : 0.f;
+          for (int j = 0; j < 16; ++j) {
+            const int jj = (j0 + j < r) ? j0 + j : r - 1;
+            bf16* dst = reinterpret_cast<bf16*>(&av[j]);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) dst[q] = A[(long long)jj * lda + k + q];
+          }
+        }
+        float xf[SK_ROWS][8];
+#pragma unroll
+        for (int i = 0; i < SK_ROWS; ++i) sk_unpack(xv[i], xf[i]);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float af[8];
+          sk_unpack(av[j], af);
+#pragma unroll
+          for (int i = 0; i < SK_ROWS; ++i)
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[i][j0 + j] += xf[i][q] * af[q];
+        }
+      }
+    } else {
+      float xf[SK_ROWS][8];
+#pragma unroll
+      for (int i = 0; i < SK_ROWS; ++i) sk_unpack(xv[i], xf[i]);
+#pragma unroll
+      for (int jv0 = 0; jv0 < R / 8; jv0 += 2) {          // 16 outputs at a time: 8 depth rows x 2 vectors
+        uint4 av[8][2];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const bf16* src = A + (long long)(k + q) * lda;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const int jv = jv0 + t;
+            if (a_vec) {
+              av[q][t] = (jv * 8 < r) ? *reinterpret_cast<const uint4*>(src + jv * 8) : make_uint4(0, 0, 0, 0);
+            } else {
+              bf16* dst = reinterpret_cast<bf16*>(&av[q][t]);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) dst[e] = (jv * 8 + e < r) ? src[jv * 8 + e] : __float2bfloat16(0.f);
+            }
+          }
         }
 #pragma unroll
-        for (int i = 0; i < SK_ROWS; ++i)
+        for (int q = 0; q < 8; ++q)
 #pragma unroll
-          for (int j = 0; j < R; ++j) acc[i][j] += xf[i][q] * ar[j];
+          for (int t = 0; t < 2; ++t) {
+            float ar[8];
+            sk_unpack(av[q][t], ar);
+#pragma unroll
+            for (int i = 0; i < SK_ROWS; ++i)
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc[i][(jv0 + t) * 8 + e] += xf[i][q] * ar[e];
+          }
       }
     }
   }
