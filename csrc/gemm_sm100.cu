@@ -1173,20 +1173,30 @@ extern "C" int mdt_gemm(const MdtGemmDesc* d, cudaStream_t stream) {
   bool tall = BN == 256 && policy == 4;
   if (BN == 256 && policy == 3) {
     // The tall kernel retires k blocks faster (0.70 us per 256 x 256 x 64 against 0.47 us per 128 x 256 x 64, i.e.
-    // 1.3x per flop) but exposes its epilogue and halves the number of tiles.  It is taken where neither matters:
-    // at least 2048 rows (a ragged last 256-row tile is then a small share; at ~1150 rows, the size of one
-    // micro-batch's expert input, the two tilings measured equal), at least three full waves of 128-row tiles (so
-    // that halving the tile count does not idle SMs in the last wave) and a depth of at least 32 k blocks.  Row-grouped products use the expected row count when the
-    // caller gave one (their buffers are sized for a capacity) and count half a padding block per group.
+    // 1.3x per flop) but exposes its epilogue (~5 us per tile, ~14 with the SwiGLU epilogue) and halves the number
+    // of tiles, which changes how full the last wave is.  Where the row count is known (dense and depth-grouped
+    // products, and row-grouped ones whose caller gave the expected rows of a capacity-sized buffer) the two are
+    // compared by waves x time per tile; the typical win at one micro-batch's ~1300 expert rows is a product with
+    // 4096 output columns whose 160 tiles would need a second, almost empty wave.  Without a row count only
+    // products of >= 2048 rows and >= 3 waves of 128-row tiles take the tall kernel.
     long long r = rows_hint;
-    if (p.mode == 1 && t_rows_hint > 0 && t_rows_hint < r) r = t_rows_hint;
+    const bool hinted = p.mode == 1 && t_rows_hint > 0;
+    if (hinted && t_rows_hint < r) r = t_rows_hint;
     long long grouped_depth = d->capacity_rows;          // mode 2 over row groups: the depth is the group's rows
     if (t_rows_hint > 0 && t_rows_hint < grouped_depth) grouped_depth = t_rows_hint;
     const double blocks = (double)r / BM + (p.mode == 1 ? 0.5 * p.G : 0.0);
     const double nb = (double)((p.N + bn_out - 1) / bn_out) * (p.mode == 2 ? p.G : 1);
     const double depth = (p.mode == 2 && d->offsets != nullptr) ? (double)grouped_depth / p.G : (double)p.K;
     const double kb = ceil(depth / BK) + ceil((double)p.K_l / BK);
-    tall = r >= 16 * BM && ceil(blocks) * nb >= 3.0 * g_num_sms && kb >= 32.0;
+    if (p.mode != 1 || hinted) {
+      const double sms = g_num_sms;
+      const double fast_path = (!p.c_fp32 && !p.accumulate) ? 0.0 : 6.0;   // the uncoalesced epilogue costs more
+      const double t1 = ceil(ceil(blocks) * nb / sms) * (fmax(kb * 0.47, 2.0) + 1.0);
+      const double t2 = ceil(ceil(blocks / 2 + (p.mode == 1 ? 0.25 * p.G : 0.0)) * nb / sms) * (kb * 0.70 + 5.0 + (p.dual ? 9.0 : 0.0) + fast_path);
+      tall = r >= 2 * BM && kb >= 32.0 && t2 < 0.9 * t1;
+    } else {
+      tall = r >= 16 * BM && ceil(blocks) * nb >= 3.0 * g_num_sms && kb >= 32.0;
+    }
   }
   const bool half_box = pair || tall;   // these kernels load B in 128-row boxes
   int rc = 0;

@@ -75,7 +75,13 @@ __device__ __forceinline__ const bf16* stage_router_weights(const bf16* __restri
   if (!staged) return w;
   const int nv = experts * (hidden / 8);
   const uint4* src = reinterpret_cast<const uint4*>(w);
-  for (int i = threadIdx.x; i < nv; i += blockDim.x) router_w_smem[i] = src[i];
+  for (int i = threadIdx.x; i < nv; i += blockDim.x * 8) {     // eight loads in flight per thread
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) { const int idx = i + u * blockDim.x; v[u] = idx < nv ? src[idx] : make_uint4(0, 0, 0, 0); }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) { const int idx = i + u * blockDim.x; if (idx < nv) router_w_smem[idx] = v[u]; }
+  }
   __syncthreads();
   return reinterpret_cast<const bf16*>(router_w_smem);
 }
