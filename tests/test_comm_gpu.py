@@ -106,8 +106,16 @@ def test_peer_wait_gives_up_with_a_status_code(cops):
     assert int(status.item()) == 0
 
 
+@pytest.fixture(params=[0, 4], ids=["tile128", "tall"])
+def gemm_tile_policy(request, cops):
+    """Runs a test with the 128-row GEMM kernel and with the tall 256 x 256 kernel forced."""
+    prev = cops.ext.gemm_set_pair_policy(request.param)
+    yield request.param
+    cops.ext.gemm_set_pair_policy(prev)
+
+
 @pytest.mark.parametrize("ws,E,tokens", [(2, 4, [300, 77]), (4, 8, [513, 128, 700, 5])])
-def test_gemm_takes_part_in_the_exchange_emulated_ranks(cops, ws, E, tokens):
+def test_gemm_takes_part_in_the_exchange_emulated_ranks(cops, ws, E, tokens, gemm_tile_policy):
     """Grouped GEMM that waits for its row tiles on the arrival counters and stores its result rows straight
     into the source ranks' buffers, for several ranks emulated on one GPU (all sends before any GEMM)."""
     from moe_distributed_training_b200.ops.reference import RoutingPlan
