@@ -42,6 +42,9 @@ def parse():
     ap.add_argument("--max-len", type=int, default=1024)
     ap.add_argument("--dispatch", default="auto")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-recompute", action="store_true",
+                    help="keep activations instead of recomputing each block in backward (not the named configuration: "
+                         "the result is labelled gradient_checkpointing=false)")
     return ap.parse_args()
 
 
@@ -131,7 +134,8 @@ def main():
     eng = build_engine(cfg, dtype=torch.bfloat16, device_type="cuda", ep_size=ep if world > 1 else 1,
                        use_lora=use_lora, lora_r=16, lora_alpha=32 if use_lora != "none" else 16, learning_rate=5e-5,
                        lr_scheduler_type="linear", num_training_steps=total_steps, max_grad_norm=1.0, seed=0,
-                       dispatch_impl=args.dispatch, ep_max_tokens=args.max_len)
+                       dispatch_impl=args.dispatch, ep_max_tokens=args.max_len,
+                       activation_checkpointing=not args.no_recompute)
     dev = eng.device
     ga = args.grad_accum
 
@@ -200,7 +204,7 @@ def main():
             "config": {"model": "Mixtral-8x7B" + (f" (TRUNCATED to {args.layers} layers: debug, invalid)" if args.layers else ""),
                        "mode": args.mode, "global_batch": world * ga, "micro_batch": 1, "grad_accum": ga,
                        "seq_len": f"uniform[{args.min_len},{args.max_len}]", "parallelism": par,
-                       "gradient_checkpointing": True, "optimizer": "AdamW lr 5e-5 linear", "lora_r": 16 if use_lora != "none" else None,
+                       "gradient_checkpointing": not args.no_recompute, "optimizer": "AdamW lr 5e-5 linear", "lora_r": 16 if use_lora != "none" else None,
                        "l2": "working set (>= 11 GB of weights per GPU) is larger than the 126 MB L2; no explicit flush",
                        "peak_mem_gib": round(mem, 1)},
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,

@@ -113,20 +113,25 @@ __global__ void ep_counts_wait_meta_kernel(long long my_base, MdtEpLayout L, int
 }
 
 // ---------------------------------------------------------------------------------------- dispatch
-constexpr int EP_ROWS_PER_CTA = 16;
+constexpr int EP_ROWS_PER_CTA = 16;   // two rows per warp
 constexpr int EP_THREADS = 256;
 
+// One warp copies a row; eight 16-byte loads per lane are in flight before the first store.
 __device__ __forceinline__ void copy_row(const uint4* __restrict__ src, uint4* __restrict__ dst, int vecs, int lane, float scale, bool scaled) {
-  if (!scaled) {
-    for (int i = lane; i < vecs; i += 32) dst[i] = src[i];
-  } else {
-    for (int i = lane; i < vecs; i += 32) {
-      uint4 u = src[i];
-      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+  for (int i = lane; i < vecs; i += 256) {
+    uint4 v[8];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(h[j]); h[j] = __floats2bfloat162_rn(f.x * scale, f.y * scale); }
-      dst[i] = u;
+    for (int u = 0; u < 8; ++u) { const int idx = i + 32 * u; v[u] = idx < vecs ? src[idx] : make_uint4(0, 0, 0, 0); }
+    if (scaled) {
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v[u]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(h[j]); h[j] = __floats2bfloat162_rn(f.x * scale, f.y * scale); }
+      }
     }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) { const int idx = i + 32 * u; if (idx < vecs) dst[idx] = v[u]; }
   }
 }
 
@@ -143,6 +148,11 @@ __global__ void ep_dispatch_kernel(const bf16* __restrict__ x, const int* __rest
   const int total = send_start[E];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int p0 = blockIdx.x * EP_ROWS_PER_CTA;
+  // A warp copies all of its rows first and then makes them visible with one system-scope fence, instead of
+  // waiting for the peers' acknowledgements once per row; lane j remembers where the j-th row went.
+  int my_d = -1;
+  long long my_row = 0;
+  int n = 0;
   for (int p = p0 + warp; p < min(p0 + EP_ROWS_PER_CTA, total); p += nwarps) {
     const int slot = src_slot[p];
     const int e = expert_of_slot[slot];
@@ -153,14 +163,16 @@ __global__ void ep_dispatch_kernel(const bf16* __restrict__ x, const int* __rest
     uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(peer_base[d] + L.off_recv_x) + row * cols);
     const bool scaled = slot_scale != nullptr;
     copy_row(src, dst, cols / 8, lane, scaled ? __bfloat162float(slot_scale[slot]) : 1.f, scaled);
-    // rows-arrived counter of the destination's 128-row tile (read by a GEMM that waits tile by tile)
-    __threadfence_system();
-    __syncwarp();
-    if (lane == 0) {
-      unsigned* tctr = reinterpret_cast<unsigned*>(peer_base[d] + L.off_tile_ctr) + (long long)parity * (L.capacity_rows / 128) + row / 128;
-      red_add_release_sys(tctr, 1u);
-      atomicAdd(&sent[d], 1u);
-    }
+    if (lane == n) { my_d = d; my_row = row; }
+    ++n;
+  }
+  // rows-arrived counters of the destinations' 128-row tiles (read by a GEMM that waits tile by tile)
+  __threadfence_system();
+  __syncwarp();
+  if (lane < n) {
+    unsigned* tctr = reinterpret_cast<unsigned*>(peer_base[my_d] + L.off_tile_ctr) + (long long)parity * (L.capacity_rows / 128) + my_row / 128;
+    red_add_release_sys(tctr, 1u);
+    atomicAdd(&sent[my_d], 1u);
   }
   __threadfence_system();
   __syncthreads();

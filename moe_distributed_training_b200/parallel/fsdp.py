@@ -102,6 +102,13 @@ class FlatParamGroup:
             self._installed_key = key
         return entry[1]
 
+    def installed_leaves(self) -> List[torch.Tensor]:
+        """Autograd-leaf views of the buffer that is currently installed (empty for frozen groups)."""
+        if self.full is None:
+            return []
+        entry = self.__dict__.get("_view_cache", {}).get(self.full.data_ptr())
+        return entry[1] if entry is not None else []
+
     def flat_grad(self, grads: List[Optional[torch.Tensor]], out: torch.Tensor) -> torch.Tensor:
         """Write per-parameter grads into the flat layout (zeros where a grad is missing)."""
         for (mod, name, shape, n, o), g in zip(self.specs, grads):
@@ -214,7 +221,7 @@ class ShardedMixtral:
     def __init__(self, model: MixtralForCausalLM, shard_group=None, replicate_group=None,
                  expert_dp_group=None, world_group=None, shard_experts: bool = False,
                  sync_each_batch: bool = False, pool_slots: int = 3, resident_params: Optional[bool] = None,
-                 resident_limit_bytes: int = 16 << 30):
+                 resident_limit_bytes: int = 16 << 30, recompute: bool = True):
         self.model = model
         self.shard_group, self.replicate_group = shard_group, replicate_group
         self.expert_dp_group, self.world_group = expert_dp_group, world_group
@@ -249,6 +256,12 @@ class ShardedMixtral:
         self.resident = bool(resident_params) and self.ws > 1
         self._param_version = 1
         self._frozen_version = 1
+        # Block recomputation (the reference wraps every decoder block in an activation-checkpoint wrapper,
+        # train_accelerate_fsdp2.py:206-224) is the default.  With `recompute=False` the blocks run under autograd
+        # directly and keep their activations (a few GB per micro-batch for Mixtral-8x7B); that needs parameter
+        # buffers that stay valid until the backward pass, i.e. resident copies or a single rank.
+        self.recompute = bool(recompute) or not (self.resident or self.ws == 1)
+        self._direct_units = set()
         if self.ws > 1 and self.resident:
             self.root_buffers = None
         elif self.ws > 1:
@@ -514,6 +527,13 @@ class ShardedMixtral:
     def run_layer(self, idx, layer, x, batch: PackedBatch):
         self._acquire(idx)
         self._prefetch(idx + 1)
+        if torch.is_grad_enabled() and not self.recompute:
+            # activations are kept: the block is part of the autograd graph; the gradients of its flat-parameter
+            # views are collected in finish_microbatch()
+            self._direct_units.add(idx)
+            y = layer(x, batch)
+            self._release(idx)
+            return y
         if torch.is_grad_enabled():
             shards = [g.shard for g in self.units[idx].groups if g.trainable]
             local = [p for p in self.units[idx].local_params if p.requires_grad]
@@ -537,6 +557,17 @@ class ShardedMixtral:
             for leaf in self._root_leaves:
                 leaf.grad = None
         self._root_leaves = []
+        for idx in sorted(self._direct_units, reverse=True):
+            unit = self.units[idx]
+            tg = unit.trainable_group
+            if tg is not None:
+                leaves = tg.installed_leaves()
+                grads = [leaf.grad for leaf in leaves]
+                if any(gr is not None for gr in grads):
+                    self._reduce_unit_grads(unit, grads)
+                for leaf in leaves:
+                    leaf.grad = None
+        self._direct_units.clear()
         for idx in list(self._slot):
             self._release(idx)
 

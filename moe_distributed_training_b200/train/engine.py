@@ -159,7 +159,8 @@ def build_engine(cfg: MixtralConfig, *, dtype: torch.dtype = torch.bfloat16, dev
                  max_grad_norm: Optional[float] = 1.0, weight_decay: float = 0.01,
                  checkpoint: Optional[str] = None, seed: int = 0, mlp_impl: str = "sparse",
                  dispatch_impl: str = "auto", sync_each_batch: bool = False,
-                 optimizer_state_dtype: Optional[torch.dtype] = None, ep_max_tokens: int = 4096) -> Engine:
+                 optimizer_state_dtype: Optional[torch.dtype] = None, ep_max_tokens: int = 4096,
+                 activation_checkpointing: bool = True) -> Engine:
     rank, world, device = init_distributed(device_type)
     ep_size = ep_size or 1
     if ep_size > 1 and world % ep_size != 0:
@@ -214,7 +215,8 @@ def build_engine(cfg: MixtralConfig, *, dtype: torch.dtype = torch.bfloat16, dev
         # accumulator would be 4 bytes x 46.7 G parameters, so gradients are reduce-scattered every micro-batch
         sync_each_batch = True
     runner = ShardedMixtral(model, shard_group, replicate_group, expert_dp_group, world_group,
-                            shard_experts=shard_experts, sync_each_batch=sync_each_batch)
+                            shard_experts=shard_experts, sync_each_batch=sync_each_batch,
+                            recompute=activation_checkpointing)
     params = [p for p in model.parameters() if p.requires_grad]
     opt = FusedAdamW(params, lr=learning_rate, weight_decay=weight_decay, state_dtype=optimizer_state_dtype)
     sched = get_scheduler(lr_scheduler_type, opt, num_warmup_steps, num_training_steps)

@@ -115,6 +115,7 @@ def run_training(
     device_type: str = "cuda",
     dispatch_impl: str = "auto",
     sync_each_batch: bool = False,
+    activation_checkpointing: bool = True,
     seed: int = 0,
     save_path: Optional[str] = None,
     resume_from: Optional[str] = None,
@@ -152,7 +153,7 @@ def run_training(
         learning_rate=learning_rate, lr_scheduler_type=lr_scheduler_type, num_warmup_steps=num_warmup_steps,
         num_training_steps=max(total_steps, 1), max_grad_norm=max_grad_norm, checkpoint=ckpt, seed=seed,
         mlp_impl="scattermoe" if use_scattermoe else "sparse", dispatch_impl=dispatch_impl,
-        sync_each_batch=_sync_each_batch(sync_each_batch))
+        sync_each_batch=_sync_each_batch(sync_each_batch), activation_checkpointing=activation_checkpointing)
     start_step = 0
     if resume_from:
         from ..checkpoint.state import load_training_state

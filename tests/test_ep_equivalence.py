@@ -37,6 +37,17 @@ def _run(rank, world, mode, steps):
               lr_scheduler_type="constant")
     if mode == "ep":
         eng = build_engine(cfg, ep_size=world, **kw)
+    elif mode == "ep-pool":
+        import os
+        os.environ["MDT_RESIDENT_PARAMS"] = "0"     # gather per use through the buffer pool
+        eng = build_engine(cfg, ep_size=world, **kw)
+        assert not eng.runner.resident
+    elif mode == "ep-keep-activations":
+        eng = build_engine(cfg, ep_size=world, activation_checkpointing=False, **kw)
+        assert eng.runner.resident and not eng.runner.recompute
+    elif mode == "ep-lora-keep-activations":
+        eng = build_engine(cfg, ep_size=world, use_lora="all", activation_checkpointing=False, **kw)
+        assert not eng.runner.recompute
     elif mode == "tp":
         eng = build_engine(cfg, ep_size=2, use_tp_sharding=True, **kw)
     elif mode == "fsdp":
@@ -103,6 +114,43 @@ def test_ep2_matches_unsharded():
     for rank, (losses, grads, ep_rank) in enumerate(res):
         assert abs(losses[0] - ref_losses[rank]) < 1e-5
         _compare(ref_grads, grads, cfg, ep_rank, 2)
+
+
+def test_ep2_gather_per_use_matches_unsharded():
+    """Parameters re-gathered for every use of a block (buffer pool) instead of resident full copies."""
+    ref_losses, ref_grads, cfg = _reference(2)
+    res = run_distributed(_run, 2, "ep-pool", 1)
+    for rank, (losses, grads, ep_rank) in enumerate(res):
+        assert abs(losses[0] - ref_losses[rank]) < 1e-5
+        _compare(ref_grads, grads, cfg, ep_rank, 2)
+
+
+def test_ep2_without_recomputation_matches_unsharded():
+    """Blocks run under autograd directly (activations kept) and give the same gradients."""
+    ref_losses, ref_grads, cfg = _reference(2)
+    res = run_distributed(_run, 2, "ep-keep-activations", 1)
+    for rank, (losses, grads, ep_rank) in enumerate(res):
+        assert abs(losses[0] - ref_losses[rank]) < 1e-5
+        _compare(ref_grads, grads, cfg, ep_rank, 2)
+    ref_losses, ref_grads, cfg = _reference(2, use_lora="all")
+    res = run_distributed(_run, 2, "ep-lora-keep-activations", 1)
+    for rank, (losses, grads, ep_rank) in enumerate(res):
+        assert abs(losses[0] - ref_losses[rank]) < 1e-5
+        _compare(ref_grads, grads, cfg, ep_rank, 2)
+
+
+def test_single_rank_without_recomputation_matches_recomputation():
+    from moe_distributed_training_b200.train.engine import build_engine
+    _, ref_grads, cfg = _reference(1)
+    torch.manual_seed(0)
+    eng = build_engine(cfg, dtype=torch.float32, device_type="cpu", max_grad_norm=None, seed=0, activation_checkpointing=False)
+    assert not eng.runner.recompute
+    eng.forward_backward(_rank_batch(cfg, 0), 1.0)
+    eng.runner.reduce_gradients()
+    grads = _collect(eng)
+    assert set(grads) == set(ref_grads)
+    for name, g in grads.items():
+        assert (g - ref_grads[name]).abs().max().item() <= 2e-6 + 1e-4 * ref_grads[name].abs().max().item(), name
 
 
 def test_fsdp2_no_ep_matches_unsharded():

@@ -37,6 +37,7 @@ def main(
     device_type: str = "cuda",
     dispatch_impl: str = "auto",
     sync_each_batch: bool = False,
+    activation_checkpointing: bool = True,
     seed: int = 0,
     save_path: str = None,
     resume_from: str = None,

@@ -48,7 +48,7 @@ def main(
         learning_rate=learning_rate, truncate_model_for_debug=truncate_model_for_debug,
         expert_degree=None, use_lora="none", model_name_or_path=model_name_or_path, model_preset=model_preset,
         data_path=data_path, num_synthetic_examples=num_synthetic_examples, device_type=device_type,
-        sync_each_batch=True, seed=seed, max_steps=max_steps,
+        sync_each_batch=True, seed=seed, max_steps=max_steps, activation_checkpointing=gradient_checkpointing,
         save_path=None if save_strategy == "no" else output_dir, sharding_strategy="fsdp1")
 
 
