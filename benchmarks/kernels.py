@@ -40,6 +40,8 @@ def main():
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--ffn", type=int, default=14336)
     ap.add_argument("--out", default="")
+    ap.add_argument("--tilings", action="store_true",
+                    help="only compare the three GEMM tilings (128-row, CTA pair, tall) on a few shapes")
     args = ap.parse_args()
     from moe_distributed_training_b200.ops import cuda_ops as ops
     peaks = {}
@@ -62,6 +64,22 @@ def main():
             r["gbs"] = round(bytes_ / ms / 1e6, 1); r["frac_of_copy_peak"] = round(bytes_ / ms / 1e6 / peak_bw, 3)
         res[name] = r
         print(name, r, flush=True)
+
+    if args.tilings:
+        for (M, N, K) in [(8192, 8192, 8192), (8192, 8192, 512), (1152, 4096, 4096), (1280, 14336, 4096), (1280, 4096, 14336),
+                          (4096, 4096, 4096)]:
+            x, w = torch.randn(M, K, device=dev, dtype=bf) * 0.1, torch.randn(N, K, device=dev, dtype=bf) * 0.1
+            out = torch.empty(M, N, device=dev, dtype=bf)
+            for name, policy in (("tile128", 0), ("pair", 2), ("tall", 4)):
+                prev = ops.ext.gemm_set_pair_policy(policy)
+                report(f"gemm_nt_{M}x{N}x{K}_{name}", timeit(lambda: ops.mm_nt(x, w, out=out), flush=flush), flops=2.0 * M * N * K)
+                ops.ext.gemm_set_pair_policy(prev)
+            del x, w, out
+        ops.check_status(dev)
+        if args.out:
+            os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
+            json.dump(res, open(args.out, "w"), indent=1)
+        return
 
     # dense GEMMs (attention projections at T tokens) and a square reference point
     for (M, N, K) in [(8192, 8192, 8192), (T, 4096, 4096), (T, 32000, 4096)]:
