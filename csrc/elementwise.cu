@@ -250,23 +250,27 @@ template <typename T> __device__ __forceinline__ void stf(T* p, long long i, flo
 template <> __device__ __forceinline__ void stf<float>(float* p, long long i, float v) { p[i] = v; }
 template <> __device__ __forceinline__ void stf<bf16>(bf16* p, long long i, float v) { p[i] = __float2bfloat16(v); }
 
+// bias corrections enter as reciprocals (ibc1 = 1 / (1 - beta1^t), ibc2 likewise) so that the update costs one
+// square root and one division per element; both use the fast single-precision forms, whose error (a few ulp of
+// fp32) is far below the bf16 resolution of the parameters and moments they are rounded to
 __device__ __forceinline__ void adam_update(float& p, float g, float& m, float& v, float lr, float b1, float b2, float eps,
-                                            float wd, float bc1, float bc2, float gscale) {
+                                            float wd, float ibc1, float ibc2, float gscale) {
   const float gg = g * gscale;
   m = b1 * m + (1.f - b1) * gg;
   v = b2 * v + (1.f - b2) * gg * gg;
-  const float denom = sqrtf(v / bc2) + eps;
-  p = p * (1.f - lr * wd) - lr * (m / bc1) / denom;
+  const float denom = __fsqrt_rn(v * ibc2) + eps;
+  p = p * (1.f - lr * wd) - __fdividef(lr * (m * ibc1), denom);
 }
 __device__ __forceinline__ bool aligned16(const void* a, const void* b, const void* c, const void* d) {
   return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) |
            reinterpret_cast<uintptr_t>(d)) & 15) == 0;
 }
 
-// One launch for all tensors (blockIdx.y = tensor).  All-bf16, 16-byte aligned tensors go eight elements
-// per thread through 128-bit loads, two vectors in flight; everything else, and the tail, element by element.
-__global__ void __launch_bounds__(256, 2) adamw_kernel(const MdtAdamTensor* __restrict__ tensors, float lr, float b1, float b2,
-                                                    float eps, float wd, float bc1, float bc2, float gscale) {
+// One launch for all tensors (blockIdx.y = tensor).  All-bf16, 16-byte aligned tensors go eight elements per
+// thread and iteration through 128-bit loads (four loads in flight per thread, 32 warps per SM); everything else,
+// and the tail, element by element.
+__global__ void __launch_bounds__(256, 4) adamw_kernel(const MdtAdamTensor* __restrict__ tensors, float lr, float b1, float b2,
+                                                       float eps, float wd, float ibc1, float ibc2, float gscale) {
   const MdtAdamTensor t = tensors[blockIdx.y];
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
@@ -277,34 +281,18 @@ __global__ void __launch_bounds__(256, 2) adamw_kernel(const MdtAdamTensor* __re
     const uint4* __restrict__ gp = reinterpret_cast<const uint4*>(t.g);
     uint4* __restrict__ mp = reinterpret_cast<uint4*>(t.m);
     uint4* __restrict__ vp = reinterpret_cast<uint4*>(t.v);
-    for (long long i = tid; i < nv; i += 2 * nthreads) {
-      const long long i2 = i + nthreads;
-      const bool two = i2 < nv;
-      uint4 P0 = pp[i], G0 = __ldcs(gp + i), M0 = mp[i], V0 = vp[i];
-      uint4 P1 = P0, G1 = G0, M1 = M0, V1 = V0;
-      if (two) { P1 = pp[i2]; G1 = __ldcs(gp + i2); M1 = mp[i2]; V1 = vp[i2]; }
-      bf162* ph = reinterpret_cast<bf162*>(&P0); const bf162* gh = reinterpret_cast<const bf162*>(&G0);
-      bf162* mh = reinterpret_cast<bf162*>(&M0); bf162* vh = reinterpret_cast<bf162*>(&V0);
+    for (long long i = tid; i < nv; i += nthreads) {
+      uint4 P = pp[i], G = __ldcs(gp + i), M = mp[i], V = vp[i];
+      bf162* ph = reinterpret_cast<bf162*>(&P); const bf162* gh = reinterpret_cast<const bf162*>(&G);
+      bf162* mh = reinterpret_cast<bf162*>(&M); bf162* vh = reinterpret_cast<bf162*>(&V);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         float2 p = __bfloat1622float2(ph[j]), g = __bfloat1622float2(gh[j]), m = __bfloat1622float2(mh[j]), v = __bfloat1622float2(vh[j]);
-        adam_update(p.x, g.x, m.x, v.x, lr, b1, b2, eps, wd, bc1, bc2, gscale);
-        adam_update(p.y, g.y, m.y, v.y, lr, b1, b2, eps, wd, bc1, bc2, gscale);
+        adam_update(p.x, g.x, m.x, v.x, lr, b1, b2, eps, wd, ibc1, ibc2, gscale);
+        adam_update(p.y, g.y, m.y, v.y, lr, b1, b2, eps, wd, ibc1, ibc2, gscale);
         ph[j] = __floats2bfloat162_rn(p.x, p.y); mh[j] = __floats2bfloat162_rn(m.x, m.y); vh[j] = __floats2bfloat162_rn(v.x, v.y);
       }
-      pp[i] = P0; mp[i] = M0; vp[i] = V0;
-      if (two) {
-        ph = reinterpret_cast<bf162*>(&P1); gh = reinterpret_cast<const bf162*>(&G1);
-        mh = reinterpret_cast<bf162*>(&M1); vh = reinterpret_cast<bf162*>(&V1);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float2 p = __bfloat1622float2(ph[j]), g = __bfloat1622float2(gh[j]), m = __bfloat1622float2(mh[j]), v = __bfloat1622float2(vh[j]);
-          adam_update(p.x, g.x, m.x, v.x, lr, b1, b2, eps, wd, bc1, bc2, gscale);
-          adam_update(p.y, g.y, m.y, v.y, lr, b1, b2, eps, wd, bc1, bc2, gscale);
-          ph[j] = __floats2bfloat162_rn(p.x, p.y); mh[j] = __floats2bfloat162_rn(m.x, m.y); vh[j] = __floats2bfloat162_rn(v.x, v.y);
-        }
-        pp[i2] = P1; mp[i2] = M1; vp[i2] = V1;
-      }
+      pp[i] = P; mp[i] = M; vp[i] = V;
     }
     done = nv * 8;
   }
@@ -313,7 +301,7 @@ __global__ void __launch_bounds__(256, 2) adamw_kernel(const MdtAdamTensor* __re
     const float g = t.g_fp32 ? ldf((const float*)t.g, i) : ldf((const bf16*)t.g, i);
     float m = t.s_fp32 ? ldf((const float*)t.m, i) : ldf((const bf16*)t.m, i);
     float v = t.s_fp32 ? ldf((const float*)t.v, i) : ldf((const bf16*)t.v, i);
-    adam_update(p, g, m, v, lr, b1, b2, eps, wd, bc1, bc2, gscale);
+    adam_update(p, g, m, v, lr, b1, b2, eps, wd, ibc1, ibc2, gscale);
     if (t.p_fp32) stf((float*)t.p, i, p); else stf((bf16*)t.p, i, p);
     if (t.s_fp32) { stf((float*)t.m, i, m); stf((float*)t.v, i, v); }
     else { stf((bf16*)t.m, i, m); stf((bf16*)t.v, i, v); }
@@ -462,8 +450,8 @@ extern "C" int mdt_cross_entropy(void* logits, const long long* labels, float* l
 extern "C" int mdt_adamw(const MdtAdamTensor* tensors_device, int num_tensors, long long max_n, float lr, float beta1, float beta2,
                          float eps, float weight_decay, float bc1, float bc2, float grad_scale, cudaStream_t s) {
   if (num_tensors == 0) return 0;
-  dim3 grid(grid_for((max_n + 15) / 16, 256, 148 * 8), num_tensors);
-  adamw_kernel<<<grid, 256, 0, s>>>(tensors_device, lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale);
+  dim3 grid(grid_for((max_n + 7) / 8, 256, 148 * 16), num_tensors);
+  adamw_kernel<<<grid, 256, 0, s>>>(tensors_device, lr, beta1, beta2, eps, weight_decay, 1.0f / bc1, 1.0f / bc2, grad_scale);
   MDT_CHECK_LAUNCH();
   return 0;
 }
