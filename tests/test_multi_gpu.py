@@ -34,3 +34,23 @@ def test_fused_exchange_matches_nccl_exchange(tmp_path, mode):
         for la, lb in zip(a["losses"], b["losses"]):
             assert abs(la - lb) < 2e-2 * abs(la), (a, b)
         assert abs(a["checksum"] - b["checksum"]) < 1e-3 * abs(a["checksum"]), (a, b)
+
+
+def test_rank_that_leaves_between_steps_is_detected_on_the_host(tmp_path):
+    """A rank exits between two steps (nothing of its in flight); the others see it in the store before their next
+    launch, raise RankFailure on the host, and their CUDA contexts stay usable (status word clean)."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    n = 2
+    out = str(tmp_path / "res_exit.json")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", "29640", os.path.join(HERE, "multi_gpu_worker.py"), out, "rank-exit"]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    res = [json.load(open(f"{out}.rank{r}")) for r in range(n)]
+    assert res[n - 1].get("left") is True
+    for r in range(n - 1):
+        assert res[r]["detected"] == [n - 1], res[r]
+        assert res[r]["step_count"] == 1          # the second step never started
