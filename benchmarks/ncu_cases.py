@@ -1,6 +1,6 @@
 """Small single-GPU cases for profiler captures: one kernel family per case, a handful of launches.
 
-    python benchmarks/ncu_cases.py gemm|gemm_pair|expert_mlp|attention|dispatch
+    python benchmarks/ncu_cases.py gemm|gemm_pair|expert_mlp|attention|dispatch|gemm_exchange
 
 Sizes keep the working set above the 126 MB L2 where DRAM figures matter, but far below a GB of launches.
 """
@@ -66,6 +66,45 @@ def main():
                 C.ext.ep_combine_send(w.recv_x(), metas[r], w.peer_base, w.layout, r, w.capacity_rows, par)
             for r, w in enumerate(spaces):
                 C.ext.ep_wait_rows(w.my_base, w.layout, metas[r], par, status, 1)
+    elif case == "gemm_exchange":
+        # The down-projection-shaped grouped GEMM as it runs inside the expert-parallel exchange: its producer waits
+        # per 128-row tile on counters the dispatch kernel raised, and its epilogue stores every result row into the
+        # buffer of the rank that sent the token and raises that rank's arrival counter.  Two ranks emulated on one
+        # GPU: both ranks' sends are issued before any GEMM, so no launch waits for a later one.
+        from moe_distributed_training_b200.ops.reference import RoutingPlan
+        from moe_distributed_training_b200.parallel import symm
+        ws, E, k, H, N, T = 2, 2, 2, 4096, 4096, 4096
+        El = E // ws
+        spaces_out = symm.emulate_ep_workspaces(ws, E, N, T, k, dev)
+        spaces_in = symm.emulate_ep_workspaces(ws, E, H, T, k, dev)
+        status = C.status_tensor(dev)
+        W = torch.randn(E, N, H, device=dev, dtype=bf) * 0.02
+        xs = [torch.randn(T, H, device=dev, dtype=bf) for _ in range(ws)]
+        tops = [torch.randn(T, E, device=dev).topk(k, -1).indices.int() for _ in range(ws)]
+        plans = [C.make_plan(tp, E, 1, tp.numel()) for tp in tops]
+        off = [int(v) for v in C.ext.ep_meta_offsets(ws, E)]
+        metas = [torch.zeros(off[8], dtype=torch.int32, device=dev) for _ in range(ws)]
+        for epoch in (1, 2, 3):
+            par = epoch & 1
+            for r, w in enumerate(spaces_in):
+                C.ext.ep_counts_send(plans[r].tokens_per_expert, w.peer_base, w.layout, r, par, epoch)
+            for r, w in enumerate(spaces_in):
+                C.ext.ep_counts_wait_meta(w.my_base, w.layout, r, par, epoch, metas[r], status)
+            for r, w in enumerate(spaces_in):
+                C.ext.ep_dispatch(xs[r], plans[r].src_slot, tops[r].reshape(-1).contiguous(), None, metas[r], w.peer_base, w.layout, k, par)
+            for r, w in enumerate(spaces_in):
+                C.ext.ep_recv_prepare(w.my_base, w.layout, metas[r], H, par, status, False)
+            for r, (wi, wo) in enumerate(zip(spaces_in, spaces_out)):
+                rr, rp, te = C.ext.ep_fused_meta(metas[r], wi.layout, r)
+                m = metas[r]
+                rplan = RoutingPlan(m[off[1]:off[1] + El], m[off[2]:off[2] + El + 1], None, None, 1, El, capacity_rows=wi.capacity_rows)
+                peer_out = torch.tensor([b + wo.layout[9] for b in wo.bases], dtype=torch.int64, device=dev)
+                peer_arr = torch.tensor([b + wo.layout[7] + 4 * par for b in wo.bases], dtype=torch.int64, device=dev)
+                dummy = torch.empty(wi.capacity_rows, N, dtype=bf, device=dev)
+                C._g(1, wi.recv_x(), False, W[r * El:(r + 1) * El], False, dummy, N, H, rplan,
+                     wait=(wi.tile_counters(par), te), scatter=(rr, rp, peer_out, peer_arr))
+            for r, wo in enumerate(spaces_out):
+                C.ext.ep_wait_rows(wo.my_base, wo.layout, metas[r], par, status, (N + 255) // 256)
     else:
         raise SystemExit("unknown case")
     torch.cuda.synchronize()
