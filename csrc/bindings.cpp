@@ -565,14 +565,35 @@ struct RowsHint {
   ~RowsHint() { mdt_gemm_rows_hint(0); }
 };
 
+// ckpt: 0 = plain call.  1 = graph-free first pass of a block that will be recomputed: everything the backward pass
+// needs from the token exchange is returned as well (the `stash`: routing, counts, received rows, returned expert
+// outputs).  2 = the recomputation, given that stash: only RMSNorm and the gate/up GEMM run again (for the SwiGLU
+// inputs); there is no second dispatch, down projection or combine, and the returned block output is not computed
+// (the backward pass does not read it).
+// Returns {out, tokens_per_expert} (+ stash when ckpt == 1), or with grad_mode the state list that moe_block_bwd takes.
 std::vector<Tensor> moe_block_fwd(const Tensor& x, const Tensor& ln_w, const Tensor& Wr, const Tensor& w1, const Tensor& w2, const Tensor& w3,
                                   double eps, int64_t top_k, int64_t E, bool grad_mode, const std::vector<int64_t>& layout,
-                                  const std::vector<int64_t>& ep_ints, const std::vector<Tensor>& ep, const Tensor& status_t) {
+                                  const std::vector<int64_t>& ep_ints, const std::vector<Tensor>& ep, const Tensor& status_t,
+                                  int64_t ckpt, const std::vector<Tensor>& stash) {
   c10::cuda::CUDAGuard guard(x.device());
   OptTensor status = status_t;
   Tensor st = status_t;
-  const bool is_ep = !ep.empty();
   const int64_t T = x.size(0), H = x.size(1), El = w1.size(0), F = w1.size(1);
+  if (ckpt == 2) {
+    TORCH_CHECK(grad_mode && stash.size() == 14, "moe_block_fwd: recomputation needs the stash of the first pass");
+    const Tensor &tpe = stash[0], &wts = stash[1], &idx = stash[2], &ys = stash[3], &p1 = stash[4], &p2 = stash[5], &p3 = stash[6],
+                 &meta_c = stash[7], &rr = stash[8], &rp = stash[9], &te = stash[10], &xg = stash[11], &expert_sorted = stash[12],
+                 &offs = stash[13];
+    RowsHint rows_hint(meta_c.numel() > 0 ? T * top_k : 0);
+    auto nr = rmsnorm_fwd(x, ln_w, eps);
+    const int64_t R = xg.size(0);
+    Tensor h = torch::empty({R, F}, x.options()), g = torch::empty({R, F}, x.options()), u = torch::empty({R, F}, x.options());
+    ggemm(1, xg, false, w1, false, h, R, F, H, El, offs, R, w3, NONE, NONE, false, 0, g, u, false, 1.0, status, NONE, NONE, NONE, NONE, NONE, NONE);
+    Tensor out = torch::empty({T, H}, x.options());
+    return {out, tpe, nr[1], nr[0], wts, idx, ys, p1, p2, p3, meta_c, rr, rp, te, xg, g, u, h, expert_sorted, offs};
+  }
+  const bool is_ep = !ep.empty();
+  const bool keep = grad_mode || ckpt == 1;      // tensors of the exchange outlive this call
   RowsHint rows_hint(is_ep ? T * top_k : 0);   // balanced routing: a rank receives about as many rows as it sends
   auto nr = rmsnorm_fwd(x, ln_w, eps);
   Tensor xn = nr[0], rstd = nr[1];
@@ -600,7 +621,7 @@ std::vector<Tensor> moe_block_fwd(const Tensor& x, const Tensor& ln_w, const Ten
     auto fm = ep_fused_meta(meta_c, layout, rank);
     rr = fm[0]; rp = fm[1]; te = fm[2];
     Tensor eos = idx.view({-1});
-    if (grad_mode) expert_sorted = eos.index_select(0, plan[3].to(at::kLong));
+    if (keep) expert_sorted = eos.index_select(0, plan[3].to(at::kLong));
     ep_dispatch(xn, plan[3], eos, NONE, meta_c, ep[0], layout, top_k, dpar);
     ep_recv_prepare(my_base, layout, meta_c, H, dpar, st, false);
     xg = ep[4];
@@ -614,7 +635,7 @@ std::vector<Tensor> moe_block_fwd(const Tensor& x, const Tensor& ln_w, const Ten
   OptTensor g, u;
   if (grad_mode) { g = torch::empty({R, F}, x.options()); u = torch::empty({R, F}, x.options()); }
   ggemm(1, xg, false, w1, false, h, R, F, H, El, offs, cap, w3, NONE, NONE, false, 0, g, u, false, 1.0, status, w0, w1o, NONE, NONE, NONE, NONE);
-  if (is_ep && grad_mode) xg = xg.clone();
+  if (is_ep && keep) xg = xg.clone();         // the receive buffer is reused by the next exchange
   Tensor y = torch::empty({R, H}, x.options());
   ggemm(1, h, false, w2, true, y, R, H, F, El, offs, cap, NONE, NONE, NONE, false, 0, NONE, NONE, false, 1.0, status, NONE, NONE, s0, s1, s2, s3);
   if (!is_ep) {
@@ -622,10 +643,12 @@ std::vector<Tensor> moe_block_fwd(const Tensor& x, const Tensor& ln_w, const Ten
   } else {
     ep_wait_rows(ep_ints[0], layout, meta_c, ep_ints[4], st, ep_ints[5]);
     ys = ep[5].narrow(0, 0, n_slots);
-    if (grad_mode) ys = ys.clone();
+    if (keep) ys = ys.clone();
   }
   out = combine_rows(ys, plan[2], wts, top_k);
   out.add_(x);
+  if (ckpt == 1 && !grad_mode)
+    return {out, plan[0], wts, idx, ys, plan[1], plan[2], plan[3], meta_c, rr, rp, te, xg, expert_sorted, offs};
   if (!grad_mode) return {out, plan[0]};
   return {out, plan[0], rstd, xn, wts, idx, ys, plan[1], plan[2], plan[3], meta_c, rr, rp, te, xg, *g, *u, h, expert_sorted, offs};
 }

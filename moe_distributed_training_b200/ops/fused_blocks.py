@@ -323,16 +323,31 @@ class _MoEBlockNative(torch.autograd.Function):
         with torch.set_grad_enabled(grad_mode):
             w1, w2, w3, _, ws, wgrad_out = mlp.call_args(x2)
         eng, layout, ints, tens = None, [], [], []
-        if ex.ep_group is not None and ex.ep_size > 1:
+        is_ep = ex.ep_group is not None and ex.ep_size > 1
+        if is_ep:
             if ex._fused is None:
                 from ..parallel.fused_ep import FusedExpertParallel
                 ex._fused = FusedExpertParallel.for_group(ex.ep_group, a, x2.device)
             eng = ex._fused
-            assert x2.shape[0] * a.moe_top_k <= eng.wspace.capacity_slots, "more (token, choice) slots than the workspace was sized for"
-            eng.count_epoch += 1
-            layout, ints, tens = _MoEBlockNative._ep_args(eng, eng.next_phase(), x2.shape[1])
-        res = ext.moe_block_fwd(x2, ln_w, Wr.contiguous(), w1, w2, w3, layer.post_attention_layernorm.eps, a.moe_top_k,
-                                a.moe_num_experts, grad_mode, layout, ints, tens, C.status_tensor(x2.device))
+        # A block that is recomputed in the backward pass (layer._ckpt_mode: 1 = graph-free first pass, 2 = the
+        # recomputation) keeps the results of its token exchange from the first pass, so that the recomputation needs
+        # no second dispatch / down projection / combine: every rank skips them alike, no exchange epoch is used.
+        ckpt_mode = getattr(layer, "_ckpt_mode", 0)
+        stash = getattr(layer, "_moe_stash", None)
+        if ckpt_mode == 2 and grad_mode and stash is not None:
+            layer._moe_stash = None
+            res = ext.moe_block_fwd(x2, ln_w, Wr.contiguous(), w1, w2, w3, layer.post_attention_layernorm.eps, a.moe_top_k,
+                                    a.moe_num_experts, True, [], [], [], C.status_tensor(x2.device), 2, list(stash))
+        else:
+            if is_ep:
+                assert x2.shape[0] * a.moe_top_k <= eng.wspace.capacity_slots, "more (token, choice) slots than the workspace was sized for"
+                eng.count_epoch += 1
+                layout, ints, tens = _MoEBlockNative._ep_args(eng, eng.next_phase(), x2.shape[1])
+            make_stash = 1 if (ckpt_mode == 1 and not grad_mode) else 0
+            res = ext.moe_block_fwd(x2, ln_w, Wr.contiguous(), w1, w2, w3, layer.post_attention_layernorm.eps, a.moe_top_k,
+                                    a.moe_num_experts, grad_mode, layout, ints, tens, C.status_tensor(x2.device), make_stash, [])
+            if make_stash:
+                layer._moe_stash = res[1:]
         ex.last_tokens_per_expert = res[1]
         if grad_mode:
             ctx.layer, ctx.eng, ctx.ws, ctx.wgrad_out = layer, eng, float(ws), wgrad_out

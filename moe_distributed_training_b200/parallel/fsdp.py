@@ -182,8 +182,12 @@ class _LayerFn(torch.autograd.Function):
         ctx.runner, ctx.idx, ctx.batch = runner, idx, batch
         ctx.save_for_backward(x)
         layer = runner.model.model.layers[idx]
-        with torch.no_grad():
-            return layer(x, batch)
+        layer._ckpt_mode = 1 if runner.stash_exchange else 0     # the MoE sub-block may keep its exchange results
+        try:
+            with torch.no_grad():
+                return layer(x, batch)
+        finally:
+            layer._ckpt_mode = 0
 
     @staticmethod
     def backward(ctx, gout):
@@ -199,8 +203,13 @@ class _LayerFn(torch.autograd.Function):
         local = [p for p in unit.local_params if p.requires_grad]
         xin = x.detach().requires_grad_(True)
         layer = runner.model.model.layers[idx]
-        with torch.enable_grad():
-            y = layer(xin, batch)
+        layer._ckpt_mode = 2 if runner.stash_exchange else 0
+        try:
+            with torch.enable_grad():
+                y = layer(xin, batch)
+        finally:
+            layer._ckpt_mode = 0
+            layer._moe_stash = None
         grads = torch.autograd.grad(y, [xin] + leaves + local, gout, allow_unused=True)
         dx = grads[0]
         runner._reduce_unit_grads(unit, list(grads[1:1 + len(leaves)]))
@@ -262,6 +271,10 @@ class ShardedMixtral:
         # buffers that stay valid until the backward pass, i.e. resident copies or a single rank.
         self.recompute = bool(recompute) or not (self.resident or self.ws == 1)
         self._direct_units = set()
+        # Recomputed blocks keep what their MoE sub-block received and got back in the first pass (~20 MB per block
+        # and micro-batch, plus one receive-buffer copy under expert parallelism), so that the recomputation repeats
+        # neither the token exchange nor the down projection.  MDT_STASH_EXCHANGE=0 recomputes everything.
+        self.stash_exchange = os.environ.get("MDT_STASH_EXCHANGE", "1") != "0"
         if self.ws > 1 and self.resident:
             self.root_buffers = None
         elif self.ws > 1:
