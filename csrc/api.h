@@ -64,6 +64,8 @@ int mdt_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* r
                     int rows, int cols, int n_partial, cudaStream_t s);
 int mdt_rope(const void* x, void* y, const int* positions, int tokens, int heads, int head_dim, float theta,
              int inverse, cudaStream_t s);
+// dst[0 : rows_used[0]] = src[0 : rows_used[0]] for row buffers of `cols` bf16 elements sized for a capacity (n elements)
+int mdt_copy_rows_used(const void* src, void* dst, long long n, const int* rows_used, long long cols, cudaStream_t s);
 // rows_used (optional, device): number of leading rows of `cols` elements that hold data; the rest is left untouched
 int mdt_swiglu_bwd(const void* g, const void* u, const void* dh, void* dg, void* du, long long n,
                    const int* rows_used, long long cols, cudaStream_t s);

@@ -129,6 +129,16 @@ std::vector<Tensor> swiglu_bwd(const Tensor& g, const Tensor& u, const Tensor& d
                        g.size(-1), cur_stream()), "swiglu_bwd");
   return {dg, du};
 }
+// Copy of a block-padded row buffer sized for a capacity: only rows below offsets[G] are copied (the rest of the
+// result is uninitialised and, like the source's, never read).
+Tensor clone_used_rows(const Tensor& x, const Tensor& offsets) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && x.scalar_type() == at::kBFloat16 && offsets.scalar_type() == at::kInt);
+  auto y = torch::empty_like(x);
+  check(mdt_copy_rows_used(x.data_ptr(), y.data_ptr(), x.numel(), offsets.data_ptr<int>() + (offsets.numel() - 1), x.size(1),
+                           cur_stream()), "copy_rows_used");
+  return y;
+}
 Tensor embedding(const Tensor& table, const Tensor& ids) {
   CHECK_BF16(table);
   c10::cuda::CUDAGuard guard(table.device());
@@ -635,7 +645,7 @@ std::vector<Tensor> moe_block_fwd(const Tensor& x, const Tensor& ln_w, const Ten
   OptTensor g, u;
   if (grad_mode) { g = torch::empty({R, F}, x.options()); u = torch::empty({R, F}, x.options()); }
   ggemm(1, xg, false, w1, false, h, R, F, H, El, offs, cap, w3, NONE, NONE, false, 0, g, u, false, 1.0, status, w0, w1o, NONE, NONE, NONE, NONE);
-  if (is_ep && keep) xg = xg.clone();         // the receive buffer is reused by the next exchange
+  if (is_ep && keep) xg = clone_used_rows(xg, offs);   // the receive buffer is reused by the next exchange
   Tensor y = torch::empty({R, H}, x.options());
   ggemm(1, h, false, w2, true, y, R, H, F, El, offs, cap, NONE, NONE, NONE, false, 0, NONE, NONE, false, 1.0, status, NONE, NONE, s0, s1, s2, s3);
   if (!is_ep) {

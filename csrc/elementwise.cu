@@ -172,6 +172,14 @@ __global__ void swiglu_bwd_kernel(const uint4* __restrict__ g, const uint4* __re
   }
 }
 
+// Copy of a capacity-sized row buffer that touches only the rows in use (count read from device memory).
+__global__ void copy_rows_used_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long nv,
+                                      const int* __restrict__ rows_used, long long vecs_per_row) {
+  const long long lim = (long long)rows_used[0] * vecs_per_row;
+  nv = lim < nv ? lim : nv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv; i += (long long)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
 // ------------------------------------------------------------------------------------ embedding
 __global__ void embedding_kernel(const bf16* __restrict__ table, const long long* __restrict__ ids, bf16* __restrict__ out, int cols) {
   const long long id = ids[blockIdx.x];
@@ -407,6 +415,13 @@ extern "C" int mdt_swiglu_fwd(const void* g, const void* u, void* h, long long n
   if (n % 8 != 0) return -1;
   if (n == 0) return 0;
   swiglu_fwd_kernel<<<grid_for(n / 8, 256), 256, 0, s>>>((const uint4*)g, (const uint4*)u, (uint4*)h, n / 8);
+  MDT_CHECK_LAUNCH();
+  return 0;
+}
+extern "C" int mdt_copy_rows_used(const void* src, void* dst, long long n, const int* rows_used, long long cols, cudaStream_t s) {
+  if (n % 8 != 0 || cols % 8 != 0 || rows_used == nullptr) return -1;
+  if (n == 0) return 0;
+  copy_rows_used_kernel<<<grid_for(n / 8, 256), 256, 0, s>>>((const uint4*)src, (uint4*)dst, n / 8, rows_used, cols / 8);
   MDT_CHECK_LAUNCH();
   return 0;
 }
