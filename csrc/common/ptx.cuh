@@ -197,9 +197,6 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   // cluster-scope memory barrier is needed here
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes) : "memory");
-}
 // tile -> this CTA's shared memory; the byte count is credited to the mbarrier at `bar_cluster_addr`, which may
 // belong to the other CTA of the pair
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
