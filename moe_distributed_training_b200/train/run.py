@@ -51,9 +51,10 @@ def _resolve_config(model_name_or_path: Optional[str], preset: str) -> (MixtralC
         from ..parallel.shard_moe import get_resolved_checkpoint_location
         try:
             path = get_resolved_checkpoint_location(model_name_or_path)
-            return MixtralConfig.from_pretrained(path), path
+            if os.path.exists(os.path.join(path, "config.json")):
+                return MixtralConfig.from_pretrained(path), path
         except ValueError:
-            pass
+            pass   # neither a directory nor a cached hub id: random init of the preset (a tokenizer-only directory too)
     return (MixtralConfig.tiny() if preset == "tiny" else MixtralConfig.mixtral_8x7b()), None
 
 
@@ -68,7 +69,11 @@ def _load_text_dataset(path: str, tokenizer_path: str, max_seq_length: int) -> O
         return None
     if tok.pad_token is None:
         tok.pad_token = tok.eos_token
-    template = tok.encode(" ### Response", add_special_tokens=False)[2:]
+    # The reference drops the first two ids of the encoded template (train_fsdp1.py:59-61): a sentencepiece
+    # tokenizer encodes the leading space and "###" differently in the middle of a text.  Tokenizers whose encoding
+    # of the template is that short keep it whole.
+    template = tok.encode(" ### Response", add_special_tokens=False)
+    template = template[2:] if len(template) > 2 else template
     collator = DataCollatorForCompletionOnlyLM(template, tok.pad_token_id)
     with open(path) as f:
         text = f.read().strip()

@@ -164,3 +164,25 @@ def test_launcher_translates_an_accelerate_config(tmp_path):
                           os.path.join(root, "accelerate.yaml"), "--num_processes", "2", "--dry_run", "train_fsdp1.py"],
                          capture_output=True, text=True, cwd=root, check=True)
     assert "--nproc-per-node=2" in json.loads(out.stdout)["command"]
+
+
+def test_text_dataset_masks_the_prompt_with_a_local_tokenizer(tmp_path):
+    """data.json records -> token ids with everything up to the response template label-masked."""
+    import json
+    pytest = __import__("pytest")
+    tokenizers = pytest.importorskip("tokenizers")
+    transformers = pytest.importorskip("transformers")
+    from moe_distributed_training_b200.train.run import _load_text_dataset
+    words = ["<unk>", "<s>", "</s>", "###", "Response", "Instruction", ":", "hello", "world", "answer", "is", "42", "what"]
+    tok = tokenizers.Tokenizer(tokenizers.models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tok.pre_tokenizer = tokenizers.pre_tokenizers.Whitespace()
+    fast = transformers.PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="<unk>", bos_token="<s>", eos_token="</s>")
+    fast.save_pretrained(str(tmp_path))
+    data = tmp_path / "data.json"
+    data.write_text(json.dumps([{"output": "### Instruction : what is hello world ### Response : answer is 42"}]))
+    out = _load_text_dataset(str(data), str(tmp_path), 64)
+    assert len(out) == 1
+    ids, labels = out[0]["input_ids"].tolist(), out[0]["labels"].tolist()
+    assert ids == [3, 5, 6, 12, 10, 7, 8, 3, 4, 6, 9, 10, 11]
+    assert labels[:9] == [-100] * 9 and labels[9:] == ids[9:]       # prompt and template masked, answer kept
+    assert _load_text_dataset(str(tmp_path / "missing.json"), str(tmp_path), 64) is None
