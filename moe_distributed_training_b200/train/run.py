@@ -69,18 +69,28 @@ def _load_text_dataset(path: str, tokenizer_path: str, max_seq_length: int) -> O
         return None
     if tok.pad_token is None:
         tok.pad_token = tok.eos_token
-    # The reference drops the first two ids of the encoded template (train_fsdp1.py:59-61): a sentencepiece
-    # tokenizer encodes the leading space and "###" differently in the middle of a text.  Tokenizers whose encoding
-    # of the template is that short keep it whole.
-    template = tok.encode(" ### Response", add_special_tokens=False)
-    template = template[2:] if len(template) > 2 else template
-    collator = DataCollatorForCompletionOnlyLM(template, tok.pad_token_id)
     with open(path) as f:
         text = f.read().strip()
     records = json.loads(text) if text.startswith("[") else [json.loads(l) for l in text.splitlines() if l.strip()]
+    # Two record layouts: {"output": full text with " ### Response"} (train_accelerate_fsdp2.py:85-101) and alpaca
+    # records {"instruction", "output"}, which the FSDP1 script formats itself and masks up to " ### Answer:"
+    # (train_fsdp1.py:49-61).
+    alpaca = bool(records) and "instruction" in records[0]
+    template = tok.encode(" ### Answer:" if alpaca else " ### Response", add_special_tokens=False)
+    # The reference drops the first two ids of the encoded template (train_fsdp1.py:59-61) because a sentencepiece
+    # tokenizer encodes a leading space and "###" differently at the start of a text than inside one.  How many
+    # leading ids differ depends on the tokenizer, so the longest of template, template[1:], template[2:] that
+    # occurs in the example is used.
+    collators = [DataCollatorForCompletionOnlyLM(template[d:], tok.pad_token_id) for d in range(min(3, len(template)))]
+
+    def occurs(ids, sub):
+        n = len(sub)
+        return n > 0 and any(ids[i:i + n] == sub for i in range(len(ids) - n + 1))
     out = []
     for rec in records:
-        ids = tok(rec["output"])["input_ids"][:max_seq_length]
+        body = f"### Question: {rec['instruction']}\n ### Answer: {rec['output']}" if alpaca else rec["output"]
+        ids = tok(body)["input_ids"][:max_seq_length]
+        collator = next((c for d, c in enumerate(collators) if occurs(list(ids), template[d:])), collators[-1])
         b = collator([{"input_ids": ids}])
         out.append({"input_ids": b["input_ids"][0], "labels": b["labels"][0]})
     return out

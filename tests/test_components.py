@@ -173,7 +173,7 @@ def test_text_dataset_masks_the_prompt_with_a_local_tokenizer(tmp_path):
     tokenizers = pytest.importorskip("tokenizers")
     transformers = pytest.importorskip("transformers")
     from moe_distributed_training_b200.train.run import _load_text_dataset
-    words = ["<unk>", "<s>", "</s>", "###", "Response", "Instruction", ":", "hello", "world", "answer", "is", "42", "what"]
+    words = ["<unk>", "<s>", "</s>", "###", "Response", "Instruction", ":", "hello", "world", "answer", "is", "42", "what", "Question", "Answer"]
     tok = tokenizers.Tokenizer(tokenizers.models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
     tok.pre_tokenizer = tokenizers.pre_tokenizers.Whitespace()
     fast = transformers.PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="<unk>", bos_token="<s>", eos_token="</s>")
@@ -186,3 +186,9 @@ def test_text_dataset_masks_the_prompt_with_a_local_tokenizer(tmp_path):
     assert ids == [3, 5, 6, 12, 10, 7, 8, 3, 4, 6, 9, 10, 11]
     assert labels[:9] == [-100] * 9 and labels[9:] == ids[9:]       # prompt and template masked, answer kept
     assert _load_text_dataset(str(tmp_path / "missing.json"), str(tmp_path), 64) is None
+    # alpaca-style records are formatted "### Question: ... ### Answer: ..." and masked up to the answer
+    alp = tmp_path / "alpaca.json"
+    alp.write_text(json.dumps([{"instruction": "what is hello", "input": "", "output": "answer is 42"}]))
+    out = _load_text_dataset(str(alp), str(tmp_path), 64)
+    labels = out[0]["labels"].tolist()
+    assert labels[-3:] == [9, 10, 11] and all(v == -100 for v in labels[:-3])
