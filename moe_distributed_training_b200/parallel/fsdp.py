@@ -260,6 +260,11 @@ class ShardedMixtral:
         # optimizer step has changed (ZeRO-2 style).  Frozen groups are gathered once per run instead of twice per
         # block per micro-batch.  Default: on when the full copies fit in `resident_limit_bytes`.
         full_bytes = sum(g.padded * g.shard.element_size() for u in self.units + [self.root] for g in u.groups)
+        if os.environ.get("MDT_RESIDENT_LIMIT_GIB"):
+            # e.g. 100 keeps even the experts of a no-EP run resident (93 GB in bf16 for Mixtral-8x7B): no per-block
+            # gathers at all, at the price of a full parameter copy per GPU
+            resident_limit_bytes = int(float(os.environ["MDT_RESIDENT_LIMIT_GIB"]) * (1 << 30))
+        self.full_param_bytes = full_bytes
         if resident_params is None:
             resident_params = os.environ.get("MDT_RESIDENT_PARAMS", "1") != "0" and full_bytes <= resident_limit_bytes
         self.resident = bool(resident_params) and self.ws > 1
