@@ -19,5 +19,15 @@ def get_mlp_weights_lora(mod, name):
     return get_mlp_weights(mod, name), A, B, r, alpha
 
 
+def get_mlp_device_mesh_pg(mod):
+    """Process group over which `mod`'s experts are split (the reference takes the last mesh dimension of the
+    weights' DTensor mesh, megablocks_utils/config_utils.py:63-69): the tensor-parallel group in the TP mode, else the
+    expert-parallel group; None on a single rank."""
+    args = mod.args
+    if getattr(args, "tensor_parallel_group", None) is not None and args.tensor_parallel_size > 1:
+        return args.tensor_parallel_group
+    return args.expert_parallel_group if args.moe_expert_model_parallelism else None
+
+
 def update_mlp_registry():
     return {"mlp": {"sparse": "SparseMLPv2", "scattermoe": "SparseMLPv2"}}

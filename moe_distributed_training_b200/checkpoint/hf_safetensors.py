@@ -128,6 +128,49 @@ def load_moe_layer(moe_module, checkpoint_dir: str, weight_map: Dict[str, str], 
         files.close()
 
 
+def assign_mlp_v2_weights(dmoe, directory: str, settings: Dict[str, List[Tuple[str, str]]], device_mesh=None,
+                          placements=None, parallize_tensor: bool = False):
+    """Fill one MoE module from `settings`, the mapping `get_router_experts_sharded_safetensor` returns.
+
+    Same call as the reference's function of this name (megablocks_utils/shard_moe_utils.py:131-201), which reads
+    whole expert tensors on every rank, concatenates them and lets `distribute_tensor` scatter the shards.  Here a
+    rank reads only its own byte ranges: with `parallize_tensor` the slice `[rank * F/n, (rank+1) * F/n)` of every
+    expert's FFN dimension, otherwise the experts `[rank * E/n, (rank+1) * E/n)`, where rank and n come from the last
+    dimension of `device_mesh` (or, without a mesh, from the module's expert-parallel / tensor-parallel group).
+    `placements` is accepted for signature compatibility; the layout is implied by the module.
+    """
+    args = dmoe.args
+    E = args.moe_num_experts
+    group = None
+    if device_mesh is not None:
+        group = device_mesh.get_group(device_mesh.ndim - 1) if hasattr(device_mesh, "ndim") else device_mesh.get_group()
+    elif parallize_tensor:
+        group = args.tensor_parallel_group
+    elif args.moe_expert_model_parallelism:
+        group = args.expert_parallel_group
+    import torch.distributed as dist
+    n = dist.get_world_size(group) if group is not None else 1
+    r = dist.get_rank(group) if group is not None else 0
+    mlp = dmoe.experts.mlp
+    if parallize_tensor:
+        Fl = args.ffn_hidden_size // n
+        expert_ids, ffn_slice = range(E), slice(r * Fl, (r + 1) * Fl)
+    else:
+        El = E // n
+        expert_ids, ffn_slice = range(r * El, (r + 1) * El), None
+    files = _Files(directory)
+    with torch.no_grad():
+        (key, fname), = settings[KEY_ROUTER]
+        rw = dmoe.router.layer.weight
+        rw.copy_(files.get(fname).get_tensor(key).to(rw.dtype))
+        for wname in ("w1", "w2", "w3"):
+            p = getattr(mlp, wname)
+            t = load_expert_shard(files, settings[f"{KEY_EXPERTS}.{wname}"], wname, list(expert_ids), ffn_slice, p.dtype)
+            assert t.shape == p.shape, f"{wname}: checkpoint shard {tuple(t.shape)} vs parameter {tuple(p.shape)}"
+            p.copy_(t)
+    files.close()
+
+
 def load_dense(model, checkpoint_dir: str, weight_map: Optional[Dict[str, str]] = None, strict: bool = True):
     """Load every non-MoE parameter (names are identical to HF's)."""
     weight_map = weight_map or read_weight_map(checkpoint_dir)

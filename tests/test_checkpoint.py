@@ -85,6 +85,25 @@ def test_single_process_load_and_export_roundtrip(tmp_path):
             assert torch.equal(f.get_tensor(k), tensors[k]), k
 
 
+def test_assign_mlp_v2_weights_fills_a_module_from_the_key_map(tmp_path):
+    """The reference's loader entry point: key map of one layer -> router and expert weights of a MoE module."""
+    from megablocks_utils.shard_moe_utils import assign_mlp_v2_weights, get_router_experts_sharded_safetensor
+    from moe_distributed_training_b200.models.mixtral import moe_args_from_config
+    from moe_distributed_training_b200.moe.layer import dMoE
+    cfg = MixtralConfig.tiny()
+    src = str(tmp_path / "src")
+    tensors = _write_tiny_hf_checkpoint(src, cfg)
+    settings = get_router_experts_sharded_safetensor(hfst.read_weight_map(src), "model.layers.0", "block_sparse_moe")
+    moe = dMoE(moe_args_from_config(cfg, torch.float32, "cpu"))
+    assign_mlp_v2_weights(moe, src, settings, None, None)
+    F, H, E = cfg.intermediate_size, cfg.hidden_size, cfg.num_local_experts
+    assert torch.equal(moe.router.layer.weight, tensors["model.layers.0.block_sparse_moe.gate.weight"])
+    for e in range(E):
+        assert torch.equal(moe.experts.mlp.w1.view(E, F, H)[e], tensors[f"model.layers.0.block_sparse_moe.experts.{e}.w1.weight"])
+        assert torch.equal(moe.experts.mlp.w2.view(E, F, H)[e], tensors[f"model.layers.0.block_sparse_moe.experts.{e}.w2.weight"].t())
+        assert torch.equal(moe.experts.mlp.w3.view(E, F, H)[e], tensors[f"model.layers.0.block_sparse_moe.experts.{e}.w3.weight"])
+
+
 def _ep_roundtrip(rank, world, src, out):
     from moe_distributed_training_b200.checkpoint.state import save_model
     from moe_distributed_training_b200.train.engine import build_engine
