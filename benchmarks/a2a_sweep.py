@@ -47,6 +47,9 @@ def main():
     ap.add_argument("--out", default="")
     ap.add_argument("--tokens", default="1024,4096,16384,65536")
     ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--capacity-factor", type=float, default=2.5,
+                    help="receive buffers hold this many times the balanced load (smaller = denser buffers)")
+    ap.add_argument("--phases", action="store_true", help="also time dispatch alone (plan + counts + dispatch + wait)")
     args = ap.parse_args()
     from moe_distributed_training_b200.train.engine import init_distributed
     rank, ws, dev = init_distributed("cuda")
@@ -62,7 +65,7 @@ def main():
         gl = torch.Generator(device=dev).manual_seed(100 + rank)
         x = torch.randn(T, H, device=dev, generator=gl).to(torch.bfloat16)
         top = (torch.randn(T, E, device=dev, generator=gl) + bias).topk(k, -1).indices.int()
-        wsp = symm.create_ep_workspace(group, E, H, T, k, dev, capacity_factor=2.5 * ws if ws > 1 else None)
+        wsp = symm.create_ep_workspace(group, E, H, T, k, dev, capacity_factor=args.capacity_factor * ws if ws > 1 else None)
         eng = fused_ep.FusedExpertParallel(wsp, k, dev)
         eos = top.reshape(-1).contiguous()
         El = E // ws
@@ -92,7 +95,15 @@ def main():
             ys = xs.new_empty(sum(both[0]), H)
             dist.all_to_all_single(ys, yr, both[0], both[1])
 
+        def fused_dispatch_only():
+            plan = C.make_plan(top, E, 1, top.numel())
+            meta = eng.exchange_counts(plan.tokens_per_expert)
+            par = eng.next_phase()
+            eng.dispatch(x, plan.src_slot, eos, None, meta, k, par)
+
         t_f = timed(fused)
+        C.check_status(dev)
+        t_d = timed(fused_dispatch_only) if args.phases else None
         C.check_status(dev)
         t_n = timed(nccl)
         tot = torch.tensor([bytes_remote], device=dev, dtype=torch.float64)
@@ -103,6 +114,9 @@ def main():
                "fused_gbs_per_direction": round(2 * mx / t_f / 1e6, 1), "nccl_gbs_per_direction": round(2 * mx / t_n / 1e6, 1),
                "fused_fraction_of_measured_link": round(2 * mx / t_f / 1e6 / LINK_GBS, 3),
                "speedup_vs_nccl": round(t_n / t_f, 2)}
+        if t_d is not None:
+            row["fused_dispatch_only_ms"] = round(t_d, 4)
+            row["fused_dispatch_gbs"] = round(mx / t_d / 1e6, 1)
         results.append(row)
         if rank == 0:
             print(json.dumps(row), flush=True)
