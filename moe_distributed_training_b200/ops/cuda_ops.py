@@ -9,7 +9,6 @@ been built: there is no silent PyTorch fallback for CUDA tensors.
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 

@@ -8,7 +8,6 @@ the scale / cast / accumulate that otherwise follow the collective.
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.distributed as dist

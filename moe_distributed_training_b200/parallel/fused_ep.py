@@ -14,7 +14,6 @@ from __future__ import annotations
 from typing import Optional
 
 import torch
-import torch.distributed as dist
 
 from .. import ops
 from ..ops.reference import RoutingPlan

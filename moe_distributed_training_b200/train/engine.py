@@ -34,7 +34,6 @@ from ..moe.layer import dMoE
 from ..optim.adamw import FusedAdamW
 from ..optim.clip import clip_grad_norm_
 from ..optim.schedulers import get_scheduler
-from ..parallel import collectives as coll
 from ..parallel.fsdp import ShardedMixtral
 from ..parallel.shard_moe import (KEY_DATA_PARALLEL, KEY_EXPERT_PARALLEL, get_moe_kwargs, shard_moe)
 from ..peft.lora import ATTENTION_TARGETS, get_peft_model

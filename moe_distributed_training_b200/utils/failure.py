@@ -19,7 +19,6 @@ import time
 from typing import List, Optional
 
 import torch
-import torch.distributed as dist
 
 
 class RankFailure(RuntimeError):

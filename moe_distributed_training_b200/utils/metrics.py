@@ -11,7 +11,6 @@ from __future__ import annotations
 import json
 import time
 from contextlib import contextmanager
-from typing import Optional
 
 import torch
 import torch.distributed as dist

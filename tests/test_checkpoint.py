@@ -3,7 +3,6 @@ import json
 import os
 
 import torch
-from safetensors.torch import save_file
 
 from dist_utils import run_distributed
 from moe_distributed_training_b200 import MixtralConfig
