@@ -63,9 +63,10 @@ struct Tile {
   int g, m0, n0, krow0, num_kb, num_kb_l;
 };
 
-// Maps a linear tile index to its coordinates; returns false past the last tile.
+// Maps a linear tile index to its coordinates; returns false past the last tile.  (Also callable on the host, where
+// a unit test enumerates the tiles of random problems and checks that they cover every block exactly once.)
 template <int BN_OUT>
-__device__ __forceinline__ bool get_tile(const GemmParams& p, int t, Tile& o) {
+__host__ __device__ __forceinline__ bool get_tile(const GemmParams& p, int t, Tile& o) {
   const int n_blocks = (p.N + BN_OUT - 1) / BN_OUT;
   o.num_kb_l = (p.K_l + BK - 1) / BK;
   if (p.mode == 2) {
@@ -385,7 +386,7 @@ struct PairTile {
 // Pair tiles cover 256 rows.  In the grouped-rows mode a pair never straddles two groups: a group with an odd
 // number of 128-row blocks ends with a pair whose second half is idle (second_ok = 0).
 template <int BN_OUT>
-__device__ __forceinline__ bool get_pair_tile(const GemmParams& p, int t, PairTile& o) {
+__host__ __device__ __forceinline__ bool get_pair_tile(const GemmParams& p, int t, PairTile& o) {
   const int n_blocks = (p.N + BN_OUT - 1) / BN_OUT;
   o.num_kb_l = (p.K_l + BK - 1) / BK;
   o.second_ok = 1;
