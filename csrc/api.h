@@ -55,6 +55,10 @@ int mdt_gemm_max_pairs(void);
 // Expected total rows of the row-grouped (mode 1) products this host thread issues next, for buffers sized to a
 // capacity; 0 = unknown.  Only guides the choice of tile shape.
 void mdt_gemm_rows_hint(long long rows);
+// The tiling mdt_gemm would pick for `d` under `policy` (see mdt_gemm_set_pair_policy) with that rows hint on a GPU with
+// `num_sms` SMs: 0 = 128-row tiles, 1 = CTA pair, 2 = tall.  Reads only M, N, K, K_l, G, mode, dual, c_fp32, accumulate,
+// capacity_rows and whether offsets is set; needs no GPU.
+int mdt_gemm_choose_tiling(const MdtGemmDesc* d, int policy, long long rows_hint, int num_sms);
 // upper bound on the pair kernel's grid, in pairs (0 = the resident maximum); for scaling measurements
 void mdt_gemm_set_pair_cap(int pairs);
 

@@ -735,6 +735,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cross_entropy", &cross_entropy);
   m.def("gemm_set_pair_policy", [](int64_t policy) { return (int64_t)mdt_gemm_set_pair_policy((int)policy); });
   m.def("gemm_set_pair_cap", [](int64_t n) { mdt_gemm_set_pair_cap((int)n); });
+  m.def("gemm_choose_tiling", [](int64_t mode, int64_t M, int64_t N, int64_t K, int64_t K_l, int64_t G, int64_t capacity_rows, bool dual,
+                                 bool c_fp32, bool accumulate, bool has_offsets, int64_t policy, int64_t rows_hint, int64_t num_sms) {
+    MdtGemmDesc d;
+    memset(&d, 0, sizeof(d));
+    static const int dummy_offsets = 0;
+    d.mode = (int)mode; d.M = (int)M; d.N = (int)N; d.K = (int)K; d.K_l = (int)K_l; d.G = (int)G; d.capacity_rows = capacity_rows;
+    d.dual = dual; d.c_fp32 = c_fp32; d.accumulate = accumulate; d.offsets = has_offsets ? &dummy_offsets : nullptr;
+    return (int64_t)mdt_gemm_choose_tiling(&d, (int)policy, rows_hint, (int)num_sms);
+  });
   m.def("gemm_rows_hint", [](int64_t rows) { mdt_gemm_rows_hint((long long)rows); });
   m.def("gemm_max_pairs", []() { return (int64_t)mdt_gemm_max_pairs(); });
   m.def("skinny_mm", &skinny_mm);

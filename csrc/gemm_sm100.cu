@@ -1127,11 +1127,57 @@ static int pair_policy() {
   return g_pair_policy;
 }
 
+// Which kernel runs a product: 0 = 128-row tiles, 1 = CTA pair, 2 = tall 256 x 256 tiles.  Pure arithmetic on the
+// descriptor (no CUDA call), so that it can be examined without a GPU.
+static int choose_tiling(const MdtGemmDesc* d, int policy, long long thread_rows_hint, int num_sms) {
+  const int G = d->G < 1 ? 1 : d->G;
+  const int BN = (d->dual || d->N > 128) ? 256 : 128;
+  const int bn_out = d->dual ? BN / 2 : BN;
+  if (BN != 256) return 0;
+  // The CTA-pair kernel needs 256-row pair tiles that are mostly full: dense and depth-grouped products with
+  // M >= 256, and row-grouped products whose groups average at least four 128-row blocks.
+  const long long rows_hint = (d->mode == 1) ? d->capacity_rows : d->M;
+  const bool fills = rows_hint >= 2 * BM && (d->mode != 1 || rows_hint >= (long long)G * 4 * BM);
+  if (policy == 2 || (policy == 1 && fills)) return 1;
+  if (policy == 4) return 2;
+  if (policy != 3) return 0;
+  // The tall kernel retires k blocks faster (0.70 us per 256 x 256 x 64 against 0.47 us per 128 x 256 x 64, i.e.
+  // 1.3x per flop) but exposes its epilogue (~5 us per tile, ~14 with the SwiGLU epilogue) and halves the number
+  // of tiles, which changes how full the last wave is.  Where the row count is known (dense and depth-grouped
+  // products, and row-grouped ones whose caller gave the expected rows of a capacity-sized buffer) the two are
+  // compared by waves x time per tile; the typical win at one micro-batch's ~1300 expert rows is a product with
+  // 4096 output columns whose 160 tiles would need a second, almost empty wave.  Without a row count only
+  // products of >= 2048 rows and >= 3 waves of 128-row tiles take the tall kernel.
+  long long r = rows_hint;
+  const bool hinted = d->mode == 1 && thread_rows_hint > 0;
+  if (hinted && thread_rows_hint < r) r = thread_rows_hint;
+  long long grouped_depth = d->capacity_rows;          // mode 2 over row groups: the depth is the group's rows
+  if (thread_rows_hint > 0 && thread_rows_hint < grouped_depth) grouped_depth = thread_rows_hint;
+  const double blocks = (double)r / BM + (d->mode == 1 ? 0.5 * G : 0.0);
+  const double nb = (double)((d->N + bn_out - 1) / bn_out) * (d->mode == 2 ? G : 1);
+  const double depth = (d->mode == 2 && d->offsets != nullptr) ? (double)grouped_depth / G : (double)d->K;
+  const double kb = ceil(depth / BK) + ceil((double)d->K_l / BK);
+  bool tall;
+  if (d->mode != 1 || hinted) {
+    const double sms = num_sms;
+    const double slow_epilogue = (!d->c_fp32 && !d->accumulate) ? 0.0 : 6.0;   // the uncoalesced epilogue costs more
+    const double t1 = ceil(ceil(blocks) * nb / sms) * (fmax(kb * 0.47, 2.0) + 1.0);
+    const double t2 = ceil(ceil(blocks / 2 + (d->mode == 1 ? 0.25 * G : 0.0)) * nb / sms) * (kb * 0.70 + 5.0 + (d->dual ? 9.0 : 0.0) + slow_epilogue);
+    tall = r >= 2 * BM && kb >= 32.0 && t2 < 0.9 * t1;
+  } else {
+    tall = r >= 16 * BM && ceil(blocks) * nb >= 3.0 * num_sms && kb >= 32.0;
+  }
+  return tall ? 2 : 0;
+}
+
 }  // namespace mdt
 
 extern "C" long long mdt_gemm_launch_count() { return mdt::g_launches; }
 extern "C" void mdt_gemm_rows_hint(long long rows) { mdt::t_rows_hint = rows; }
 extern "C" int mdt_gemm_max_pairs() { return mdt::g_max_pairs; }
+extern "C" int mdt_gemm_choose_tiling(const MdtGemmDesc* d, int policy, long long rows_hint, int num_sms) {
+  return mdt::choose_tiling(d, policy, rows_hint, num_sms);
+}
 extern "C" void mdt_gemm_set_pair_cap(int pairs) { mdt::g_pair_cap = pairs; }
 extern "C" int mdt_gemm_set_pair_policy(int policy) {
   const int old = mdt::pair_policy();
@@ -1165,40 +1211,8 @@ extern "C" int mdt_gemm(const MdtGemmDesc* d, cudaStream_t stream) {
   if (p.dual && (p.b_mn != 0 || p.c_fp32 || p.accumulate)) return -11;
   const int BN = (p.dual || p.N > 128) ? 256 : 128;
   const int bn_out = p.dual ? BN / 2 : BN;
-  // The CTA-pair kernel needs 256-row pair tiles that are mostly full: dense and depth-grouped products with
-  // M >= 256, and row-grouped products whose groups average at least four 128-row blocks.
-  const long long rows_hint = (p.mode == 1) ? d->capacity_rows : p.M;
-  const int policy = pair_policy();
-  const bool fills = rows_hint >= 2 * BM && (p.mode != 1 || rows_hint >= (long long)p.G * 4 * BM);
-  const bool pair = BN == 256 && (policy == 2 || (policy == 1 && fills));
-  bool tall = BN == 256 && policy == 4;
-  if (BN == 256 && policy == 3) {
-    // The tall kernel retires k blocks faster (0.70 us per 256 x 256 x 64 against 0.47 us per 128 x 256 x 64, i.e.
-    // 1.3x per flop) but exposes its epilogue (~5 us per tile, ~14 with the SwiGLU epilogue) and halves the number
-    // of tiles, which changes how full the last wave is.  Where the row count is known (dense and depth-grouped
-    // products, and row-grouped ones whose caller gave the expected rows of a capacity-sized buffer) the two are
-    // compared by waves x time per tile; the typical win at one micro-batch's ~1300 expert rows is a product with
-    // 4096 output columns whose 160 tiles would need a second, almost empty wave.  Without a row count only
-    // products of >= 2048 rows and >= 3 waves of 128-row tiles take the tall kernel.
-    long long r = rows_hint;
-    const bool hinted = p.mode == 1 && t_rows_hint > 0;
-    if (hinted && t_rows_hint < r) r = t_rows_hint;
-    long long grouped_depth = d->capacity_rows;          // mode 2 over row groups: the depth is the group's rows
-    if (t_rows_hint > 0 && t_rows_hint < grouped_depth) grouped_depth = t_rows_hint;
-    const double blocks = (double)r / BM + (p.mode == 1 ? 0.5 * p.G : 0.0);
-    const double nb = (double)((p.N + bn_out - 1) / bn_out) * (p.mode == 2 ? p.G : 1);
-    const double depth = (p.mode == 2 && d->offsets != nullptr) ? (double)grouped_depth / p.G : (double)p.K;
-    const double kb = ceil(depth / BK) + ceil((double)p.K_l / BK);
-    if (p.mode != 1 || hinted) {
-      const double sms = g_num_sms;
-      const double fast_path = (!p.c_fp32 && !p.accumulate) ? 0.0 : 6.0;   // the uncoalesced epilogue costs more
-      const double t1 = ceil(ceil(blocks) * nb / sms) * (fmax(kb * 0.47, 2.0) + 1.0);
-      const double t2 = ceil(ceil(blocks / 2 + (p.mode == 1 ? 0.25 * p.G : 0.0)) * nb / sms) * (kb * 0.70 + 5.0 + (p.dual ? 9.0 : 0.0) + fast_path);
-      tall = r >= 2 * BM && kb >= 32.0 && t2 < 0.9 * t1;
-    } else {
-      tall = r >= 16 * BM && ceil(blocks) * nb >= 3.0 * g_num_sms && kb >= 32.0;
-    }
-  }
+  const int tiling = choose_tiling(d, pair_policy(), t_rows_hint, g_num_sms);
+  const bool pair = tiling == 1, tall = tiling == 2;
   const bool half_box = pair || tall;   // these kernels load B in 128-row boxes
   int rc = 0;
   // A: [a_rows, a_cols] row-major, a_cols contiguous.  K-major: rows = M, cols = K.  MN-major: rows = depth, cols = M.

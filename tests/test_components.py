@@ -192,3 +192,29 @@ def test_text_dataset_masks_the_prompt_with_a_local_tokenizer(tmp_path):
     out = _load_text_dataset(str(alp), str(tmp_path), 64)
     labels = out[0]["labels"].tolist()
     assert labels[-3:] == [9, 10, 11] and all(v == -100 for v in labels[:-3])
+
+
+def test_gemm_tiling_choice_without_a_gpu():
+    """The host-side rule that picks between the 128-row, CTA-pair and tall GEMM tilings (pure arithmetic)."""
+    build = pytest.importorskip("moe_distributed_training_b200.ops.build")
+    try:
+        ext = build.load()
+    except Exception:  # noqa: BLE001
+        pytest.skip("extension not built")
+
+    def choose(mode, M, N, K, K_l=0, G=1, cap=0, dual=False, c_fp32=False, acc=False, offs=False, policy=3, hint=0, sms=148):
+        return ext.gemm_choose_tiling(mode, M, N, K, K_l, G, cap, dual, c_fp32, acc, offs, policy, hint, sms)
+    TILE128, PAIR, TALL = 0, 1, 2
+    assert choose(0, 8192, 8192, 8192) == TALL                       # many waves, long depth
+    assert choose(0, 576, 4096, 4096) == TILE128                     # attention projection of one micro-batch: one wave
+    assert choose(0, 576, 1024, 4096) == TILE128
+    assert choose(0, 576, 16, 4096) == TILE128                       # narrow outputs never use 256-wide tiles
+    assert choose(0, 1152, 32000, 4096) == TILE128                   # lm_head: 4.5 tall tiles per column block, no gain
+    # expert GEMMs inside the exchange: buffers sized for 16 384 rows, ~1 300 expected
+    assert choose(1, 0, 4096, 14336, cap=16384, offs=True, hint=1300) == TALL     # 11 x 16 tiles would need 2 waves
+    assert choose(1, 0, 4096, 14336, cap=16384, offs=True, hint=500) == TILE128   # one wave either way
+    assert choose(2, 14336, 4096, 0, cap=16384, acc=True, offs=True, hint=1152) == TILE128   # weight gradient: short depth
+    assert choose(0, 8192, 8192, 8192, policy=0) == TILE128
+    assert choose(0, 8192, 8192, 8192, policy=2) == PAIR
+    assert choose(0, 300, 520, 200, policy=4) == TALL
+    assert choose(0, 300, 128, 200, policy=4) == TILE128             # 128-wide outputs: only the 128-row kernel exists
