@@ -135,6 +135,8 @@ def run_training(
     save_path: Optional[str] = None,
     resume_from: Optional[str] = None,
     max_steps: int = 0,
+    profile_trace: Optional[str] = None,
+    profile_steps: int = 2,
     sharding_strategy: str = "fsdp2",
 ):
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -181,12 +183,28 @@ def run_training(
     timer.start()
     tokens_local = 0
     step = start_step
+    # optional torch.profiler trace of `profile_steps` optimizer steps after the first one (one file per rank,
+    # chrome://tracing format); the steps under the profiler are slower, so use it on short runs
+    prof, prof_until, prof_done = None, 0, False
     while step < total_steps:
         epoch, k = divmod(step, max(steps_per_epoch, 1))
         mbs = micro[k * ga:(k + 1) * ga]
         tokens_local += sum(int(m["input_ids"].numel()) for m in mbs)
+        if profile_trace and prof is None and not prof_done and step == start_step + min(1, total_steps - start_step - 1):
+            from torch.profiler import ProfilerActivity, profile
+            acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if dev.type == "cuda" else [])
+            prof = profile(activities=acts)
+            prof.__enter__()
+            prof_until = step + max(1, profile_steps)
         out = engine.train_step(mbs)
         step += 1
+        if prof is not None and (step >= prof_until or step >= total_steps):
+            if dev.type == "cuda":
+                torch.cuda.synchronize(dev)
+            prof.__exit__(None, None, None)
+            os.makedirs(profile_trace, exist_ok=True)
+            prof.export_chrome_trace(os.path.join(profile_trace, f"trace_rank{rank:05d}.json"))
+            prof, prof_done = None, True
         gn = out["grad_norm"]
         log_json(rank, epoch=round(step / max(steps_per_epoch, 1), 2), loss=float(out["loss"]),
                  learning_rate=engine.scheduler.get_last_lr()[0], grad_norm=float(gn) if gn is not None else 0.0,

@@ -218,3 +218,13 @@ def test_gemm_tiling_choice_without_a_gpu():
     assert choose(0, 8192, 8192, 8192, policy=2) == PAIR
     assert choose(0, 300, 520, 200, policy=4) == TALL
     assert choose(0, 300, 128, 200, policy=4) == TILE128             # 128-wide outputs: only the 128-row kernel exists
+
+
+def test_profile_trace_flag_writes_a_trace(tmp_path):
+    from moe_distributed_training_b200.train.run import run_training
+    out = tmp_path / "traces"
+    run_training(model_preset="tiny", model_name_or_path=None, device_type="cpu", load_model_dtype="float32",
+                 gradient_accumulation_steps=2, max_steps=3, num_synthetic_examples=8, data_path=str(tmp_path / "none.json"),
+                 profile_trace=str(out), profile_steps=1)
+    files = list(out.glob("trace_rank*.json"))
+    assert len(files) == 1 and files[0].stat().st_size > 1000

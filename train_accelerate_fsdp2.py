@@ -42,6 +42,8 @@ def main(
     save_path: str = None,
     resume_from: str = None,
     max_steps: int = 0,
+    profile_trace: str = None,
+    profile_steps: int = 2,
 ):
     kw = dict(locals())
     if kw.pop("debug"):
