@@ -378,6 +378,7 @@ constexpr int PAIR_BN = 256;
 constexpr int PAIR_STAGES = 7;
 constexpr int PAIR_B_BYTES = 128 * BK * 2;
 constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;
+static_assert(PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256 <= 227 * 1024, "pair kernel: stages + barriers exceed the shared memory of a CTA");
 
 struct PairTile {
   int g, m0, n0, krow0, num_kb, num_kb_l, second_ok;
@@ -703,6 +704,8 @@ constexpr int TALL_THREADS = 320;
 constexpr int TALL_STAGES = 3;
 constexpr int TALL_BN = 256;
 constexpr int TALL_STAGE_BYTES = 2 * A_BYTES + TALL_BN * BK * 2;
+static_assert(TALL_STAGES * TALL_STAGE_BYTES + 1024 + 256 + 8 * 2048 <= 227 * 1024, "tall kernel: stages + barriers + store stage exceed the shared memory of a CTA");
+static_assert(TALL_THREADS == 32 * (2 + 8), "tall kernel: producer, MMA issuer and eight epilogue warps");
 
 __global__ void __launch_bounds__(TALL_THREADS, 1) gemm_sm100_tall_kernel(const __grid_constant__ GemmParams p) {
   constexpr int STAGES = TALL_STAGES;
