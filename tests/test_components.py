@@ -228,3 +228,18 @@ def test_profile_trace_flag_writes_a_trace(tmp_path):
                  profile_trace=str(out), profile_steps=1)
     files = list(out.glob("trace_rank*.json"))
     assert len(files) == 1 and files[0].stat().st_size > 1000
+
+
+def test_fsdp1_entry_accepts_the_reference_readme_command(tmp_path):
+    """Every flag of the reference README's FSDP1 command line (README.md:58-80) is understood."""
+    import os, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, os.path.join(root, "train_fsdp1.py"), "--accelerator_config", os.path.join(root, "accelerator_config.json"),
+           "--data_path", str(tmp_path / "data.json"), "--torch_dtype", "float32", "--bf16", "False", "--output_dir", str(tmp_path / "results"),
+           "--num_train_epochs", "1", "--per_device_train_batch_size", "1", "--per_device_eval_batch_size", "1",
+           "--gradient_accumulation_steps", "2", "--gradient_checkpointing", "True", "--evaluation_strategy", "no",
+           "--save_strategy", "no", "--learning_rate", "5e-5", "--lr_scheduler_type", "linear", "--logging_steps", "1",
+           "--use_megablocks_sharding", "True", "--model_preset", "tiny", "--device_type", "cpu", "--num_synthetic_examples", "4"]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=root)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    assert "train_runtime" in p.stdout

@@ -17,7 +17,10 @@ from moe_distributed_training_b200.train.run import run_training
 def main(
     use_megablocks_sharding: bool = False,
     truncate_model_for_debug: bool = False,
+    accelerator_config: str = None,
     per_device_train_batch_size: int = 1,
+    per_device_eval_batch_size: int = 1,
+    evaluation_strategy: str = "no",
     gradient_accumulation_steps: int = 1,
     learning_rate: float = 5e-5,
     lr_scheduler_type: str = "linear",
@@ -39,6 +42,14 @@ def main(
     max_steps: int = 0,
     seed: int = 0,
 ):
+    if evaluation_strategy != "no":
+        raise ValueError("evaluation_strategy: only 'no' is supported (the reference runs no evaluation either)")
+    sync_each_batch = True       # what the reference's accelerator_config.json sets (accelerator_config.json:1-4)
+    if accelerator_config:
+        import json
+        with open(accelerator_config) as f:
+            ga = json.load(f).get("gradient_accumulation_kwargs") or {}
+        sync_each_batch = bool(ga.get("sync_each_batch", sync_each_batch))
     return run_training(
         max_seq_length=max_seq_length, load_model_dtype="bfloat16" if bf16 else torch_dtype,
         per_device_train_batch_size=per_device_train_batch_size,
@@ -48,7 +59,7 @@ def main(
         learning_rate=learning_rate, truncate_model_for_debug=truncate_model_for_debug,
         expert_degree=None, use_lora="none", model_name_or_path=model_name_or_path, model_preset=model_preset,
         data_path=data_path, num_synthetic_examples=num_synthetic_examples, device_type=device_type,
-        sync_each_batch=True, seed=seed, max_steps=max_steps, activation_checkpointing=gradient_checkpointing,
+        sync_each_batch=sync_each_batch, seed=seed, max_steps=max_steps, activation_checkpointing=gradient_checkpointing,
         save_path=None if save_strategy == "no" else output_dir, sharding_strategy="fsdp1")
 
 
