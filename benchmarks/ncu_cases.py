@@ -59,11 +59,11 @@ def main():
             for r, w in enumerate(spaces):
                 C.ext.ep_counts_wait_meta(w.my_base, w.layout, r, par, epoch, metas[r], status)
             for r, w in enumerate(spaces):
-                C.ext.ep_dispatch(xs[r], plans[r].src_slot, tops[r].reshape(-1).contiguous(), None, metas[r], w.peer_base, w.layout, k, par)
+                C.ext.ep_dispatch(xs[r], plans[r].src_slot, tops[r].reshape(-1).contiguous(), None, metas[r], w.peer_base, w.layout, r, k, par, status)
             for r, w in enumerate(spaces):
                 C.ext.ep_recv_prepare(w.my_base, w.layout, metas[r], H, par, status, True)
             for r, w in enumerate(spaces):
-                C.ext.ep_combine_send(w.recv_x(), metas[r], w.peer_base, w.layout, r, w.capacity_rows, par)
+                C.ext.ep_combine_send(w.recv_x(), metas[r], w.peer_base, w.layout, r, w.capacity_rows, par, status)
             for r, w in enumerate(spaces):
                 C.ext.ep_wait_rows(w.my_base, w.layout, metas[r], par, status, 1)
     elif case == "gemm_exchange":
@@ -91,7 +91,7 @@ def main():
             for r, w in enumerate(spaces_in):
                 C.ext.ep_counts_wait_meta(w.my_base, w.layout, r, par, epoch, metas[r], status)
             for r, w in enumerate(spaces_in):
-                C.ext.ep_dispatch(xs[r], plans[r].src_slot, tops[r].reshape(-1).contiguous(), None, metas[r], w.peer_base, w.layout, k, par)
+                C.ext.ep_dispatch(xs[r], plans[r].src_slot, tops[r].reshape(-1).contiguous(), None, metas[r], w.peer_base, w.layout, r, k, par, status)
             for r, w in enumerate(spaces_in):
                 C.ext.ep_recv_prepare(w.my_base, w.layout, metas[r], H, par, status, False)
             for r, (wi, wo) in enumerate(zip(spaces_in, spaces_out)):

@@ -9,6 +9,15 @@ extern "C" {
 #endif
 
 // ---- GEMM family (gemm_sm100.cu) -------------------------------------------------------------
+// Readiness of an operand that lies inside a buffer which an all-gather (mdt_ag_pull with progress flags, csrc/comm.h)
+// is still filling on another stream.  The buffer consists of shards of `shard_bytes`, each cut into
+// `chunks_per_rank` chunks of `chunk_bytes`; ready[shard * chunks_per_rank + chunk] reaches `epoch` when that chunk
+// has landed.  `offset_bytes` is the operand's offset inside the buffer.  ready == NULL: the operand is complete.
+typedef struct MdtOperandReady {
+  const unsigned* ready; unsigned epoch; int chunks_per_rank;
+  long long offset_bytes, shard_bytes, chunk_bytes;
+} MdtOperandReady;
+
 typedef struct MdtGemmDesc {
   int mode;            // 0 dense, 1 grouped rows, 2 grouped depth (weight gradient)
   int M, N, K;         // mode 0/1: C is [M(or capacity), N], depth K.  mode 2: C_g is [M, N], depth = rows of g (K if offsets == NULL)
@@ -38,6 +47,10 @@ typedef struct MdtGemmDesc {
   // buffer peer_out[row_dest_rank[r]] (bf16, row stride ldc; rank < 0: row dropped) and then adds, per tile and
   // destination, the number of rows delivered to the counter peer_arrive[rank] (release, system scope).
   const int* row_dest_rank; const int* row_dest_row; const long long* peer_out; const long long* peer_arrive; int num_peers;
+  // mode 0/1, optional: B (B2) is still being gathered from the peers' shards.  Before a CTA loads the part of B that
+  // an output tile needs it waits (bounded) for the chunks that hold it, so the product starts on the weights that
+  // have arrived (the local shard first) while the rest of the all-gather is in flight.
+  MdtOperandReady b_ready, b2_ready;
 } MdtGemmDesc;
 
 int mdt_gemm(const MdtGemmDesc* desc, cudaStream_t stream);

@@ -19,6 +19,7 @@
 #include <mutex>
 
 #include "api.h"
+#include "common/host.h"
 #include "common/ptx.cuh"
 
 namespace mdt {
@@ -505,7 +506,8 @@ extern "C" int mdt_attention_bwd(const void* q, const void* k, const void* v, co
   ++g_att_launches;
   const long long total = th * HD + 2LL * total_tokens * heads_kv * HD;
   long long blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  const long long cap = (long long)sm_count_of_current_device() * 16;
+  if (blocks > cap) blocks = cap;
   attn_bwd_finalize_kernel<<<(unsigned)blocks, 256, 0, s>>>(dq32, dk32, dv32, (bf16*)dq, (bf16*)dk, (bf16*)dv, total_tokens, heads_q, heads_kv);
   ++g_att_launches;
   cudaError_t e = cudaGetLastError();

@@ -5,6 +5,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <mutex>
 #include <optional>
 #include <vector>
 
@@ -33,6 +34,35 @@ static void fill_operand3(const Tensor& t, long long& rows, long long& cols, lon
   if (t.dim() == 2) { fill_operand(t, rows, cols, ld); gs = rows * ld; return; }
   TORCH_CHECK(t.dim() == 3 && t.stride(2) == 1, "B must be [G, rows, cols] with unit inner stride");
   rows = t.size(1); cols = t.size(2); ld = t.stride(1); gs = t.stride(0);
+}
+
+// ---- buffers that an all-gather with progress flags is filling (or has filled) -----------------------------------
+// ag_pull_flagged() records (buffer range -> flags, epoch, chunk geometry) here; gemm() looks its B operands up and,
+// on a hit, lets the kernel wait for the chunks it needs instead of the whole gather.  An entry keeps its flag tensor
+// alive and stays until the same buffer is gathered again: flags of a finished gather all equal the epoch, so a
+// product whose operand merely lies in memory that used to be such a buffer passes its waits at once.
+namespace {
+struct PendingGather { uintptr_t base; int64_t bytes; Tensor ready; unsigned epoch; int chunks_per_rank; int64_t shard_bytes, chunk_bytes; };
+std::mutex g_pending_mutex;
+std::vector<PendingGather> g_pending;
+void lookup_ready(const void* ptr, MdtOperandReady* out) {
+  out->ready = nullptr;
+  if (ptr == nullptr) return;
+  const uintptr_t a = reinterpret_cast<uintptr_t>(ptr);
+  std::lock_guard<std::mutex> lock(g_pending_mutex);
+  for (const auto& e : g_pending) {
+    if (a >= e.base && a < e.base + (uintptr_t)e.bytes) {
+      out->ready = (const unsigned*)e.ready.data_ptr();
+      out->epoch = e.epoch; out->chunks_per_rank = e.chunks_per_rank;
+      out->offset_bytes = (long long)(a - e.base); out->shard_bytes = e.shard_bytes; out->chunk_bytes = e.chunk_bytes;
+      return;
+    }
+  }
+}
+}  // namespace
+void gather_registry_clear() {
+  std::lock_guard<std::mutex> lock(g_pending_mutex);
+  g_pending.clear();
 }
 
 // C = alpha * op(A) op(B) (+ LoRA segment) with the options of MdtGemmDesc; see csrc/api.h
@@ -78,6 +108,10 @@ void gemm(int64_t mode, const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, 
     d.peer_out = (const long long*)peer_out->data_ptr<int64_t>(); d.peer_arrive = (const long long*)peer_arrive->data_ptr<int64_t>();
     d.num_peers = (int)peer_out->numel();
   }
+  if (mode != 2) {
+    lookup_ready(d.B, &d.b_ready);
+    if (d.dual) lookup_ready(d.B2, &d.b2_ready);
+  }
   check(mdt_gemm(&d, cur_stream()), "mdt_gemm");
 }
 
@@ -96,7 +130,8 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& w, const Tensor& 
   auto dy2 = dy.reshape({-1, x.size(-1)}).contiguous();
   auto dx = torch::empty_like(x2);
   const int rows = (int)x2.size(0), cols = (int)x2.size(1);
-  const int np = rows < 148 ? (rows < 1 ? 1 : rows) : 148;
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  const int np = rows < sms ? (rows < 1 ? 1 : rows) : sms;
   auto dwp = torch::empty({np, cols}, x.options().dtype(at::kFloat));
   check(mdt_rmsnorm_bwd(x2.data_ptr(), w.data_ptr(), dy2.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(), dwp.data_ptr<float>(), rows, cols, np, cur_stream()), "rmsnorm_bwd");
   return {dx.view(x.sizes()), dwp};
@@ -305,22 +340,25 @@ void ep_counts_wait_meta(int64_t my_base, std::vector<int64_t> layout, int64_t r
   check(mdt_ep_counts_wait_meta(my_base, L, (int)rank, (int)parity, (unsigned)epoch, meta.data_ptr<int>(), status.data_ptr<int>(), cur_stream()), "ep_counts_wait_meta");
 }
 void ep_dispatch(const Tensor& x, const Tensor& src_slot, const Tensor& expert_of_slot, const OptTensor& slot_scale, const Tensor& meta,
-                 const Tensor& peer_base, std::vector<int64_t> layout, int64_t top_k, int64_t parity) {
+                 const Tensor& peer_base, std::vector<int64_t> layout, int64_t rank, int64_t top_k, int64_t parity, const OptTensor& status) {
   CHECK_BF16(x);
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.is_contiguous() && expert_of_slot.scalar_type() == at::kInt && expert_of_slot.is_contiguous());
   check(mdt_ep_dispatch(x.data_ptr(), src_slot.data_ptr<int>(), expert_of_slot.data_ptr<int>(), cptr(slot_scale), meta.data_ptr<int>(), ptrs(peer_base),
-                        to_layout(layout), (int)expert_of_slot.numel(), (int)top_k, (int)x.size(1), (int)parity, cur_stream()), "ep_dispatch");
+                        to_layout(layout), (int)rank, (int)expert_of_slot.numel(), (int)top_k, (int)x.size(1), (int)parity,
+                        status.has_value() ? status->data_ptr<int>() : nullptr, cur_stream()), "ep_dispatch");
 }
 void ep_recv_prepare(int64_t my_base, std::vector<int64_t> layout, const Tensor& meta, int64_t cols, int64_t parity, Tensor& status, bool wait_all) {
   c10::cuda::CUDAGuard guard(meta.device());
   check(mdt_ep_recv_prepare(my_base, to_layout(layout), meta.data_ptr<int>(), (int)cols, (int)parity, wait_all, status.data_ptr<int>(), cur_stream()), "ep_recv_prepare");
 }
-void ep_combine_send(const Tensor& y, const Tensor& meta, const Tensor& peer_base, std::vector<int64_t> layout, int64_t rank, int64_t max_rows, int64_t parity) {
+void ep_combine_send(const Tensor& y, const Tensor& meta, const Tensor& peer_base, std::vector<int64_t> layout, int64_t rank, int64_t max_rows,
+                     int64_t parity, const OptTensor& status) {
   CHECK_BF16(y);
   c10::cuda::CUDAGuard guard(y.device());
   TORCH_CHECK(y.is_contiguous());
-  check(mdt_ep_combine_send(y.data_ptr(), meta.data_ptr<int>(), ptrs(peer_base), to_layout(layout), (int)rank, (int)max_rows, (int)y.size(1), (int)parity, cur_stream()), "ep_combine_send");
+  check(mdt_ep_combine_send(y.data_ptr(), meta.data_ptr<int>(), ptrs(peer_base), to_layout(layout), (int)rank, (int)max_rows, (int)y.size(1), (int)parity,
+                            status.has_value() ? status->data_ptr<int>() : nullptr, cur_stream()), "ep_combine_send");
 }
 void ep_wait_rows(int64_t my_base, std::vector<int64_t> layout, const Tensor& meta, int64_t parity, Tensor& status, int64_t mult) {
   c10::cuda::CUDAGuard guard(meta.device());
@@ -341,14 +379,54 @@ std::vector<int64_t> ep_meta_offsets(int64_t ws, int64_t E) {
   return {mdt_ep_meta_counts(ws, E), mdt_ep_meta_recv_tot(ws, E), mdt_ep_meta_recv_off(ws, E), mdt_ep_meta_dst_row(ws, E),
           mdt_ep_meta_send_start(ws, E), mdt_ep_meta_seg_row(ws, E), mdt_ep_meta_seg_pos(ws, E), mdt_ep_meta_scalars(ws, E), mdt_ep_meta_size(ws, E)};
 }
-void ag_pull(Tensor& out, const Tensor& peer_shard, int64_t ws, int64_t bytes_per_rank) {
+void ag_pull(Tensor& out, const Tensor& peer_shard, int64_t ws, int64_t rank, int64_t bytes_per_rank, int64_t max_ctas) {
   c10::cuda::CUDAGuard guard(out.device());
-  check(mdt_ag_pull(out.data_ptr(), ptrs(peer_shard), (int)ws, bytes_per_rank, cur_stream()), "ag_pull");
+  check(mdt_ag_pull(out.data_ptr(), ptrs(peer_shard), (int)ws, (int)rank, bytes_per_rank, nullptr, 0, 0, (int)max_ctas, cur_stream()), "ag_pull");
+}
+// Number of progress flags of a gathered buffer with shards of `bytes_per_rank` bytes, and the chunk size in bytes.
+std::vector<int64_t> ag_chunks(int64_t ws, int64_t bytes_per_rank) {
+  return {(int64_t)mdt_ag_chunks_per_rank(bytes_per_rank) * ws, (int64_t)mdt_ag_chunk_bytes(bytes_per_rank)};
+}
+// All-gather that publishes its progress in `ready` (int32 [ws * chunks per rank], values only ever grow; `epoch` must
+// exceed every earlier epoch used with these flags) and registers the buffer, so that products whose weight operand
+// lies inside it wait chunk by chunk.  Chunks [0, priority_chunks) of the buffer are fetched before all others.
+void ag_pull_flagged(Tensor& out, const Tensor& peer_shard, int64_t ws, int64_t rank, int64_t bytes_per_rank, Tensor& ready, int64_t epoch,
+                     int64_t priority_chunks, int64_t max_ctas) {
+  c10::cuda::CUDAGuard guard(out.device());
+  const int cpr = mdt_ag_chunks_per_rank(bytes_per_rank);
+  TORCH_CHECK(ready.scalar_type() == at::kInt && ready.is_contiguous() && ready.numel() >= (int64_t)cpr * ws, "ready: int32 [ws * chunks per rank]");
+  TORCH_CHECK(out.is_contiguous() && out.numel() * out.element_size() >= bytes_per_rank * ws);
+  {
+    std::lock_guard<std::mutex> lock(g_pending_mutex);
+    const uintptr_t base = reinterpret_cast<uintptr_t>(out.data_ptr());
+    PendingGather e{base, bytes_per_rank * ws, ready, (unsigned)epoch, cpr, bytes_per_rank, mdt_ag_chunk_bytes(bytes_per_rank)};
+    bool found = false;
+    for (auto& old : g_pending) {
+      // a new gather into overlapping memory replaces what was known about it
+      if (base < old.base + (uintptr_t)old.bytes && old.base < base + (uintptr_t)e.bytes) { if (!found) { old = e; found = true; } else { old.bytes = 0; } }
+    }
+    if (!found) g_pending.push_back(e);
+  }
+  check(mdt_ag_pull(out.data_ptr(), ptrs(peer_shard), (int)ws, (int)rank, bytes_per_rank, (unsigned*)ready.data_ptr(), (unsigned)epoch, (int)priority_chunks,
+                    (int)max_ctas, cur_stream()), "ag_pull");
+}
+// the current stream waits (one small kernel) until chunks [first, last) of a flagged gather have landed
+void ag_wait_chunks(const Tensor& ready, int64_t first, int64_t last, int64_t epoch, Tensor& status) {
+  c10::cuda::CUDAGuard guard(ready.device());
+  check(mdt_ag_wait_chunks((const unsigned*)ready.data_ptr(), (int)first, (int)last, (unsigned)epoch, status.data_ptr<int>(), cur_stream()), "ag_wait_chunks");
 }
 void rs_pull(Tensor& out, const Tensor& peer_full, int64_t ws, int64_t rank, bool in_fp32, double scale, bool accumulate) {
   c10::cuda::CUDAGuard guard(out.device());
   TORCH_CHECK(out.is_contiguous());
   check(mdt_rs_pull(out.data_ptr(), ptrs(peer_full), (int)ws, (int)rank, out.numel(), in_fp32, out.scalar_type() == at::kFloat, (float)scale, accumulate, cur_stream()), "rs_pull");
+}
+// announce + wait + reduce-scatter of one group in one kernel (csrc/comm.cu::rs_block_kernel)
+void rs_block(Tensor& out, const Tensor& peer_full, const Tensor& peer_flags, int64_t my_flags, int64_t flag_index, int64_t ws, int64_t rank,
+              bool in_fp32, double scale, bool accumulate, int64_t epoch, Tensor& status, int64_t max_ctas) {
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(out.is_contiguous());
+  check(mdt_rs_block(out.data_ptr(), ptrs(peer_full), ptrs(peer_flags), my_flags, (int)flag_index, (int)ws, (int)rank, out.numel(), in_fp32,
+                     out.scalar_type() == at::kFloat, (float)scale, accumulate, (unsigned)epoch, status.data_ptr<int>(), (int)max_ctas, cur_stream()), "rs_block");
 }
 void barrier_arrive(const Tensor& peer_flags, int64_t ws, int64_t rank, int64_t epoch) {
   c10::cuda::CUDAGuard guard(peer_flags.device());
@@ -632,7 +710,7 @@ std::vector<Tensor> moe_block_fwd(const Tensor& x, const Tensor& ln_w, const Ten
     rr = fm[0]; rp = fm[1]; te = fm[2];
     Tensor eos = idx.view({-1});
     if (keep) expert_sorted = eos.index_select(0, plan[3].to(at::kLong));
-    ep_dispatch(xn, plan[3], eos, NONE, meta_c, ep[0], layout, top_k, dpar);
+    ep_dispatch(xn, plan[3], eos, NONE, meta_c, ep[0], layout, rank, top_k, dpar, status);
     ep_recv_prepare(my_base, layout, meta_c, H, dpar, st, false);
     xg = ep[4];
     const int o2 = mdt_ep_meta_recv_off(L.ws, L.num_experts);
@@ -690,7 +768,7 @@ std::vector<Tensor> moe_block_bwd(const Tensor& dy, const std::vector<Tensor>& s
   } else {
     const int64_t my_base = ep_ints[0], dpar = ep_ints[4];
     MdtEpLayout L = to_layout(layout);
-    ep_dispatch(d_rows, ep[6].narrow(0, 0, n_slots), expert_sorted, NONE, meta_c, ep[0], layout, 1, dpar);
+    ep_dispatch(d_rows, ep[6].narrow(0, 0, n_slots), expert_sorted, NONE, meta_c, ep[0], layout, ep_ints[1], 1, dpar, status);
     ep_recv_prepare(my_base, layout, meta_c, H, dpar, st, false);
     dyg = ep[4]; cap = L.capacity_rows;
     w0 = ep[3]; w1o = te; s0 = rr; s1 = rp; s2 = ep[1]; s3 = ep[2];
@@ -760,13 +838,23 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attention_bwd", &attention_bwd);
   m.def("ep_counts_send", &ep_counts_send);
   m.def("ep_counts_wait_meta", &ep_counts_wait_meta);
-  m.def("ep_dispatch", &ep_dispatch);
+  m.def("ep_dispatch", &ep_dispatch, py::arg("x"), py::arg("src_slot"), py::arg("expert_of_slot"), py::arg("slot_scale"), py::arg("meta"),
+        py::arg("peer_base"), py::arg("layout"), py::arg("rank"), py::arg("top_k"), py::arg("parity"), py::arg("status") = py::none());
   m.def("ep_recv_prepare", &ep_recv_prepare);
-  m.def("ep_combine_send", &ep_combine_send);
+  m.def("ep_combine_send", &ep_combine_send, py::arg("y"), py::arg("meta"), py::arg("peer_base"), py::arg("layout"), py::arg("rank"),
+        py::arg("max_rows"), py::arg("parity"), py::arg("status") = py::none());
   m.def("ep_wait_rows", &ep_wait_rows);
   m.def("ep_fused_meta", &ep_fused_meta);
   m.def("ep_meta_offsets", &ep_meta_offsets);
-  m.def("ag_pull", &ag_pull);
+  m.def("ag_pull", &ag_pull, py::arg("out"), py::arg("peer_shard"), py::arg("ws"), py::arg("rank"), py::arg("bytes_per_rank"), py::arg("max_ctas") = 0);
+  m.def("ag_pull_flagged", &ag_pull_flagged, py::arg("out"), py::arg("peer_shard"), py::arg("ws"), py::arg("rank"), py::arg("bytes_per_rank"),
+        py::arg("ready"), py::arg("epoch"), py::arg("priority_chunks") = 0, py::arg("max_ctas") = 0);
+  m.def("ag_chunks", &ag_chunks);
+  m.def("ag_wait_chunks", &ag_wait_chunks);
+  m.def("gather_registry_clear", &gather_registry_clear);
+  m.def("rs_block", &rs_block, py::arg("out"), py::arg("peer_full"), py::arg("peer_flags"), py::arg("my_flags"), py::arg("flag_index"), py::arg("ws"),
+        py::arg("rank"), py::arg("in_fp32"), py::arg("scale"), py::arg("accumulate"), py::arg("epoch"), py::arg("status"), py::arg("max_ctas") = 0);
+  m.def("set_peer_wait_limit_ms", [](int64_t ms) { mdt_set_peer_wait_limit_ms((long long)ms); });
   m.def("rs_pull", &rs_pull);
   m.def("barrier_arrive", &barrier_arrive);
   m.def("barrier_wait", &barrier_wait);

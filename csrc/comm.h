@@ -41,18 +41,34 @@ extern "C" {
 #endif
 int mdt_ep_counts_send(const int* counts, const long long* peer_base, MdtEpLayout L, int rank, int parity, unsigned epoch, cudaStream_t s);
 int mdt_ep_counts_wait_meta(long long my_base, MdtEpLayout L, int rank, int parity, unsigned epoch, int* meta, int* status, cudaStream_t s);
+// `status` (device word, may be NULL): a kernel of an exchange returns at once when it is already non-zero.
 int mdt_ep_dispatch(const void* x, const int* src_slot, const int* expert_of_slot, const void* slot_scale, const int* meta,
-                    const long long* peer_base, MdtEpLayout L, int num_slots, int top_k, int cols, int parity, cudaStream_t s);
+                    const long long* peer_base, MdtEpLayout L, int rank, int num_slots, int top_k, int cols, int parity,
+                    const int* status, cudaStream_t s);
 int mdt_ep_recv_prepare(long long my_base, MdtEpLayout L, const int* meta, int cols, int parity, int wait_all, int* status, cudaStream_t s);
 int mdt_ep_fused_meta(const int* meta, MdtEpLayout L, int rank, int* row_rank, int* row_pos, int* tile_expected, cudaStream_t s);
 int mdt_ep_combine_send(const void* y, const int* meta, const long long* peer_base, MdtEpLayout L, int rank, int max_rows, int cols,
-                        int parity, cudaStream_t s);
+                        int parity, const int* status, cudaStream_t s);
 int mdt_ep_wait_rows(long long my_base, MdtEpLayout L, const int* meta, int parity, int mult, int* status, cudaStream_t s);
-int mdt_ag_pull(void* out, const long long* peer_shard, int ws, long long bytes_per_rank, cudaStream_t s);
+// All-gather by peer reads with optional progress flags: the buffer is cut into mdt_ag_chunks_per_rank() chunks per
+// shard of mdt_ag_chunk_bytes() bytes; ready[r * chunks_per_rank + c] = epoch once chunk c of rank r's shard has landed.
+long long mdt_ag_chunk_bytes(long long bytes_per_rank);
+int mdt_ag_chunks_per_rank(long long bytes_per_rank);
+// The first `prio_chunks` chunks of the buffer are fetched before all others.
+int mdt_ag_pull(void* out, const long long* peer_shard, int ws, int rank, long long bytes_per_rank, unsigned* ready, unsigned epoch,
+                int prio_chunks, int max_ctas, cudaStream_t s);
+int mdt_ag_wait_chunks(const unsigned* ready, int first, int last, unsigned epoch, int* status, cudaStream_t s);
 int mdt_rs_pull(void* out, const long long* peer_full, int ws, int rank, long long n, int in_fp32, int out_fp32, float scale,
                 int accumulate, cudaStream_t s);
+// announce + wait + reduce in one kernel (see rs_block_kernel); flag tables hold u32 [slots][ws]
+int mdt_rs_block(void* out, const long long* peer_full, const long long* peer_flags, long long my_flags, int flag_index, int ws, int rank,
+                 long long n, int in_fp32, int out_fp32, float scale, int accumulate, unsigned epoch, int* status, int max_ctas,
+                 cudaStream_t s);
 int mdt_barrier_arrive(const long long* peer_flags, int ws, int rank, unsigned epoch, cudaStream_t s);
 int mdt_barrier_wait(const void* my_flags, int ws, unsigned epoch, int* status, long long limit_ms, cudaStream_t s);  // limit_ms <= 0: default
+// limit of every wait for a peer (also the GEMM's waits for operands that other GPUs or streams deliver); ms <= 0 restores 10 s
+void mdt_set_peer_wait_limit_ms(long long ms);
+unsigned long long mdt_peer_wait_limit_ns(void);
 long long mdt_comm_launch_count(void);
 #ifdef __cplusplus
 }

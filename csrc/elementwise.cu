@@ -5,6 +5,7 @@
 #include <stdint.h>
 
 #include "api.h"
+#include "common/host.h"
 
 namespace mdt {
 
@@ -378,7 +379,9 @@ __global__ void __launch_bounds__(256) axpby_kernel(void* __restrict__ y, const 
   }
 }
 
-static inline int grid_for(long long work_items, int block, int cap = 148 * 16) {
+// cap: upper bound on the grid in CTAs; <= 0 means -cap CTAs per SM of the current device (default 16 per SM)
+static inline int grid_for(long long work_items, int block, int cap = -16) {
+  if (cap <= 0) cap = sm_count_of_current_device() * -cap;
   long long g = (work_items + block - 1) / block;
   return (int)(g < 1 ? 1 : (g > cap ? cap : g));
 }
@@ -465,14 +468,14 @@ extern "C" int mdt_cross_entropy(void* logits, const long long* labels, float* l
 extern "C" int mdt_adamw(const MdtAdamTensor* tensors_device, int num_tensors, long long max_n, float lr, float beta1, float beta2,
                          float eps, float weight_decay, float bc1, float bc2, float grad_scale, cudaStream_t s) {
   if (num_tensors == 0) return 0;
-  dim3 grid(grid_for((max_n + 7) / 8, 256, 148 * 16), num_tensors);
+  dim3 grid(grid_for((max_n + 7) / 8, 256, -16), num_tensors);
   adamw_kernel<<<grid, 256, 0, s>>>(tensors_device, lr, beta1, beta2, eps, weight_decay, 1.0f / bc1, 1.0f / bc2, grad_scale);
   MDT_CHECK_LAUNCH();
   return 0;
 }
 extern "C" int mdt_sumsq(const void* x, long long n, int fp32, float* out_accum, cudaStream_t s) {
   if (n == 0) return 0;
-  sumsq_kernel<<<grid_for(n, 256 * 8, 148 * 4), 256, 0, s>>>(x, n, fp32, out_accum);
+  sumsq_kernel<<<grid_for(n, 256 * 8, -4), 256, 0, s>>>(x, n, fp32, out_accum);
   MDT_CHECK_LAUNCH();
   return 0;
 }

@@ -31,6 +31,7 @@
 #include <tuple>
 
 #include "api.h"
+#include "comm.h"
 #include "common/ptx.cuh"
 
 namespace mdt {
@@ -54,10 +55,42 @@ struct GemmParams {
   int* status;
   const unsigned* tile_ready; const int* tile_expected;
   const int* row_dest_rank; const int* row_dest_row; const long long* peer_out; const long long* peer_arrive; int num_peers;
+  unsigned long long peer_wait_ns;   // limit of the waits for operands that other GPUs or streams deliver
+  // B (and B2) may be part of a buffer that an all-gather is still filling: see MdtGemmDesc::b_ready
+  MdtOperandReady rdy_b, rdy_b2;
+  long long b_rows, ldb, b_group_stride;
 };
-#ifndef MDT_GEMM_PEER_WAIT_NS
-#define MDT_GEMM_PEER_WAIT_NS 10000000000ull
-#endif
+
+// Bounded wait until the chunks of the gathered buffer that hold bytes [off, off + len) of an operand have landed.
+__device__ __forceinline__ bool wait_operand_ready(const MdtOperandReady& r, long long off, long long len, unsigned long long limit_ns) {
+  if (r.ready == nullptr || len <= 0) return true;
+  const long long o0 = r.offset_bytes + off, o1 = o0 + len - 1;
+  const int c0 = (int)(o0 / r.shard_bytes) * r.chunks_per_rank + (int)((o0 % r.shard_bytes) / r.chunk_bytes);
+  const int c1 = (int)(o1 / r.shard_bytes) * r.chunks_per_rank + (int)((o1 % r.shard_bytes) / r.chunk_bytes);
+  for (int c = c0; c <= c1; ++c)
+    if (!wait_ge(r.ready + c, r.epoch, limit_ns)) return false;
+  return true;
+}
+// The part of B that the tile (group g, columns from n0, `rows` output columns) reads: whole rows of a K-major B,
+// the whole matrix of the group for an MN-major one.
+__device__ __forceinline__ bool wait_b_tile(const GemmParams& p, int g, int n0, int rows) {
+  if (p.rdy_b.ready == nullptr && p.rdy_b2.ready == nullptr) return true;
+  long long off, len;
+  if (p.b_mn == 0) {
+    const long long r = (long long)rows < p.b_rows - n0 ? rows : p.b_rows - n0;
+    off = ((long long)g * p.b_group_stride + (long long)n0 * p.ldb) * 2;
+    len = r * p.ldb * 2;
+  } else {
+    off = (long long)g * p.b_group_stride * 2;
+    len = p.b_rows * p.ldb * 2;
+  }
+  return wait_operand_ready(p.rdy_b, off, len, p.peer_wait_ns) && wait_operand_ready(p.rdy_b2, off, len, p.peer_wait_ns);
+}
+// A GEMM that takes part in an exchange does nothing when the status word is already set (an earlier wait of the
+// exchange ran out: its metadata describe no rows and nothing may be stored into a peer on the strength of them).
+__device__ __forceinline__ bool gemm_dead(const GemmParams& p) {
+  return p.status != nullptr && (p.tile_ready != nullptr || p.row_dest_rank != nullptr) && *reinterpret_cast<const volatile int*>(p.status) != 0;
+}
 
 struct Tile {
   int g, m0, n0, krow0, num_kb, num_kb_l;
@@ -164,7 +197,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     if (p.status != nullptr) atomicCAS(p.status, 0, code);
   };
 
-  if (warp == 0 && lane == 0) {
+  const bool dead = gemm_dead(p);
+  if (dead) {
+    // nothing to do; fall through to the common exit
+  } else if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------------ TMA producer
     prefetch_tensormap(&p.tmA); prefetch_tensormap(&p.tmB);
     uint32_t it = 0;
@@ -175,7 +211,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       if (p.tile_ready != nullptr) {
         // rows of this tile are stored by peer GPUs: wait for them, then order the TMA reads after the acquire
         const int ti = t.m0 / BM;
-        if (!wait_ge(p.tile_ready + ti, (unsigned)p.tile_expected[ti], MDT_GEMM_PEER_WAIT_NS)) { fail(ST_TIMEOUT_PEER); ok = false; break; }
+        if (!wait_ge(p.tile_ready + ti, (unsigned)p.tile_expected[ti], p.peer_wait_ns)) { fail(ST_TIMEOUT_PEER); ok = false; break; }
+        fence_proxy_async_all();
+      }
+      if (p.mode != 2 && total_kb > 0 && (p.rdy_b.ready != nullptr || p.rdy_b2.ready != nullptr)) {
+        // the weight operand is part of a buffer that an all-gather on another stream is still filling
+        if (!wait_b_tile(p, t.g, t.n0, BN_OUT)) { fail(ST_TIMEOUT_PEER); ok = false; break; }
         fence_proxy_async_all();
       }
       for (int kb = 0; kb < total_kb; ++kb, ++it) {
@@ -277,8 +318,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
       bool store_ok = row_ok;
       if (p.row_dest_rank != nullptr) {          // result rows go straight into peers' buffers
         dest = row_ok ? p.row_dest_rank[row] : -1;
+        const int drow = row_ok ? p.row_dest_row[row] : -1;
+        if (dest >= p.num_peers || drow < 0) dest = -1;
         store_ok = dest >= 0;
-        if (store_ok) { Cout = reinterpret_cast<void*>(p.peer_out[dest]); base = (long long)p.row_dest_row[row] * p.ldc; }
+        if (store_ok) { Cout = reinterpret_cast<void*>(p.peer_out[dest]); base = (long long)drow * p.ldc; }
       }
       if (total_kb == 0) {
         if (!p.accumulate && row_ok) {
@@ -471,7 +514,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1) gem
     if (p.status != nullptr) atomicCAS(p.status, 0, code);
   };
 
-  if (warp == 0 && lane == 0) {
+  const bool dead = gemm_dead(p);   // the same in both CTAs of the pair: the word never returns to zero while kernels run
+  if (dead) {
+    // nothing to do; fall through to the common exit
+  } else if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------------ TMA producer (one per CTA)
     prefetch_tensormap(&p.tmA); prefetch_tensormap(&p.tmB);
     uint32_t it = 0;
@@ -483,7 +529,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1) gem
       const bool half_ok = cta_rank == 0 || t.second_ok;
       if (p.tile_ready != nullptr && half_ok && total_kb > 0) {
         const int ti = my_m0 / BM;
-        if (!wait_ge(p.tile_ready + ti, (unsigned)p.tile_expected[ti], MDT_GEMM_PEER_WAIT_NS)) { fail(ST_TIMEOUT_PEER); ok = false; break; }
+        if (!wait_ge(p.tile_ready + ti, (unsigned)p.tile_expected[ti], p.peer_wait_ns)) { fail(ST_TIMEOUT_PEER); ok = false; break; }
+        fence_proxy_async_all();
+      }
+      if (p.mode != 2 && total_kb > 0 && (p.rdy_b.ready != nullptr || p.rdy_b2.ready != nullptr)) {
+        if (!wait_b_tile(p, t.g, t.n0, BN_OUT)) { fail(ST_TIMEOUT_PEER); ok = false; break; }
         fence_proxy_async_all();
       }
       for (int kb = 0; kb < total_kb; ++kb, ++it) {
@@ -578,8 +628,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1) gem
       bool store_ok = row_ok;
       if (p.row_dest_rank != nullptr) {          // result rows go straight into peers' buffers
         dest = row_ok ? p.row_dest_rank[row] : -1;
+        const int drow = row_ok ? p.row_dest_row[row] : -1;
+        if (dest >= p.num_peers || drow < 0) dest = -1;
         store_ok = dest >= 0;
-        if (store_ok) { Cout = reinterpret_cast<void*>(p.peer_out[dest]); base = (long long)p.row_dest_row[row] * p.ldc; }
+        if (store_ok) { Cout = reinterpret_cast<void*>(p.peer_out[dest]); base = (long long)drow * p.ldc; }
       }
       if (total_kb == 0) {
         if (!p.accumulate && row_ok) {
@@ -744,7 +796,10 @@ __global__ void __launch_bounds__(TALL_THREADS, 1) gemm_sm100_tall_kernel(const 
     if (p.status != nullptr) atomicCAS(p.status, 0, code);
   };
 
-  if (warp == 0 && lane == 0) {
+  const bool dead = gemm_dead(p);
+  if (dead) {
+    // nothing to do; fall through to the common exit
+  } else if (warp == 0 && lane == 0) {
     // ------------------------------------------------------------------ TMA producer
     prefetch_tensormap(&p.tmA); prefetch_tensormap(&p.tmB);
     uint32_t it = 0;
@@ -755,9 +810,13 @@ __global__ void __launch_bounds__(TALL_THREADS, 1) gemm_sm100_tall_kernel(const 
       if (p.tile_ready != nullptr && total_kb > 0) {
         for (int h = 0; h < (t.second_ok ? 2 : 1) && ok; ++h) {
           const int ti = t.m0 / BM + h;
-          if (!wait_ge(p.tile_ready + ti, (unsigned)p.tile_expected[ti], MDT_GEMM_PEER_WAIT_NS)) { fail(ST_TIMEOUT_PEER); ok = false; }
+          if (!wait_ge(p.tile_ready + ti, (unsigned)p.tile_expected[ti], p.peer_wait_ns)) { fail(ST_TIMEOUT_PEER); ok = false; }
         }
         if (!ok) break;
+        fence_proxy_async_all();
+      }
+      if (p.mode != 2 && total_kb > 0 && (p.rdy_b.ready != nullptr || p.rdy_b2.ready != nullptr)) {
+        if (!wait_b_tile(p, t.g, t.n0, BN_OUT)) { fail(ST_TIMEOUT_PEER); ok = false; break; }
         fence_proxy_async_all();
       }
       for (int kb = 0; kb < total_kb; ++kb, ++it) {
@@ -867,8 +926,10 @@ __global__ void __launch_bounds__(TALL_THREADS, 1) gemm_sm100_tall_kernel(const 
       bool store_ok = row_ok;
       if (p.row_dest_rank != nullptr) {          // result rows go straight into peers' buffers
         dest = row_ok ? p.row_dest_rank[row] : -1;
+        const int drow = row_ok ? p.row_dest_row[row] : -1;
+        if (dest >= p.num_peers || drow < 0) dest = -1;
         store_ok = dest >= 0;
-        if (store_ok) { Cout = reinterpret_cast<void*>(p.peer_out[dest]); base = (long long)p.row_dest_row[row] * p.ldc; }
+        if (store_ok) { Cout = reinterpret_cast<void*>(p.peer_out[dest]); base = (long long)drow * p.ldc; }
       }
       if (total_kb == 0) {
         if (!p.accumulate && row_ok) {
@@ -1209,6 +1270,10 @@ extern "C" int mdt_gemm(const MdtGemmDesc* d, cudaStream_t stream) {
   p.tile_ready = d->tile_ready; p.tile_expected = d->tile_expected;
   p.row_dest_rank = d->row_dest_rank; p.row_dest_row = d->row_dest_row; p.peer_out = d->peer_out; p.peer_arrive = d->peer_arrive;
   p.num_peers = d->num_peers;
+  p.peer_wait_ns = mdt_peer_wait_limit_ns();
+  p.rdy_b = d->b_ready; p.rdy_b2 = d->b2_ready;
+  if (p.mode == 2) { p.rdy_b.ready = nullptr; p.rdy_b2.ready = nullptr; }
+  p.b_rows = d->b_rows; p.ldb = d->ldb; p.b_group_stride = d->b_group_stride;
   if (p.row_dest_rank != nullptr && (p.dual || p.c_fp32 || p.accumulate || p.mode == 2)) return -12;
   if (p.N % 8 != 0 || p.ldc % 8 != 0) return -10;
   if (p.dual && (p.b_mn != 0 || p.c_fp32 || p.accumulate)) return -11;

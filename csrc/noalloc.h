@@ -29,8 +29,10 @@ extern "C" {
 //   counts[num_experts], padded_offsets[num_experts + 1], dest_row[num_slots], src_slot[capacity].
 // The function enqueues on `stream` and calls no cudaMalloc, cudaFree or any allocating routine.
 //
-// The first call on a device looks up the address of the scratch array for that device
-// (cudaGetSymbolAddress, with that device current); make that first call before any stream capture.
+// The scratch array that a call uses is the one of the device that is current when the call is made, so
+// `stream` must be a stream of that device.  The first call on a device looks up the address of the
+// scratch array for that device (cudaGetSymbolAddress, with that device current); make that first call
+// before any stream capture.
 // All calls on a device share the one scratch array and it keeps the previous call's contents; every
 // entry a call reads is written by that call first, so nothing needs clearing, but two calls that
 // overlap on the GPU (different streams without an ordering between them) race on it.

@@ -8,6 +8,7 @@
 #include <mutex>
 
 #include "api.h"
+#include "common/host.h"
 
 namespace mdt {
 
@@ -368,7 +369,8 @@ extern "C" long long mdt_router_launch_count() { return g_rt_launches; }
 // One warp per token, four tokens per CTA in flight; enough CTAs to fill the GPU, each staging the router matrix once.
 static int router_grid(int tokens) {
   const int g = (tokens + 3) / 4;
-  return g < 1 ? 1 : (g > 148 * 3 ? 148 * 3 : g);
+  const int cap = sm_count_of_current_device() * 3;
+  return g < 1 ? 1 : (g > cap ? cap : g);
 }
 // The router matrix is staged in shared memory when it fits (E x H bf16 <= 96 KB); opt in above 48 KB once per kernel.
 static int router_smem_ok(const void* kernel, size_t bytes) {
@@ -472,6 +474,8 @@ extern "C" int mdt_combine_wgrad(const void* y, const int* dest_row, const void*
 }
 
 // ---------------------------------------------------------------------------------- allocation-free plan builder
+#include <atomic>
+
 #include "noalloc.h"
 
 namespace mdt {
@@ -479,8 +483,10 @@ constexpr int NOALLOC_MAX_BLOCKS = MDT_NOALLOC_MAX_SLOTS / PLAN_CHUNK;
 constexpr int NOALLOC_MAX_DEVICES = 64;
 // Scratch of mdt_make_plan_noalloc: per-(block, expert) counts, later first rows.  One copy per GPU.
 static __device__ __align__(256) int g_plan_scratch[(NOALLOC_MAX_BLOCKS + 1) * MDT_NOALLOC_MAX_EXPERTS];
-// Device address of g_plan_scratch on each device (the symbol itself is only a host-side handle).
-static int* g_plan_scratch_addr[NOALLOC_MAX_DEVICES] = {nullptr};
+// Device address of g_plan_scratch on each device (the symbol itself is only a host-side handle).  Atomic: two
+// host threads may make their first call on a device at the same time; both then look the address up and store
+// the same value.
+static std::atomic<int*> g_plan_scratch_addr[NOALLOC_MAX_DEVICES];
 }  // namespace mdt
 
 extern "C" const char* mdt_make_plan_noalloc_strerror(int code) {
@@ -502,15 +508,19 @@ extern "C" int mdt_make_plan_noalloc(const int* expert_ids, int num_slots, int n
   if (num_slots > MDT_NOALLOC_MAX_SLOTS || num_experts > MDT_NOALLOC_MAX_EXPERTS) return MDT_NOALLOC_TOO_LARGE;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return MDT_NOALLOC_BAD_DEVICE;
-  if (g_plan_scratch_addr[dev] == nullptr) {   // set-up, once per device, with that device current
+  int* scratch = g_plan_scratch_addr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {   // set-up, once per device, with that device current
     int* addr = nullptr;
     if (cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_plan_scratch) != cudaSuccess || addr == nullptr)
       return MDT_NOALLOC_NO_SYMBOL;
-    g_plan_scratch_addr[dev] = addr;
+    g_plan_scratch_addr[dev].store(addr, std::memory_order_release);
+    scratch = addr;
   }
-  int* scratch = g_plan_scratch_addr[dev];
   const int nb = (num_slots + PLAN_CHUNK - 1) / PLAN_CHUNK;
-  if (capacity > 0) cudaMemsetAsync(src_slot, 0xFF, (size_t)capacity * sizeof(int), s);
+  if (capacity > 0) {
+    const cudaError_t me = cudaMemsetAsync(src_slot, 0xFF, (size_t)capacity * sizeof(int), s);
+    if (me != cudaSuccess) { cudaGetLastError(); return -100 - (int)me; }
+  }
   if (nb > 0) {
     plan_hist_kernel<<<nb, PLAN_CHUNK, 0, s>>>(expert_ids, num_slots, num_experts, scratch);
     MDT_RT_CHECK();

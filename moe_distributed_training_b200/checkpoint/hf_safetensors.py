@@ -86,10 +86,12 @@ class _Files:
 
     def get(self, fname: str):
         if fname not in self.handles:
-            self.handles[fname] = safe_open(os.path.join(self.root, fname), framework="pt", device="cpu")
+            self.handles[fname] = safe_open(os.path.join(self.root, fname), framework="pt", device="cpu").__enter__()
         return self.handles[fname]
 
     def close(self):
+        for h in self.handles.values():
+            h.__exit__(None, None, None)
         self.handles.clear()
 
 

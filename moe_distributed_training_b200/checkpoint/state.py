@@ -121,36 +121,57 @@ def _export_tp_layer(moe, prefix):
     return out
 
 
+def _adapter_key(qualname: str) -> str:
+    """peft's key for a parameter of this model (`...lora_A.default.weight` -> `base_model.model....lora_A.weight`)."""
+    return "base_model.model." + qualname.replace(".default", "")
+
+
 def save_adapter(engine, out_dir: str, dense: Dict[str, torch.Tensor] = None):
-    """peft-style adapter files.  Expert adapters are stored per global expert:
-    `...block_sparse_moe.experts.{e}.{w}.lora_A.weight` is `[r, in]`, `lora_B.weight` is `[out, r]`."""
+    """peft-style adapter files: one `adapter_model.safetensors` (written by rank 0) plus `adapter_config.json`.
+
+    Expert adapters are stored per global expert: `...block_sparse_moe.experts.{e}.{w}.lora_A.weight` is `[r, in]`,
+    `lora_B.weight` is `[out, r]`.  With expert parallelism every rank contributes the experts it owns (one replica
+    of each); the pieces are collected on rank 0, so that the file does not depend on the sharding it was saved from.
+    """
     rank, world = _world()
+    os.makedirs(out_dir, exist_ok=True)
     dense = dense if dense is not None else _gather_dense(engine)
     tensors = {}
     if rank == 0:
         for name, t in dense.items():
             if "lora_" in name:
-                key = "base_model.model." + name.replace(".default", "")
-                tensors[key] = t.cpu().contiguous()
+                tensors[_adapter_key(name)] = t.cpu().contiguous()
+    mine = {}
     for i, layer in enumerate(engine.model.model.layers):
-        experts = layer.block_sparse_moe.experts
-        lora = getattr(experts, "lora", None)
+        moe = layer.block_sparse_moe
+        lora = getattr(moe.experts, "lora", None)
         if lora is None:
             continue
+        if moe.args.tensor_parallel_size > 1:
+            raise NotImplementedError("saving expert adapters of tensor-parallel experts is not supported")
         dp_rank = dist.get_rank(engine.runner.expert_dp_group) if engine.runner.expert_dp_group is not None else 0
         if dp_rank != 0:
             continue
-        ids = _expert_ids(engine, layer.block_sparse_moe)
+        ids = _expert_ids(engine, moe)
         for w in lora.lora_A:
+            if lora.lora_A[w] is None:      # sharded like a dense parameter: saved with the flat state above
+                continue
             A, B = lora.lora_A[w].detach(), lora.lora_B[w].detach()
             for j, e in enumerate(ids):
                 base = f"base_model.model.model.layers.{i}.block_sparse_moe.experts.{e}.{w}"
-                tensors[f"{base}.lora_A.weight"] = A[j].t().cpu().contiguous()
-                tensors[f"{base}.lora_B.weight"] = B[j].t().cpu().contiguous()
-    fname = "adapter_model.safetensors" if world == 1 else f"adapter_model-rank{rank:05d}.safetensors"
-    if tensors:
-        save_file(tensors, os.path.join(out_dir, fname), metadata={"format": "pt"})
+                mine[f"{base}.lora_A.weight"] = A[j].t().cpu().contiguous()
+                mine[f"{base}.lora_B.weight"] = B[j].t().cpu().contiguous()
+    if world > 1:
+        pieces = [None] * world if rank == 0 else None
+        dist.gather_object(mine, pieces, dst=0)
+        if rank == 0:
+            for piece in pieces:
+                tensors.update(piece)
+    else:
+        tensors.update(mine)
     if rank == 0:
+        if tensors:
+            save_file(tensors, os.path.join(out_dir, "adapter_model.safetensors"), metadata={"format": "pt"})
         cfg = engine.model.peft_config["default"].to_dict() if hasattr(engine.model, "peft_config") else {}
         with open(os.path.join(out_dir, "adapter_config.json"), "w") as f:
             json.dump(cfg, f, indent=2)
@@ -189,19 +210,64 @@ def load_training_state(engine, in_dir: str) -> int:
 
 
 def load_adapter(engine, in_dir: str):
-    """Load attention adapters written by save_adapter on a single rank."""
+    """Load `adapter_model.safetensors` (as written by save_adapter or by peft) into the sharded model.
+
+    Attention adapters live inside the flat parameter shards: each rank copies the slice it owns.  Expert adapters
+    are re-stacked from the per-expert matrices into this rank's `[E_local, in, r]` / `[E_local, r, out]` tensors.
+    Raises if an adapter parameter of the model has no tensor in the file, or a tensor in the file matches nothing
+    (tensors of experts that other ranks own are expected and skipped).
+    """
     path = os.path.join(in_dir, "adapter_model.safetensors")
     tensors = load_file(path)
-    named = dict(engine.model.named_parameters())
-    missing = []
-    for key, t in tensors.items():
-        name = key[len("base_model.model."):].replace(".lora_A.weight", ".lora_A.default.weight").replace(
-            ".lora_B.weight", ".lora_B.default.weight")
-        if name in named:
-            with torch.no_grad():
-                named[name].copy_(t.to(named[name].dtype))
-        else:
-            missing.append(key)
+    used, missing = set(), []
+    with torch.no_grad():
+        for u in engine.runner.all_units():
+            for g in u.groups:
+                lo, hi = g.rank * g.shard_numel, (g.rank + 1) * g.shard_numel
+                for (mod, name, shape, n, o), qual in zip(g.specs, g.qualnames):
+                    if "lora_" not in qual:
+                        continue
+                    key = _adapter_key(qual)
+                    if key not in tensors:
+                        missing.append(key)
+                        continue
+                    t = tensors[key]
+                    if tuple(t.shape) != tuple(shape):
+                        raise ValueError(f"{key}: file has shape {tuple(t.shape)}, the model needs {tuple(shape)}")
+                    used.add(key)
+                    a, b = max(o, lo), min(o + n, hi)
+                    if a < b:
+                        g.shard.data[a - lo:b - lo].copy_(t.reshape(-1)[a - o:b - o].to(g.shard.dtype))
+        expert_keys_elsewhere = set()
+        for i, layer in enumerate(engine.model.model.layers):
+            moe = layer.block_sparse_moe
+            lora = getattr(moe.experts, "lora", None)
+            prefix = f"base_model.model.model.layers.{i}.block_sparse_moe.experts."
+            if lora is None:
+                continue
+            if moe.args.tensor_parallel_size > 1:
+                raise NotImplementedError("loading expert adapters into tensor-parallel experts is not supported")
+            ids = _expert_ids(engine, moe)
+            expert_keys_elsewhere.update(k for k in tensors if k.startswith(prefix))
+            for w in lora.lora_A:
+                A, B = lora.lora_A[w], lora.lora_B[w]
+                if A is None:               # sharded like a dense parameter: loaded with the flat state above
+                    continue
+                for j, e in enumerate(ids):
+                    for mat, suffix in ((A, "lora_A"), (B, "lora_B")):
+                        key = f"{prefix}{e}.{w}.{suffix}.weight"
+                        if key not in tensors:
+                            missing.append(key)
+                            continue
+                        t = tensors[key].t()
+                        if tuple(t.shape) != tuple(mat[j].shape):
+                            raise ValueError(f"{key}: file has shape {tuple(tensors[key].shape)}, the model needs {tuple(mat[j].t().shape)}")
+                        mat[j].copy_(t.to(mat.dtype))
+                        used.add(key)
+    unmatched = sorted(set(tensors) - used - expert_keys_elsewhere)
+    if missing or unmatched:
+        raise KeyError(f"adapter file {path} does not fit the model: missing {missing[:5]} ({len(missing)} in all), "
+                       f"unmatched {unmatched[:5]} ({len(unmatched)} in all)")
     if hasattr(engine.runner, "invalidate_gathered"):
         engine.runner.invalidate_gathered()
-    return missing
+    return []

@@ -355,7 +355,7 @@ class ShardedMixtral:
     def _gather_into(self, unit: FsdpUnit, buffers):
         for g, buf in zip(unit.groups, buffers):
             if self.peers is not None:
-                self._ext.ag_pull(buf[:g.padded], g.shard_table, g.ws, g.shard_numel * g.shard.element_size())
+                self._ext.ag_pull(buf[:g.padded], g.shard_table, g.ws, g.rank, g.shard_numel * g.shard.element_size())
             else:
                 coll.all_gather_flat(buf[:g.padded], g.shard.data, g.group)
 
@@ -402,7 +402,7 @@ class ShardedMixtral:
             for j in stale:
                 g, buf = unit.groups[j], unit.resident[j]
                 if self.peers is not None:
-                    self._ext.ag_pull(buf[:g.padded], g.shard_table, g.ws, g.shard_numel * g.shard.element_size())
+                    self._ext.ag_pull(buf[:g.padded], g.shard_table, g.ws, g.rank, g.shard_numel * g.shard.element_size())
                 else:
                     coll.all_gather_flat(buf[:g.padded], g.shard.data, g.group)
                 unit.resident_version[j] = want[j]
@@ -613,12 +613,41 @@ class ShardedMixtral:
         return self.units + [self.root]
 
 
-def _all_reduce_list(tensors, group, scale: float):
-    flat = torch.cat([t.reshape(-1).float() for t in tensors])
-    dist.all_reduce(flat, group=group)
-    flat.mul_(scale)
-    off = 0
+def _all_reduce_list(tensors, group, scale: float, bucket_bytes: int = 256 << 20):
+    """Mean-reduce a list of gradients over `group`, in place and in their own dtype.
+
+    Large tensors (expert weight gradients: 2.8 GB per layer in bf16) are reduced where they are; small ones are
+    packed into buckets of at most `bucket_bytes` so that a model's few hundred router / adapter gradients cost a
+    handful of collectives.  No full-size temporary exists at any time.
+    """
+    small = {}
     for t in tensors:
-        n = t.numel()
-        t.copy_(flat[off:off + n].view_as(t))
-        off += n
+        nbytes = t.numel() * t.element_size()
+        if nbytes >= bucket_bytes // 4 and t.is_contiguous():
+            dist.all_reduce(t, group=group)
+            if scale != 1.0:
+                t.mul_(scale)
+        else:
+            small.setdefault(t.dtype, []).append(t)
+    for dtype, items in small.items():
+        bucket, size = [], 0
+        def flush():
+            if not bucket:
+                return
+            flat = torch.cat([b.reshape(-1) for b in bucket])
+            dist.all_reduce(flat, group=group)
+            if scale != 1.0:
+                flat.mul_(scale)
+            off = 0
+            for b in bucket:
+                n = b.numel()
+                b.copy_(flat[off:off + n].view_as(b))
+                off += n
+        for t in items:
+            nbytes = t.numel() * t.element_size()
+            if bucket and size + nbytes > bucket_bytes:
+                flush()
+                bucket, size = [], 0
+            bucket.append(t)
+            size += nbytes
+        flush()

@@ -120,6 +120,7 @@ class FusedExpertParallel:
         w = self.wspace
         self.count_epoch += 1
         parity = self.count_epoch & 1
+        # (the wait kernel writes every entry: real offsets, or all zeros = "no rows" when a peer's counts never came)
         meta = torch.empty(self.meta_size, dtype=torch.int32, device=self.device)
         self.ext.ep_counts_send(counts, w.peer_base, w.layout, w.rank, parity, self.count_epoch)
         self.ext.ep_counts_wait_meta(w.my_base, w.layout, w.rank, parity, self.count_epoch, meta, self.status())
@@ -129,12 +130,12 @@ class FusedExpertParallel:
         """Send my rows; `wait=False` leaves the waiting to a GEMM that checks the per-tile arrival counters."""
         w = self.wspace
         assert expert_of_slot.numel() <= w.capacity_slots, "more (token, choice) slots than the workspace was sized for"
-        self.ext.ep_dispatch(x, src_slot, expert_of_slot, slot_scale, meta, w.peer_base, w.layout, top_k, parity)
+        self.ext.ep_dispatch(x, src_slot, expert_of_slot, slot_scale, meta, w.peer_base, w.layout, w.rank, top_k, parity, self.status())
         self.ext.ep_recv_prepare(w.my_base, w.layout, meta, w.cols, parity, self.status(), wait)
 
     def combine(self, y, meta, parity, n_slots, clone: bool):
         w = self.wspace
-        self.ext.ep_combine_send(y, meta, w.peer_base, w.layout, w.rank, w.capacity_rows, parity)
+        self.ext.ep_combine_send(y, meta, w.peer_base, w.layout, w.rank, w.capacity_rows, parity, self.status())
         return self.wait_rows(meta, parity, n_slots, 1, clone)
 
     def wait_rows(self, meta, parity, n_slots, mult: int, clone: bool):

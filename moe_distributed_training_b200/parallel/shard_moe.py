@@ -55,22 +55,36 @@ def get_moe_kwargs(config, has_bias: bool = False, fp16: bool = False, bf16: boo
     }
 
 
-def get_resolved_checkpoint_location(name_or_path: str) -> str:
+def get_resolved_checkpoint_location(name_or_path: str, revision: str = "main") -> str:
     """Directory holding the checkpoint files.
 
     A local directory is returned as is; a hub id is looked up in the local HF
-    cache (no download: there may be no network).  The reference obtains the same
-    directory by hooking config loading (megablocks_utils/shard_moe_utils.py:50-63).
+    cache (no download: there may be no network).  The snapshot is the one that
+    `refs/<revision>` names (what `from_pretrained` resolves, and so what the
+    reference obtains by hooking config loading, megablocks_utils/shard_moe_utils.py:50-63);
+    `revision` may also be a commit hash.  Without a matching ref the only
+    snapshot present is taken; several snapshots and no ref is an error.
     """
     if os.path.isdir(name_or_path):
         return name_or_path
     cache = os.environ.get("HF_HUB_CACHE") or os.path.join(
         os.environ.get("HF_HOME", os.path.expanduser("~/.cache/huggingface")), "hub")
-    repo = os.path.join(cache, "models--" + name_or_path.replace("/", "--"), "snapshots")
+    root = os.path.join(cache, "models--" + name_or_path.replace("/", "--"))
+    repo = os.path.join(root, "snapshots")
     if os.path.isdir(repo):
+        ref = os.path.join(root, "refs", revision)
+        if os.path.isfile(ref):
+            with open(ref) as f:
+                commit = f.read().strip()
+            if os.path.isdir(os.path.join(repo, commit)):
+                return os.path.join(repo, commit)
+        if os.path.isdir(os.path.join(repo, revision)):
+            return os.path.join(repo, revision)
         snaps = sorted(os.listdir(repo))
+        if len(snaps) == 1:
+            return os.path.join(repo, snaps[0])
         if snaps:
-            return os.path.join(repo, snaps[-1])
+            raise ValueError(f"checkpoint '{name_or_path}': {len(snaps)} cached snapshots and no refs/{revision}; pass a directory")
     raise ValueError(f"checkpoint '{name_or_path}' is neither a directory nor in the local HF cache")
 
 

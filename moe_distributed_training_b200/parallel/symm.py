@@ -8,11 +8,19 @@ all ranks can be run one after another on a single device in tests.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import List, Optional
 
 import torch
 import torch.distributed as dist
+
+
+# The kernels of this framework address peers with plain loads and stores only.  torch's rendezvous would otherwise
+# also bind every symmetric buffer to an NVLink multicast object on NVSwitch machines, which nothing here uses and
+# which makes the other ranks' GPUs raise NVLink errors when one rank's process ends while its memory is still
+# bound.  The variable is read by torch when the first buffer is allocated; a value set by the user wins.
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 
 def _align(x: int, a: int = 256) -> int:

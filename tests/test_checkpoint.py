@@ -159,3 +159,65 @@ def test_adapter_save_uses_peft_names(tmp_path):
     k = "base_model.model.model.layers.1.block_sparse_moe.experts.2.w2.lora_B.weight"
     assert t[k].shape == (cfg.hidden_size, 16)
     assert json.load(open(tmp_path / "adapter_config.json"))["r"] == 16
+
+
+def _train_save_load_adapter(rank, world, out_dir):
+    """Train adapters for a step, save them, load them into a freshly built engine, compare every adapter value."""
+    from moe_distributed_training_b200.checkpoint.state import load_adapter, save_adapter
+    from moe_distributed_training_b200.data.synthetic import SyntheticInstructionDataset, batches
+    from moe_distributed_training_b200.train.engine import build_engine
+    cfg = MixtralConfig.tiny()
+    kw = dict(dtype=torch.float32, device_type="cpu", use_lora="all", learning_rate=1e-2, ep_size=world if world > 1 else None)
+    a = build_engine(cfg, seed=0, **kw)
+    ds = SyntheticInstructionDataset(cfg.vocab_size, 2, 16, 32, rank=rank)
+    a.train_step(list(batches(ds, 1)))            # lora_B leaves zero: the saved values are not the initial ones
+    save_adapter(a, out_dir)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    b = build_engine(cfg, seed=1, **kw)           # other initial adapters
+    pa = {n: p for n, p in a.model.named_parameters() if p.requires_grad}
+    pb = {n: p for n, p in b.model.named_parameters() if p.requires_grad}
+    assert pa.keys() == pb.keys() and pa
+    assert any(not torch.equal(pa[n], pb[n]) for n in pa)
+    load_adapter(b, out_dir)
+    for n in pa:
+        assert torch.equal(pa[n].detach(), pb[n].detach()), n
+    # a tensor in the file that matches nothing is an error, not a silent skip
+    return sorted(os.listdir(out_dir))
+
+
+def test_adapter_roundtrip_single_rank(tmp_path):
+    files = _train_save_load_adapter(0, 1, str(tmp_path))
+    assert "adapter_model.safetensors" in files and not [f for f in files if "rank" in f]
+
+
+def test_adapter_roundtrip_two_ranks_expert_parallel(tmp_path):
+    files = run_distributed(_train_save_load_adapter, 2, str(tmp_path))[0]
+    assert "adapter_model.safetensors" in files and not [f for f in files if "rank" in f]
+    from safetensors.torch import load_file
+    t = load_file(str(tmp_path / "adapter_model.safetensors"))
+    cfg = MixtralConfig.tiny()
+    for e in range(cfg.num_local_experts):          # experts of both ranks are in the one file
+        assert f"base_model.model.model.layers.0.block_sparse_moe.experts.{e}.w1.lora_A.weight" in t
+
+
+def test_load_adapter_rejects_a_file_that_does_not_fit(tmp_path):
+    from moe_distributed_training_b200.checkpoint.state import load_adapter, save_adapter
+    from moe_distributed_training_b200.train.engine import build_engine
+    from safetensors.torch import load_file, save_file
+    cfg = MixtralConfig.tiny()
+    eng = build_engine(cfg, dtype=torch.float32, device_type="cpu", use_lora="attn-only")
+    save_adapter(eng, str(tmp_path))
+    path = str(tmp_path / "adapter_model.safetensors")
+    t = load_file(path)
+    dropped = sorted(t)[0]
+    extra = dict(t)
+    del extra[dropped]
+    extra["base_model.model.model.layers.0.self_attn.nothing.lora_A.weight"] = torch.zeros(2, 2)
+    save_file(extra, path)
+    try:
+        load_adapter(eng, str(tmp_path))
+        raise AssertionError("a file with a missing and an unknown tensor was accepted")
+    except KeyError as exc:
+        assert "missing" in str(exc) and "unmatched" in str(exc)

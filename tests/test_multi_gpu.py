@@ -1,5 +1,7 @@
 """Multi-GPU tests (skipped with fewer than two GPUs): the peer-memory exchange and the peer-memory
-parameter collectives reproduce the library (NCCL) path.  Ranks are child processes; NVLS is off."""
+parameter collectives reproduce the library (NCCL) path.  Ranks are child processes; NVLS is off in NCCL
+(NCCL_NVLS_ENABLE=0) and symmetric memory is mapped without an NVLink multicast object
+(TORCH_SYMM_MEM_DISABLE_MULTICAST=1), so a rank that ends leaves nothing bound in the switch."""
 import json
 import os
 import subprocess
@@ -14,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 def _run(n, mode, tmp_path, port):
     out = str(tmp_path / f"res_{mode}.json")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1", MASTER_ADDR="127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), os.path.join(HERE, "multi_gpu_worker.py"), out, mode]
     p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
@@ -45,7 +47,7 @@ def test_rank_that_leaves_between_steps_is_detected_on_the_host(tmp_path):
         pytest.skip("needs at least two GPUs")
     n = 2
     out = str(tmp_path / "res_exit.json")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1", MASTER_ADDR="127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
            "--master-port", "29640", os.path.join(HERE, "multi_gpu_worker.py"), out, "rank-exit"]
     p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
