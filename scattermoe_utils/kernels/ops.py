@@ -21,15 +21,17 @@ def padded_block_indices(sorted_experts_idxs: torch.Tensor, k: int, N_BLOCK_SIZE
     """(start row of every work block, inclusive cumsum of per-expert counts) — scattermoe's helper.
 
     Expert groups are not padded in memory: counts (300, 200) give blocks starting at
-    [0, 128, 256, 300, 428].
+    [0, 128, 256, 300, 428].  Computed with tensor operations on the input's device (the number of blocks
+    depends on the data, so sizing the result costs one read of a scalar).
     """
     counts = torch.bincount(sorted_experts_idxs.long(), minlength=k)
     expert_offsets = counts.cumsum(-1)
     starts = expert_offsets - counts
-    blocks = []
-    for s, c in zip(starts.tolist(), counts.tolist()):
-        blocks += list(range(s, s + c, N_BLOCK_SIZE))
-    return torch.tensor(blocks, dtype=torch.long, device=sorted_experts_idxs.device), expert_offsets
+    blocks_per = (counts + (N_BLOCK_SIZE - 1)) // N_BLOCK_SIZE
+    first_block = blocks_per.cumsum(-1) - blocks_per
+    expert_of_block = torch.repeat_interleave(torch.arange(k, device=counts.device), blocks_per)
+    j = torch.arange(expert_of_block.numel(), device=counts.device) - first_block[expert_of_block]
+    return starts[expert_of_block] + j * N_BLOCK_SIZE, expert_offsets
 
 
 def _plan_from_sorted(sorted_expert_idxs: torch.Tensor, E: int):
@@ -62,15 +64,35 @@ def scatter2scatter_lora(X, W, A, B, lora_alp, sorted_expert_idxs, sorted_scatte
 
 
 def group_bwd_AB(DY, X, A, B, scaling, expert_offsets, E):
-    """LoRA factor gradients on expert-grouped X [M,K], DY [M,N]; returns (dA [E,K,r], dB [E,r,N])."""
+    """LoRA factor gradients on expert-grouped X [M,K], DY [M,N]; returns (dA [E,K,r], dB [E,r,N]).
+
+    On CUDA: four launches of the grouped GEMM family, nothing else (no base-weight product):
+    `s DY B^T` and `s X A` as row-grouped products, then the two depth-grouped reductions
+    `dA_e = X_e^T (s DY_e B_e^T)` and `dB_e = (s X_e A_e)^T DY_e`, each over all rows of the expert.
+    """
     counts = torch.diff(expert_offsets, prepend=expert_offsets.new_zeros(1))
     sorted_ids = torch.repeat_interleave(torch.arange(E, device=X.device), counts.long(), output_size=X.shape[0])
     plan = _plan_from_sorted(sorted_ids, E)
-    Al, Bl = A.detach().requires_grad_(True), B.detach().requires_grad_(True)
     xg = ops.gather_rows(X.detach(), plan)
-    W0 = torch.zeros(E, X.shape[1], DY.shape[1], dtype=X.dtype, device=X.device)
-    with torch.enable_grad():
-        yg = ops.grouped_linear(xg, W0, plan, trans_b=False, lora=(Al, Bl, float(scaling)))
-    dyg = ops.gather_rows(DY, plan)
-    dA, dB = torch.autograd.grad(yg, [Al, Bl], dyg)
+    dyg = ops.gather_rows(DY.detach(), plan)
+    if X.is_cuda and ops.get_backend() == "native":
+        from moe_distributed_training_b200.ops import cuda_ops as C
+        Ad, Bd = A.detach().contiguous(), B.detach().contiguous()
+        r, K, N, R = Ad.shape[2], X.shape[1], DY.shape[1], xg.shape[0]
+        dt = torch.empty(R, r, dtype=X.dtype, device=X.device)
+        C._g(1, dyg, False, Bd, False, dt, r, N, plan, alpha=float(scaling))
+        t = torch.empty(R, r, dtype=X.dtype, device=X.device)
+        C._g(1, xg, False, Ad, True, t, r, K, plan, alpha=float(scaling))
+        dA, dB = torch.empty_like(Ad), torch.empty_like(Bd)
+        C._g(2, xg, True, dt, True, dA, r, 0, plan)
+        C._g(2, t, True, dyg, True, dB, N, 0, plan)
+        return dA, dB
+    # CPU / library path: the same two reductions, stated per expert
+    dA, dB = torch.zeros_like(A), torch.zeros_like(B)
+    offs = plan.padded_offsets.tolist()
+    cnt = plan.tokens_per_expert.tolist()
+    for e in range(E):
+        xe, dye = xg[offs[e]:offs[e] + cnt[e]].float(), dyg[offs[e]:offs[e] + cnt[e]].float()
+        dA[e] = (float(scaling) * xe.t() @ (dye @ B[e].float().t())).to(A.dtype)
+        dB[e] = (float(scaling) * (xe @ A[e].float()).t() @ dye).to(B.dtype)
     return dA, dB

@@ -13,8 +13,22 @@ def _rel_err(a, b):
 
 
 def _close(a, b, tol=2e-2, name=""):
+    """Norm-wise relative error of the whole tensor, and of every row and every column on its own, so that a
+    single wrong row, or one wrong column block, fails although it barely moves the overall norm.  Rows and columns
+    are measured against their own norm, floored at a tenth of the typical one (near-zero rows of a reference
+    carry no relative information)."""
     err = _rel_err(a, b)
     assert err < tol, f"{name}: relative error {err:.4g} (tolerance {tol})"
+    a2, b2 = a.float(), b.float()
+    if a2.dim() < 2 or a2.numel() == 0:
+        return
+    a2, b2 = a2.reshape(-1, a2.shape[-1]), b2.reshape(-1, b2.shape[-1])
+    for dim, what in ((1, "row"), (0, "column")):
+        ref_norm = b2.norm(dim=dim)
+        floor = 0.1 * ref_norm.mean().clamp(min=1e-12)
+        rel = (a2 - b2).norm(dim=dim) / ref_norm.clamp(min=floor)
+        worst = int(rel.argmax())
+        assert float(rel[worst]) < 4 * tol, f"{name}: {what} {worst} relative error {float(rel[worst]):.4g} (tolerance {4 * tol})"
 
 
 @pytest.fixture(scope="module")
@@ -509,3 +523,32 @@ def test_fused_moe_block_matches_composed_ops(ops, lora):
         if a is not None:
             _close(a, b, 3e-2, f"fused moe block grad {i}")
     ops.check_status(DEV)
+
+
+def test_group_bwd_ab_direct_products_match_fp32():
+    """The reference-named LoRA gradient entry point: four grouped-GEMM launches, full reductions over K and N."""
+    from scattermoe_utils.kernels.ops import group_bwd_AB, padded_block_indices
+    torch.manual_seed(21)
+    E, K, N, r, s = 3, 384, 640, 16, 2.0
+    counts = [300, 0, 212]
+    M = sum(counts)
+    X = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    DY = torch.randn(M, N, device=DEV).to(torch.bfloat16)
+    A = (torch.randn(E, K, r, device=DEV) * 0.1).to(torch.bfloat16)
+    B = (torch.randn(E, r, N, device=DEV) * 0.1).to(torch.bfloat16)
+    offs = torch.tensor(counts, device=DEV).cumsum(0)
+    dA, dB = group_bwd_AB(DY, X, A, B, s, offs, E)
+    lo = 0
+    for e, c in enumerate(counts):
+        xe, dye = X[lo:lo + c].float(), DY[lo:lo + c].float()
+        wantA = s * xe.t() @ (dye @ B[e].float().t()).to(torch.bfloat16).float()
+        wantB = s * (xe @ A[e].float()).to(torch.bfloat16).float().t() @ dye
+        if c == 0:
+            assert float(dA[e].float().abs().max()) == 0 and float(dB[e].float().abs().max()) == 0
+        else:
+            _close(dA[e], wantA, 3e-2, f"dA[{e}]")
+            _close(dB[e], wantB, 3e-2, f"dB[{e}]")
+        lo += c
+    ids = torch.repeat_interleave(torch.arange(E, device=DEV), torch.tensor(counts, device=DEV))
+    pbi, eo = padded_block_indices(ids, E)
+    assert pbi.tolist() == [0, 128, 256, 300, 428] and eo.tolist() == [300, 300, 512]
