@@ -21,10 +21,10 @@ results go into the line's `configs` object:
 
   series workload on the library arm (torch kernels, NCCL all-to-all with host-read split sizes):
       `vs_baseline` = value / that number, measured in the same run on the same box
-  at 2+ GPUs: one optimizer step with the fused exchange and one with the NCCL exchange from the same
-      initial state on the same batch: both losses and a parameter checksum (`fused_vs_nccl`)
+  at 2+ GPUs: two optimizer steps with the fused exchange and two with the NCCL exchange from the same
+      initial state on the same batch: losses and a parameter checksum of both (`fused_vs_nccl`)
   at 8 GPUs: full fine-tune ep8, LoRA-attn ep4 x dp2, LoRA-all ep4 x dp2, and no expert parallelism
-      (everything sharded over 8 GPUs; LoRA-attn and full), each on both arms
+      (everything sharded over 8 GPUs; LoRA-attn and full), each on both arms (native, then library)
 
 `--mode`, `--ep`, `--impl library` select one of those configurations directly (that is what the child
 jobs do); `--configs none` skips the child jobs.
@@ -64,10 +64,10 @@ def parse():
                          "the result is labelled gradient_checkpointing=false)")
     ap.add_argument("--configs", default="auto", choices=["auto", "none"],
                     help="auto: after the series measurement run the other named configurations as child jobs")
-    ap.add_argument("--extras-budget-s", type=float, default=1000.0, help="time limit for all child jobs together")
+    ap.add_argument("--extras-budget-s", type=float, default=620.0, help="time limit for all child jobs together")
     ap.add_argument("--extra-steps", type=int, default=2)
     ap.add_argument("--extra-warmup", type=int, default=3)
-    ap.add_argument("--sub", default="", help="internal: this process is a child job (run | check)")
+    ap.add_argument("--sub", default="", help="internal: this process is a child job (run | pair | check)")
     ap.add_argument("--sub-out", default="")
     return ap.parse_args()
 
@@ -151,6 +151,19 @@ def parallelism_name(world, ep):
     return f"ep{ep}" + (f"xdp{dp}" if dp > 1 else "")
 
 
+def release_engine():
+    """Drop what a finished engine left behind in this process (cached exchange workspaces, allocator blocks)."""
+    import gc
+    import torch
+    try:
+        from moe_distributed_training_b200.parallel.fused_ep import FusedExpertParallel
+        FusedExpertParallel._instances.clear()
+    except Exception:  # noqa: BLE001
+        pass
+    gc.collect()
+    torch.cuda.empty_cache()
+
+
 def run_measurement(args):
     """Builds the engine for (mode, ep, impl), measures `value` and `e2e`; returns (result dict on rank 0 or None)."""
     import torch
@@ -169,18 +182,22 @@ def run_measurement(args):
     ep = args.ep or world
     if world == 1:
         ep = 1
+    from moe_distributed_training_b200 import ops
+    dispatch = args.dispatch
     if args.impl == "library":
-        from moe_distributed_training_b200 import ops
         ops.set_backend("library")
         os.environ["MDT_PEER_COLLECTIVES"] = "0"        # NCCL all-gather / reduce-scatter
-        if args.dispatch == "auto":
-            args.dispatch = "nccl"
+        if dispatch == "auto":
+            dispatch = "nccl"
+    else:
+        ops.set_backend("native")
+        os.environ.pop("MDT_PEER_COLLECTIVES", None)
     use_lora = {"lora-attn": "attn-only", "lora-all": "all", "full": "none"}[args.mode]
     total_steps = args.steps * 2 + args.warmup + 4
     eng = build_engine(cfg, dtype=torch.bfloat16, device_type="cuda", ep_size=ep,
                        use_lora=use_lora, lora_r=16, lora_alpha=32 if use_lora != "none" else 16, learning_rate=5e-5,
                        lr_scheduler_type="linear", num_training_steps=total_steps, max_grad_norm=1.0, seed=0,
-                       dispatch_impl=args.dispatch, ep_max_tokens=args.max_len,
+                       dispatch_impl=dispatch, ep_max_tokens=args.max_len,
                        activation_checkpointing=not args.no_recompute)
     dev = eng.device
     ga = args.grad_accum
@@ -261,12 +278,33 @@ def run_measurement(args):
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
         }
     del eng
+    release_engine()
     return line
+
+
+def run_pair(args):
+    """One configuration on both arms in one job: native first, then library.  The result file is rewritten after
+    each arm, so that the first arm's numbers survive if the second one fails or runs out of time."""
+    rank = int(os.environ.get("RANK", 0))
+    out = {}
+    for impl in ("native", "library"):
+        args.impl = impl
+        try:
+            out[impl] = brief(run_measurement(args)) if rank == 0 else run_measurement(args)
+        except Exception as exc:  # noqa: BLE001
+            out[impl] = {"error": repr(exc)[:400]}
+            if rank == 0:
+                with open(args.sub_out, "w") as f:
+                    json.dump(out, f)
+            raise
+        if rank == 0:
+            with open(args.sub_out, "w") as f:
+                json.dump(out, f)
+    return out if rank == 0 else None
 
 
 def run_check(args):
     """One optimizer step with the fused exchange and one with the NCCL exchange, same initial state, same batch."""
-    import gc
     import torch
     import torch.distributed as dist
     from moe_distributed_training_b200 import MixtralConfig
@@ -295,8 +333,7 @@ def run_check(args):
             losses = (lt / world).tolist()
         out[impl] = {"losses_mean_over_ranks": [round(x, 6) for x in losses], "trainable_abs_sum": float(chk.item())}
         del eng
-        gc.collect()
-        torch.cuda.empty_cache()
+        release_engine()
     a, b = out["fused"], out["nccl"]
     out["max_rel_loss_diff"] = max(abs(x - y) / max(abs(y), 1e-9) for x, y in zip(a["losses_mean_over_ranks"], b["losses_mean_over_ranks"]))
     out["rel_checksum_diff"] = abs(a["trainable_abs_sum"] - b["trainable_abs_sum"]) / max(abs(b["trainable_abs_sum"]), 1e-9)
@@ -331,17 +368,30 @@ def run_child(n, extra_args, timeout_s, port):
         except subprocess.TimeoutExpired:
             os.killpg(proc.pid, signal.SIGKILL)       # the session this function started, nothing else
             proc.communicate()
-            return {"error": f"child job exceeded its {int(timeout_s)} s limit", "wall_s": round(time.time() - t0, 1)}
+            res = _read_partial(out_path)
+            res["error"] = f"child job exceeded its {int(timeout_s)} s limit"
+            res["wall_s"] = round(time.time() - t0, 1)
+            return res
         if proc.returncode != 0 or not os.path.exists(out_path):
-            tail = [ln for ln in (log or "").strip().splitlines() if ln.strip()][-6:]
-            return {"error": f"child job exited with {proc.returncode}", "log_tail": tail, "wall_s": round(time.time() - t0, 1)}
-        with open(out_path) as f:
-            res = json.load(f)
-        os.remove(out_path)
+            tail = [ln[-300:] for ln in (log or "").strip().splitlines() if ln.strip()][-6:]
+            res = _read_partial(out_path)
+            res.update({"error": f"child job exited with {proc.returncode}", "log_tail": tail, "wall_s": round(time.time() - t0, 1)})
+            return res
+        res = _read_partial(out_path)
         res["wall_s"] = round(time.time() - t0, 1)
         return res
     except Exception as exc:  # noqa: BLE001
         return {"error": repr(exc), "wall_s": round(time.time() - t0, 1)}
+
+
+def _read_partial(path):
+    try:
+        with open(path) as f:
+            res = json.load(f)
+        os.remove(path)
+        return res if isinstance(res, dict) else {}
+    except Exception:  # noqa: BLE001
+        return {}
 
 
 def brief(res):
@@ -349,7 +399,7 @@ def brief(res):
     if res is None or "error" in res:
         return res
     keep = {"tokens_per_s": res["value"], "ms_per_step": res["ms_per_step"], "steps": res["steps"], "warmup": res["warmup"],
-            "peak_mem_gib": res["config"]["peak_mem_gib"], "parallelism": res["config"]["parallelism"], "wall_s": res.get("wall_s")}
+            "peak_mem_gib": res["config"]["peak_mem_gib"], "parallelism": res["config"]["parallelism"]}
     if res.get("e2e"):
         keep["e2e_tokens_per_s"] = res["e2e"]["value"]
         keep["last_loss"] = res["e2e"]["last_loss"]
@@ -360,65 +410,68 @@ def run_extras(args, world, line):
     """Child jobs after the series measurement (rank 0 only, the process group is closed, the other ranks are gone)."""
     deadline = time.time() + args.extras_budget_s
     port0 = int(os.environ.get("MASTER_PORT", "29500")) + 101
-    common = ["--steps", str(args.extra_steps), "--warmup", str(args.extra_warmup), "--configs", "none", "--sub", "run",
+    common = ["--steps", str(args.extra_steps), "--warmup", str(args.extra_warmup), "--configs", "none", "--no-e2e",
               "--min-len", str(args.min_len), "--max-len", str(args.max_len), "--grad-accum", str(args.grad_accum)]
     if args.layers:
         common += ["--layers", str(args.layers)]
-    jobs = [("series_library", ["--mode", "lora-attn", "--impl", "library"])]
+    # in order of importance: what does not fit the time limit is reported as skipped
+    jobs = [("series_library", ["--sub", "run", "--mode", "lora-attn", "--impl", "library"])]
+    # the named configurations belong to 8 GPUs; MDT_BENCH_ALL_CONFIGS=1 runs their counterparts on fewer (to try the
+    # machinery on a small box; the names then carry the actual sizes)
+    all_configs = world == 8 or (world >= 2 and os.environ.get("MDT_BENCH_ALL_CONFIGS") == "1")
+    half = world // 2
+    if all_configs:
+        jobs.append((f"full_ep{world}", ["--sub", "pair", "--mode", "full", "--ep", str(world)]))
+        if half >= 2:
+            jobs += [(f"lora_attn_ep{half}xdp2", ["--sub", "pair", "--mode", "lora-attn", "--ep", str(half)]),
+                     (f"lora_all_ep{half}xdp2", ["--sub", "pair", "--mode", "lora-all", "--ep", str(half)])]
+        jobs.append(("lora_attn_no_ep", ["--sub", "pair", "--mode", "lora-attn", "--ep", "1"]))
     if world >= 2:
         jobs.append(("fused_vs_nccl", None))
-    if world == 8:
-        for name, mode, ep in (("full_ep8", "full", 8), ("lora_attn_ep4xdp2", "lora-attn", 4), ("lora_all_ep4xdp2", "lora-all", 4),
-                               ("lora_attn_no_ep", "lora-attn", 1), ("full_no_ep", "full", 1)):
-            for impl in ("native", "library"):
-                jobs.append((f"{name}.{impl}", ["--mode", mode, "--ep", str(ep), "--impl", impl]))
-    configs, i = {}, 0
-    for name, extra in jobs:
+    if all_configs:
+        jobs.append(("full_no_ep", ["--sub", "pair", "--mode", "full", "--ep", "1"]))
+    configs = {}
+    for i, (name, extra) in enumerate(jobs):
         left = deadline - time.time()
-        i += 1
-        if left < 60:
+        if left < 45:
             configs[name] = {"skipped": "time limit for the additional configurations reached"}
             continue
-        limit = min(left, 420.0)
+        limit = min(left, 330.0)
         if extra is None:
             sub = ["--sub", "check", "--configs", "none", "--min-len", str(args.min_len), "--max-len", str(args.max_len)]
             if args.layers:
                 sub += ["--layers", str(args.layers)]
             configs[name] = run_child(world, sub, limit, port0 + i)
+        elif "pair" in extra:
+            configs[name] = run_child(world, common + extra, limit, port0 + i)
         else:
-            configs[name] = brief(run_child(world, common + extra, limit, port0 + i))
-    # native / library ratios
+            res = run_child(world, common + extra, limit, port0 + i)
+            configs[name] = brief(res) if "value" in res else res
     lib = configs.get("series_library") or {}
     if lib.get("tokens_per_s"):
         line["vs_baseline"] = round(line["value"] / lib["tokens_per_s"], 3)
-        line["vs_baseline_is"] = ("value / tokens_per_s of the same workload on this repo's library arm (torch kernels + NCCL with "
-                                  "host-read split sizes) in a child job of this run; the reference publishes no tokens/s and cannot run here")
-    grouped = {}
-    for name, res in configs.items():
-        if "." in name:
-            cfg_name, impl = name.rsplit(".", 1)
-            grouped.setdefault(cfg_name, {})[impl] = res
-        else:
-            grouped[name] = res
-    for cfg_name, pair in grouped.items():
-        if isinstance(pair, dict) and "native" in pair and "library" in pair:
-            a, b = pair["native"] or {}, pair["library"] or {}
-            if a.get("tokens_per_s") and b.get("tokens_per_s"):
-                pair["native_over_library"] = round(a["tokens_per_s"] / b["tokens_per_s"], 3)
-    # the reference's README reports run-time ratios of expert parallelism over plain FSDP2: 3.49x (full), 2.43x (LoRA)
+        line["vs_baseline_is"] = ("value / tokens_per_s of the same workload on this repo's library arm (torch kernels, NCCL all-to-all with "
+                                  "host-read split sizes) measured by a child job of this run; the reference publishes no tokens/s and "
+                                  "cannot be run here")
+    for name, pair in configs.items():
+        a, b = (pair.get("native") or {}), (pair.get("library") or {})
+        if a.get("tokens_per_s") and b.get("tokens_per_s"):
+            pair["native_over_library"] = round(a["tokens_per_s"] / b["tokens_per_s"], 3)
+
     def tps(c, impl="native"):
-        return ((grouped.get(c) or {}).get(impl) or {}).get("tokens_per_s")
+        return ((configs.get(c) or {}).get(impl) or {}).get("tokens_per_s")
+    # the reference's README reports run-time ratios of expert parallelism over plain FSDP2: 3.49x (full), 2.43x (LoRA)
     ratios = {}
-    if tps("full_ep8") and tps("full_no_ep"):
-        ratios["full_ep8_over_no_ep"] = round(tps("full_ep8") / tps("full_no_ep"), 2)
+    if tps(f"full_ep{world}") and tps("full_no_ep"):
+        ratios[f"full_ep{world}_over_no_ep"] = round(tps(f"full_ep{world}") / tps("full_no_ep"), 2)
     if tps("lora_attn_no_ep"):
-        ratios["lora_attn_ep8_over_no_ep"] = round(line["value"] / tps("lora_attn_no_ep"), 2)
+        ratios[f"lora_attn_ep{world}_over_no_ep"] = round(line["value"] / tps("lora_attn_no_ep"), 2)
     if ratios:
-        ratios["reference_readme_other_hardware"] = {"full_ep8_over_no_ep": 3.49, "lora_attn_ep8_over_no_ep": 2.43}
-        grouped["ep_over_no_ep"] = ratios
-    line["configs"] = grouped
-    line["configs_note"] = (f"child jobs on the same GPUs after the series measurement: {args.extra_warmup} warm-up + {args.extra_steps} timed "
-                            f"optimizer steps each, same data recipe; total limit {int(args.extras_budget_s)} s")
+        ratios["reference_readme_other_hardware_8_gpus"] = {"full_ep8_over_no_ep": 3.49, "lora_attn_ep8_over_no_ep": 2.43}
+        configs["ep_over_no_ep"] = ratios
+    line["configs"] = configs
+    line["configs_note"] = (f"child jobs on the same GPUs after the series measurement, {args.extra_warmup} warm-up + {args.extra_steps} timed "
+                            f"optimizer steps per arm, same data recipe, device-input timing; together limited to {int(args.extras_budget_s)} s")
 
 
 def main():
@@ -431,6 +484,8 @@ def main():
     rank = int(os.environ.get("RANK", 0))
     if args.sub == "check":
         res = run_check(args)
+    elif args.sub == "pair":
+        res = run_pair(args)
     else:
         res = run_measurement(args)
     if world > 1:

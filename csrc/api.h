@@ -51,6 +51,7 @@ typedef struct MdtGemmDesc {
   // an output tile needs it waits (bounded) for the chunks that hold it, so the product starts on the weights that
   // have arrived (the local shard first) while the rest of the all-gather is in flight.
   MdtOperandReady b_ready, b2_ready;
+  MdtOperandReady bl_ready;   // the same for B_l (the whole matrix of the tile's group is waited for)
 } MdtGemmDesc;
 
 int mdt_gemm(const MdtGemmDesc* desc, cudaStream_t stream);

@@ -111,6 +111,7 @@ void gemm(int64_t mode, const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, 
   if (mode != 2) {
     lookup_ready(d.B, &d.b_ready);
     if (d.dual) lookup_ready(d.B2, &d.b2_ready);
+    if (d.K_l > 0) lookup_ready(d.B_l, &d.bl_ready);
   }
   check(mdt_gemm(&d, cur_stream()), "mdt_gemm");
 }

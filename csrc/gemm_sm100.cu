@@ -57,8 +57,8 @@ struct GemmParams {
   const int* row_dest_rank; const int* row_dest_row; const long long* peer_out; const long long* peer_arrive; int num_peers;
   unsigned long long peer_wait_ns;   // limit of the waits for operands that other GPUs or streams deliver
   // B (and B2) may be part of a buffer that an all-gather is still filling: see MdtGemmDesc::b_ready
-  MdtOperandReady rdy_b, rdy_b2;
-  long long b_rows, ldb, b_group_stride;
+  MdtOperandReady rdy_b, rdy_b2, rdy_bl;
+  long long b_rows, ldb, b_group_stride, bl_rows, ldb_l, bl_group_stride;
 };
 
 // Bounded wait until the chunks of the gathered buffer that hold bytes [off, off + len) of an operand have landed.
@@ -74,6 +74,8 @@ __device__ __forceinline__ bool wait_operand_ready(const MdtOperandReady& r, lon
 // The part of B that the tile (group g, columns from n0, `rows` output columns) reads: whole rows of a K-major B,
 // the whole matrix of the group for an MN-major one.
 __device__ __forceinline__ bool wait_b_tile(const GemmParams& p, int g, int n0, int rows) {
+  if (p.rdy_bl.ready != nullptr && p.K_l > 0 &&
+      !wait_operand_ready(p.rdy_bl, (long long)g * p.bl_group_stride * 2, p.bl_rows * p.ldb_l * 2, p.peer_wait_ns)) return false;   // whole matrix
   if (p.rdy_b.ready == nullptr && p.rdy_b2.ready == nullptr) return true;
   long long off, len;
   if (p.b_mn == 0) {
@@ -214,7 +216,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         if (!wait_ge(p.tile_ready + ti, (unsigned)p.tile_expected[ti], p.peer_wait_ns)) { fail(ST_TIMEOUT_PEER); ok = false; break; }
         fence_proxy_async_all();
       }
-      if (p.mode != 2 && total_kb > 0 && (p.rdy_b.ready != nullptr || p.rdy_b2.ready != nullptr)) {
+      if (p.mode != 2 && total_kb > 0 && (p.rdy_b.ready != nullptr || p.rdy_b2.ready != nullptr || p.rdy_bl.ready != nullptr)) {
         // the weight operand is part of a buffer that an all-gather on another stream is still filling
         if (!wait_b_tile(p, t.g, t.n0, BN_OUT)) { fail(ST_TIMEOUT_PEER); ok = false; break; }
         fence_proxy_async_all();
@@ -532,7 +534,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1) gem
         if (!wait_ge(p.tile_ready + ti, (unsigned)p.tile_expected[ti], p.peer_wait_ns)) { fail(ST_TIMEOUT_PEER); ok = false; break; }
         fence_proxy_async_all();
       }
-      if (p.mode != 2 && total_kb > 0 && (p.rdy_b.ready != nullptr || p.rdy_b2.ready != nullptr)) {
+      if (p.mode != 2 && total_kb > 0 && (p.rdy_b.ready != nullptr || p.rdy_b2.ready != nullptr || p.rdy_bl.ready != nullptr)) {
         if (!wait_b_tile(p, t.g, t.n0, BN_OUT)) { fail(ST_TIMEOUT_PEER); ok = false; break; }
         fence_proxy_async_all();
       }
@@ -815,7 +817,7 @@ __global__ void __launch_bounds__(TALL_THREADS, 1) gemm_sm100_tall_kernel(const 
         if (!ok) break;
         fence_proxy_async_all();
       }
-      if (p.mode != 2 && total_kb > 0 && (p.rdy_b.ready != nullptr || p.rdy_b2.ready != nullptr)) {
+      if (p.mode != 2 && total_kb > 0 && (p.rdy_b.ready != nullptr || p.rdy_b2.ready != nullptr || p.rdy_bl.ready != nullptr)) {
         if (!wait_b_tile(p, t.g, t.n0, BN_OUT)) { fail(ST_TIMEOUT_PEER); ok = false; break; }
         fence_proxy_async_all();
       }
@@ -1271,9 +1273,10 @@ extern "C" int mdt_gemm(const MdtGemmDesc* d, cudaStream_t stream) {
   p.row_dest_rank = d->row_dest_rank; p.row_dest_row = d->row_dest_row; p.peer_out = d->peer_out; p.peer_arrive = d->peer_arrive;
   p.num_peers = d->num_peers;
   p.peer_wait_ns = mdt_peer_wait_limit_ns();
-  p.rdy_b = d->b_ready; p.rdy_b2 = d->b2_ready;
-  if (p.mode == 2) { p.rdy_b.ready = nullptr; p.rdy_b2.ready = nullptr; }
+  p.rdy_b = d->b_ready; p.rdy_b2 = d->b2_ready; p.rdy_bl = d->bl_ready;
+  if (p.mode == 2) { p.rdy_b.ready = nullptr; p.rdy_b2.ready = nullptr; p.rdy_bl.ready = nullptr; }
   p.b_rows = d->b_rows; p.ldb = d->ldb; p.b_group_stride = d->b_group_stride;
+  p.bl_rows = d->bl_rows; p.ldb_l = d->ldb_l; p.bl_group_stride = d->bl_group_stride;
   if (p.row_dest_rank != nullptr && (p.dual || p.c_fp32 || p.accumulate || p.mode == 2)) return -12;
   if (p.N % 8 != 0 || p.ldc % 8 != 0) return -10;
   if (p.dual && (p.b_mn != 0 || p.c_fp32 || p.accumulate)) return -11;

@@ -60,10 +60,11 @@ def materialize_module(module: nn.Module, device, seed: int, prefix: str, std: f
             if sub.router.layer.weight.device.type == "meta":
                 args = sub.args
                 args.device = device
-                sub.router.layer.weight = nn.Parameter(torch.empty_like(sub.router.layer.weight, device=device))
+                old_r = sub.router.layer.weight
+                sub.router.layer.weight = nn.Parameter(torch.empty_like(old_r, device=device), requires_grad=old_r.requires_grad)
                 for wname in ("w1", "w2", "w3"):
                     old = getattr(sub.experts.mlp, wname)
-                    setattr(sub.experts.mlp, wname, nn.Parameter(torch.empty_like(old, device=device)))
+                    setattr(sub.experts.mlp, wname, nn.Parameter(torch.empty_like(old, device=device), requires_grad=old.requires_grad))
                 init_moe_(sub, seed, full_name, range(args.moe_num_experts), None, args.ffn_hidden_size)
             continue
         for pname, p in list(sub._parameters.items()):
@@ -77,6 +78,13 @@ def materialize_module(module: nn.Module, device, seed: int, prefix: str, std: f
                 t.fill_(1.0)
             elif "lora_B" in tag:
                 t.zero_()
+            elif ".lora_A." in tag:
+                # adapter created on the meta device: the same seeded kaiming-uniform values that
+                # `peft.lora.get_peft_model` gives an adapter created on a real device
+                gen = torch.Generator(device=t.device)
+                gen.manual_seed(_seed_of(seed, tag.split(".lora_A.")[0] + ".lora_A"))
+                bound = 1.0 / (t.shape[-1] ** 0.5)
+                t.uniform_(-bound, bound, generator=gen)
             else:
                 seeded_normal_(t, std, seed, tag)
             sub._parameters[pname] = nn.Parameter(t, requires_grad=p.requires_grad)

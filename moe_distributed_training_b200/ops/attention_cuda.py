@@ -12,8 +12,21 @@ import torch
 import torch.nn.functional as F
 
 
+def _sdpa_backends():
+    """Flash / memory-efficient SDPA (what the reference's `attn_implementation='sdpa'` selects under its torch 2.3),
+    not the cuDNN backend: that one builds a new execution plan for every new sequence length (6-7 ms of host time
+    per call), which one-sequence micro-batches of random length would pay on every call."""
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+    return sdpa_kernel([SDPBackend.FLASH_ATTENTION, SDPBackend.EFFICIENT_ATTENTION, SDPBackend.MATH])
+
+
 def sdpa_attention(q, k, v, cu_seqlens, max_seqlen=None):
-    """Library path (cuDNN / flash SDPA): the baseline, and the route for head_dim != 128."""
+    """Library path (torch SDPA): the baseline, and the route for head_dim != 128."""
+    with _sdpa_backends():
+        return _sdpa_attention(q, k, v, cu_seqlens, max_seqlen)
+
+
+def _sdpa_attention(q, k, v, cu_seqlens, max_seqlen=None):
     T = q.shape[0]
     nseq = cu_seqlens.numel() - 1
     if nseq == 1:

@@ -41,6 +41,14 @@ def _round_up(x: int, m: int) -> int:
     return (x + m - 1) // m * m
 
 
+def _gemm_only_weight(qualname: str, p) -> bool:
+    """Projection and expert weight matrices: read by nothing but the GEMM kernels' weight-operand loads."""
+    if p.dim() != 2 or p.numel() < int(os.environ.get("MDT_GEMM_ONLY_MIN_NUMEL", 1 << 20)) or "lora_" in qualname:
+        return False
+    leaf = qualname.rsplit(".", 2)
+    return qualname.endswith("_proj.weight") or (len(leaf) >= 2 and leaf[-1] in ("w1", "w2", "w3") and ".experts." in qualname)
+
+
 class FlatParamGroup:
     """Parameters of one unit flattened into a single buffer sharded over `group`."""
 
@@ -56,7 +64,14 @@ class FlatParamGroup:
         p0 = entries[0][2]
         self.dtype, self.device = p0.dtype, p0.device
         self.qualnames = []
+        # Large matrices that are only ever read as the weight operand of a GEMM go to the back of the buffer;
+        # everything else (norm weights, the router, adapters) comes first.  A gather with progress flags then
+        # delivers the small front part first, and the GEMMs wait for their own part of the rest themselves.
+        entries = sorted(entries, key=lambda e: 1 if _gemm_only_weight(e[3], e[2]) else 0)
+        self.small_numel = 0
         for mod, name, p, qual in entries:
+            if not _gemm_only_weight(qual, p):
+                self.small_numel = off + _round_up(p.numel(), 8)
             self.specs.append((mod, name, tuple(p.shape), p.numel(), off))
             self.qualnames.append(qual)
             off += _round_up(p.numel(), 8)  # 16-byte aligned starts (bulk-copy friendly)
@@ -173,6 +188,20 @@ class _BufferPool:
         self.owner[i] = None
         self.free_events[i] = event
 
+    def flags(self, slot, groups, ext):
+        """Progress-flag tensors of the buffers of `slot` (one per group; created on first use).  A flag tensor belongs
+        to a buffer, not to a unit: its epoch grows with every gather into that buffer."""
+        store = self.__dict__.setdefault("_flags", {})
+        out = []
+        for j, g in enumerate(groups):
+            key = (slot, j)
+            if key not in store:
+                # sized for the largest unit that can use the buffer: flags of a chunk layout never exceed one per 16 bytes
+                n = max(int(ext.ag_chunks(g.ws, 16 * ((self.slots[slot][j].numel() * self.slots[slot][j].element_size() // g.ws + 15) // 16))[0]), 1)
+                store[key] = {"ready": torch.zeros(n + g.ws, dtype=torch.int32, device=self.slots[slot][j].device), "epoch": 0}
+            out.append(store[key])
+        return out
+
 
 class _LayerFn(torch.autograd.Function):
     """One decoder block: graph-free forward, recompute + backward + gradient reduction."""
@@ -230,7 +259,7 @@ class ShardedMixtral:
     def __init__(self, model: MixtralForCausalLM, shard_group=None, replicate_group=None,
                  expert_dp_group=None, world_group=None, shard_experts: bool = False,
                  sync_each_batch: bool = False, pool_slots: int = 3, resident_params: Optional[bool] = None,
-                 resident_limit_bytes: int = 16 << 30, recompute: bool = True):
+                 resident_limit_bytes: int = 16 << 30, recompute: bool = True, lazy_init=None):
         self.model = model
         self.shard_group, self.replicate_group = shard_group, replicate_group
         self.expert_dp_group, self.world_group = expert_dp_group, world_group
@@ -241,6 +270,11 @@ class ShardedMixtral:
         self.units: List[FsdpUnit] = []
         for i, layer in enumerate(layers):
             exclude = () if shard_experts else (layer.block_sparse_moe,)
+            if lazy_init is not None:
+                # blocks still on the meta device: create this block's tensors now; FlatParamGroup keeps the shard
+                # and drops the rest before the next block is created
+                from ..models.init import materialize_module
+                materialize_module(layer, lazy_init[0], lazy_init[1], f"model.layers.{i}", std=lazy_init[2])
             self.units.append(FsdpUnit(f"layers.{i}", [(f"model.layers.{i}", layer)], shard_group, exclude))
         self.root = FsdpUnit("root", [("model.embed_tokens", model.model.embed_tokens),
                                       ("model.norm", model.model.norm), ("lm_head", model.lm_head)], shard_group)
@@ -250,11 +284,20 @@ class ShardedMixtral:
             for g in u.groups:
                 shards.append(g.shard)
         model._flat_shards = shards
-        dev = next(model.parameters()).device
+        dev = next(p for p in model.parameters() if p.device.type != "meta").device
         self.device = dev
         self.is_cuda = dev.type == "cuda"
-        self.comm_stream = torch.cuda.Stream(device=dev) if (self.is_cuda and self.ws > 1) else None
+        # side streams get a high priority: their kernels are small and others wait for what they deliver
+        self.comm_stream = torch.cuda.Stream(device=dev, priority=-1) if (self.is_cuda and self.ws > 1) else None
+        self.rs_stream = torch.cuda.Stream(device=dev, priority=-1) if (self.is_cuda and self.ws > 1) else None
         self.pool = None
+        self._last_microbatch = False
+        self._rs_epoch = 0
+        self._rs_events = []
+        # MDT_FLAGGED_GATHER=0: the compute stream waits for a whole gather instead of the GEMMs waiting per chunk
+        self.flagged_gather = os.environ.get("MDT_FLAGGED_GATHER", "1") != "0"
+        # MDT_OVERLAP_RS=0: all gradient reduce-scatters after the last backward instead of block by block during it
+        self.overlap_rs = os.environ.get("MDT_OVERLAP_RS", "1") != "0"
         # With 180 GB per GPU the gathered dense parameters of a Mixtral-8x7B (3.2 GB in bf16) can simply stay
         # resident: every rank keeps a full copy next to its shard and re-reads from its peers only the groups an
         # optimizer step has changed (ZeRO-2 style).  Frozen groups are gathered once per run instead of twice per
@@ -310,7 +353,7 @@ class ShardedMixtral:
             if g.trainable:
                 g.arena_acc_off = off
                 off = symm._align(off + g.padded * 4)
-        self.peers = symm.FlatPeers(self.shard_group, off, self.device)
+        self.peers = symm.FlatPeers(self.shard_group, off, self.device, flag_slots=max(64, len(self.units) + 8))
         self._ext = cuda_ops.ext
         self._status = cuda_ops.status_tensor(self.device)
         buf = self.peers.buffer
@@ -327,6 +370,8 @@ class ShardedMixtral:
                 g.acc_table = self.peers.table(g.arena_acc_off)
         self._flag_off = self.peers.nbytes - self.peers.flag_bytes
         self._flag_table = self.peers.table(self._flag_off)
+        for i, u in enumerate(self.all_units()):
+            u.flag_index = 1 + i                     # slot 0 belongs to the barrier
         self.peer_barrier()
 
     def peer_barrier(self):
@@ -352,12 +397,29 @@ class ShardedMixtral:
         self.peer_barrier()
 
     # ------------------------------------------------------------------ buffers
-    def _gather_into(self, unit: FsdpUnit, buffers):
-        for g, buf in zip(unit.groups, buffers):
+    def _gather_into(self, unit: FsdpUnit, buffers, flags=None):
+        """`flags` (one entry per group, None or a dict with the progress-flag tensor of the destination buffer): the
+        gather publishes its progress there and returns what a consumer needs to wait on the small front part."""
+        waits = []
+        for j, (g, buf) in enumerate(zip(unit.groups, buffers)):
             if self.peers is not None:
-                self._ext.ag_pull(buf[:g.padded], g.shard_table, g.ws, g.rank, g.shard_numel * g.shard.element_size())
+                nbytes = g.shard_numel * g.shard.element_size()
+                fl = flags[j] if flags is not None else None
+                if fl is not None and g.small_numel < g.numel:
+                    fl["epoch"] += 1
+                    nflags, chunk_bytes = self._ext.ag_chunks(g.ws, nbytes)
+                    cpr = nflags // g.ws
+                    small = g.small_numel * g.shard.element_size()
+                    last = ((small - 1) // nbytes) * cpr + ((small - 1) % nbytes) // chunk_bytes if small > 0 else -1
+                    self._ext.ag_pull_flagged(buf[:g.padded], g.shard_table, g.ws, g.rank, nbytes, fl["ready"], fl["epoch"], last + 1)
+                    waits.append((fl["ready"], last + 1, fl["epoch"]))
+                else:
+                    self._ext.ag_pull(buf[:g.padded], g.shard_table, g.ws, g.rank, nbytes)
+                    waits.append(None)
             else:
                 coll.all_gather_flat(buf[:g.padded], g.shard.data, g.group)
+                waits.append(None)
+        return waits
 
     def _start_gather(self, idx: int):
         """Issue the all-gather of unit idx (on the side stream when there is one)."""
@@ -374,6 +436,10 @@ class ShardedMixtral:
         slot = self.pool.acquire(idx)
         self._slot[idx] = slot
         bufs = self.pool.slots[slot][:len(unit.groups)]
+        flags = None
+        if self.peers is not None and self.flagged_gather and ops.get_backend() == "native":
+            flags = self.pool.flags(slot, [g for g in unit.groups], self._ext)
+        unit.flag_waits = None
         if self.comm_stream is not None:
             ev = self.pool.free_events[slot]
             # the shards may have just been written by the optimizer on the compute stream
@@ -381,9 +447,11 @@ class ShardedMixtral:
             with torch.cuda.stream(self.comm_stream):
                 if ev is not None:
                     self.comm_stream.wait_event(ev)
-                self._gather_into(unit, bufs)
+                waits = self._gather_into(unit, bufs, flags)
                 unit.ready_event = torch.cuda.Event()
                 unit.ready_event.record(self.comm_stream)
+            if any(w is not None for w in waits):
+                unit.flag_waits = waits
         else:
             self._gather_into(unit, bufs)
         unit.buffers = bufs
@@ -421,7 +489,25 @@ class ShardedMixtral:
         unit = self.units[idx]
         self._start_gather(idx)
         if unit.ready_event is not None:
-            torch.cuda.current_stream().wait_event(unit.ready_event)
+            waits = getattr(unit, "flag_waits", None)
+            if waits is None:
+                torch.cuda.current_stream().wait_event(unit.ready_event)
+            else:
+                # The compute stream does not wait for the gather: it waits (one small kernel) for the front part of
+                # each flagged buffer, which every kernel may read, and the GEMMs wait for the chunks of their weight
+                # operands themselves (csrc/gemm_sm100.cu: wait_b_tile), starting on what has arrived.
+                for w in waits:
+                    if w is not None and w[1] > 0:
+                        self._ext.ag_wait_chunks(w[0], 0, w[1], w[2], self._status)
+                # (a group gathered without flags, e.g. the adapters, is copied by an earlier kernel on the same side
+                # stream than a flagged group that follows it, so a published chunk of the latter implies that the
+                # former is complete; if no flagged group has a front part to wait for, or the flagged group comes
+                # first, fall back to the event)
+                last_plain = max((j for j, w in enumerate(waits) if w is None), default=-1)
+                first_waited = min((j for j, w in enumerate(waits) if w is not None and w[1] > 0), default=None)
+                if first_waited is None or last_plain > first_waited:
+                    torch.cuda.current_stream().wait_event(unit.ready_event)
+                unit.flag_waits = None
             unit.ready_event = None
         if not backward:
             for g, buf in zip(unit.groups, unit.buffers):
@@ -447,20 +533,49 @@ class ShardedMixtral:
         unit.buffers = None
 
     # ------------------------------------------------------------------ gradients
+    def begin_microbatch(self, is_last: bool):
+        """Tell the runner whether the micro-batch about to run is the last one of its optimizer step.  In the last one
+        every block's gradient reduce-scatter starts, on a side stream, as soon as that block's backward has finished
+        (the reference's FSDP2 reduces inside backward too, train_accelerate_fsdp2.py:334-339), instead of all of them
+        after the last backward."""
+        self._last_microbatch = bool(is_last)
+        if is_last:
+            self._rs_epoch += 1
+
     def _reduce_unit_grads(self, unit: FsdpUnit, grads):
         g = unit.trainable_group
         if g is None:
             return
         scale = 1.0 / (self.ws * self.rep)
         if self.sync_each_batch or self.ws == 1:
+            # double-buffered flat gradient: the reduction of one block runs on the side stream while the next block's
+            # backward fills the other buffer
             key = (g.padded, g.dtype)
-            tmp = self._grad_tmp.get(key)
-            if tmp is None:
-                tmp = self._grad_tmp[key] = torch.zeros(g.padded, dtype=g.dtype, device=self.device)
+            ring = self._grad_tmp.get(key)
+            if ring is None:
+                n_buf = 2 if (self.rs_stream is not None and self.overlap_rs) else 1
+                ring = self._grad_tmp[key] = {"bufs": [torch.zeros(g.padded, dtype=g.dtype, device=self.device) for _ in range(n_buf)],
+                                              "events": [None] * n_buf, "next": 0}
+            i = ring["next"]
+            ring["next"] = (i + 1) % len(ring["bufs"])
+            tmp = ring["bufs"][i]
+            if ring["events"][i] is not None:
+                torch.cuda.current_stream().wait_event(ring["events"][i])     # its previous reduction has read it
             g.flat_grad(grads, tmp)
             if g.shard.grad is None:
                 g.shard.grad = torch.zeros_like(g.shard.data)
-            coll.reduce_scatter_flat(g.shard.grad, tmp, g.group, scale=scale, accumulate=True)
+            if len(ring["bufs"]) > 1 and self.ws > 1:
+                ready = torch.cuda.Event()
+                ready.record(torch.cuda.current_stream())
+                with torch.cuda.stream(self.rs_stream):
+                    self.rs_stream.wait_event(ready)
+                    coll.reduce_scatter_flat(g.shard.grad, tmp, g.group, scale=scale, accumulate=True)
+                    done = torch.cuda.Event()
+                    done.record(self.rs_stream)
+                ring["events"][i] = done
+                self._rs_events.append(done)
+            else:
+                coll.reduce_scatter_flat(g.shard.grad, tmp, g.group, scale=scale, accumulate=True)
         else:
             if g.acc is None:
                 g.acc = torch.zeros(g.padded, dtype=torch.float32, device=self.device)
@@ -474,34 +589,59 @@ class ShardedMixtral:
             if dst:
                 torch._foreach_add_(dst, src)
             g._acc_dirty = True
+            if self.peers is not None and self.overlap_rs and self._last_microbatch:
+                self._reduce_block_now(unit, g, scale)
+
+    def _reduce_block_now(self, unit: FsdpUnit, g: FlatParamGroup, scale: float):
+        """Last micro-batch: this block's accumulator is final.  One kernel on the side stream announces that to the
+        peers, waits for their announcements, reads their slices and writes the scaled, cast shard gradient, while the
+        compute stream goes on with the next block's backward."""
+        fresh = g.shard.grad is None
+        if fresh:
+            g.shard.grad = torch.empty_like(g.shard.data)
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream())
+        p = self.peers
+        with torch.cuda.stream(self.rs_stream):
+            self.rs_stream.wait_event(ready)
+            self._ext.rs_block(g.shard.grad, g.acc_table, self._flag_table, p.bases[p.rank] + self._flag_off, unit.flag_index, g.ws, g.rank,
+                               True, scale, not fresh, self._rs_epoch, self._status)
+            done = torch.cuda.Event()
+            done.record(self.rs_stream)
+        self._rs_events.append(done)
+        g._rs_done = True
 
     def reduce_gradients(self):
         """Finish the gradient reductions of one optimizer step (call after the last backward)."""
         scale = 1.0 / (self.ws * self.rep)
-        if self.peers is not None:
+        for ev in self._rs_events:                       # reductions that ran beside the backward pass
+            torch.cuda.current_stream().wait_event(ev)
+        self._rs_events = []
+        pending = [u.trainable_group for u in self.units + [self.root]
+                   if u.trainable_group is not None and u.trainable_group.acc is not None
+                   and getattr(u.trainable_group, "_acc_dirty", False) and not getattr(u.trainable_group, "_rs_done", False)]
+        if self.peers is not None and pending:
             self.peer_barrier()          # every rank has finished adding into its accumulators
-        for u in self.units + [self.root]:
-            g = u.trainable_group
-            if g is None:
-                continue
-            if g.acc is not None and getattr(g, "_acc_dirty", False):
-                if self.peers is not None:
-                    # read the peers' accumulators; scale, cast and write the shard gradient in one pass
-                    fresh = g.shard.grad is None
-                    if fresh:
-                        g.shard.grad = torch.empty_like(g.shard.data)
-                    self._ext.rs_pull(g.shard.grad, g.acc_table, g.ws, g.rank, True, scale, not fresh)
-                else:
-                    if g.shard.grad is None:
-                        g.shard.grad = torch.zeros_like(g.shard.data)
-                    coll.reduce_scatter_flat(g.shard.grad, g.acc, g.group, scale=scale, accumulate=True)
-        if self.peers is not None:
+        for g in pending:
+            if self.peers is not None:
+                # read the peers' accumulators; scale, cast and write the shard gradient in one pass
+                fresh = g.shard.grad is None
+                if fresh:
+                    g.shard.grad = torch.empty_like(g.shard.data)
+                self._ext.rs_pull(g.shard.grad, g.acc_table, g.ws, g.rank, True, scale, not fresh)
+            else:
+                if g.shard.grad is None:
+                    g.shard.grad = torch.zeros_like(g.shard.data)
+                coll.reduce_scatter_flat(g.shard.grad, g.acc, g.group, scale=scale, accumulate=True)
+        dirty = [u.trainable_group for u in self.units + [self.root]
+                 if u.trainable_group is not None and u.trainable_group.acc is not None and getattr(u.trainable_group, "_acc_dirty", False)]
+        if self.peers is not None and dirty:
             self.peer_barrier()          # every rank has finished reading before the accumulators are cleared
-        for u in self.units + [self.root]:
-            g = u.trainable_group
-            if g is not None and g.acc is not None and getattr(g, "_acc_dirty", False):
-                g.acc.zero_()
-                g._acc_dirty = False
+        for g in dirty:
+            g.acc.zero_()
+            g._acc_dirty = False
+            g._rs_done = False
+        self._last_microbatch = False
         for u in self.units + [self.root]:
             g = u.trainable_group
             if g is None:

@@ -115,7 +115,9 @@ class Engine:
             # its micro-batches longest first: ranks then work on sequences of similar length at the same time.
             microbatches = sorted(microbatches, key=lambda mb: -int(mb["input_ids"].numel()))
         loss_sum = None
-        for mb in microbatches:
+        for i, mb in enumerate(microbatches):
+            if hasattr(self.runner, "begin_microbatch"):
+                self.runner.begin_microbatch(i == ga - 1)
             l = self.forward_backward(mb, 1.0 / ga)
             loss_sum = l if loss_sum is None else loss_sum + l
         self.runner.reduce_gradients()
@@ -178,7 +180,17 @@ def build_engine(cfg: MixtralConfig, *, dtype: torch.dtype = torch.bfloat16, dev
                          parallize_tensor=use_tp_sharding, seed=seed)
     elif world > 1:
         mesh = init_device_mesh(device_type, (world,), mesh_dim_names=(KEY_DATA_PARALLEL,))
-    materialize_module(model, device, seed, "", std=cfg.initializer_range)
+    targets = lora_targets(use_lora, True)
+    # Without expert parallelism every rank would first hold the whole model (93 GB of bf16 for Mixtral-8x7B) only
+    # to keep an eighth of it.  The decoder blocks then stay on the meta device here and the sharding layer creates
+    # each block's tensors just before it cuts out its shard (same seeds per tensor name, so the same values).
+    lazy_blocks = (world > 1 and ep_size <= 1 and checkpoint is None
+                   and (targets is None or "experts" not in targets))
+    if lazy_blocks:
+        for prefix, mod in (("model.embed_tokens", model.model.embed_tokens), ("model.norm", model.model.norm), ("lm_head", model.lm_head)):
+            materialize_module(mod, device, seed, prefix, std=cfg.initializer_range)
+    else:
+        materialize_module(model, device, seed, "", std=cfg.initializer_range)
     if checkpoint is not None:
         from ..checkpoint import hf_safetensors as hfst
         from ..parallel.shard_moe import get_resolved_checkpoint_location
@@ -190,7 +202,6 @@ def build_engine(cfg: MixtralConfig, *, dtype: torch.dtype = torch.bfloat16, dev
                 hfst.load_moe_layer(layer.block_sparse_moe, ckpt_dir, wm, f"model.layers.{i}", "block_sparse_moe",
                                     range(cfg.num_local_experts))
 
-    targets = lora_targets(use_lora, True)
     if targets is not None:
         get_peft_model(model, LoraConfig(r=lora_r, lora_alpha=lora_alpha, target_modules=targets),
                        adapter_dtype=dtype, seed=seed)
@@ -215,7 +226,8 @@ def build_engine(cfg: MixtralConfig, *, dtype: torch.dtype = torch.bfloat16, dev
         sync_each_batch = True
     runner = ShardedMixtral(model, shard_group, replicate_group, expert_dp_group, world_group,
                             shard_experts=shard_experts, sync_each_batch=sync_each_batch,
-                            recompute=activation_checkpointing)
+                            recompute=activation_checkpointing,
+                            lazy_init=(device, seed, cfg.initializer_range) if lazy_blocks else None)
     params = [p for p in model.parameters() if p.requires_grad]
     opt = FusedAdamW(params, lr=learning_rate, weight_decay=weight_decay, state_dtype=optimizer_state_dtype)
     sched = get_scheduler(lr_scheduler_type, opt, num_warmup_steps, num_training_steps)

@@ -27,6 +27,13 @@ def main():
     ds = SyntheticInstructionDataset(cfg.vocab_size, 6, 100, 400, seed=3, rank=rank)
     mbs = [collate_packed([ex]) for ex in ds.examples]
     result = {}
+    if mode.endswith("-pool"):
+        # gather per use through the buffer pool (no resident copies), with matrices of the tiny model counted as
+        # GEMM-only weights: the peer-memory arm then runs the all-gather with progress flags and the GEMMs that
+        # wait for their weight operand chunk by chunk
+        os.environ["MDT_RESIDENT_PARAMS"] = "0"
+        os.environ["MDT_GEMM_ONLY_MIN_NUMEL"] = str(1 << 16)
+        mode = mode[:-len("-pool")]
     for impl in ("nccl", "fused"):
         if mode.startswith("fsdp"):
             # no expert parallelism: everything, experts included, is sharded; compare NCCL collectives with the

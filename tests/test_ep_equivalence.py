@@ -52,6 +52,10 @@ def _run(rank, world, mode, steps):
         eng = build_engine(cfg, ep_size=2, use_tp_sharding=True, **kw)
     elif mode == "fsdp":
         eng = build_engine(cfg, ep_size=1, **kw)
+    elif mode == "fsdp-lora":
+        # decoder blocks (frozen experts included) are created block by block inside the sharding layer, with the
+        # attention adapters added while the blocks are still on the meta device
+        eng = build_engine(cfg, ep_size=1, use_lora="attn-only", **kw)
     elif mode == "ep-lora":
         eng = build_engine(cfg, ep_size=world, use_lora="all", **kw)
     else:
@@ -159,6 +163,17 @@ def test_fsdp2_no_ep_matches_unsharded():
     for rank, (losses, grads, _) in enumerate(res):
         assert abs(losses[0] - ref_losses[rank]) < 1e-5
         # experts were sharded like dense parameters: full_state returned whole tensors
+        for name, g in grads.items():
+            err = (g - ref_grads[name]).abs().max().item()
+            assert err < 2e-6 + 1e-4 * ref_grads[name].abs().max().item(), name
+
+
+def test_fsdp2_no_ep_lora_attn_matches_unsharded():
+    ref_losses, ref_grads, cfg = _reference(2, use_lora="attn-only")
+    res = run_distributed(_run, 2, "fsdp-lora", 1)
+    for rank, (losses, grads, _) in enumerate(res):
+        assert abs(losses[0] - ref_losses[rank]) < 1e-5
+        assert set(grads) == set(ref_grads) and grads
         for name, g in grads.items():
             err = (g - ref_grads[name]).abs().max().item()
             assert err < 2e-6 + 1e-4 * ref_grads[name].abs().max().item(), name

@@ -24,14 +24,17 @@ def _run(n, mode, tmp_path, port):
     return json.load(open(out))
 
 
-@pytest.mark.parametrize("mode", ["full", "lora", "fsdp", "fsdp-lora"])
+MODES = ["full", "lora", "fsdp", "fsdp-lora", "full-pool", "fsdp-lora-pool"]
+
+
+@pytest.mark.parametrize("mode", MODES)
 def test_fused_exchange_matches_nccl_exchange(tmp_path, mode):
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least two GPUs")
     # two ranks by default; MDT_TEST_RANKS=4 (with at least four GPUs) runs the same comparison on four
     n = 4 if (n >= 4 and os.environ.get("MDT_TEST_RANKS") == "4") else 2
-    res = _run(n, mode, tmp_path, 29610 + ["full", "lora", "fsdp", "fsdp-lora"].index(mode))
+    res = _run(n, mode, tmp_path, 29610 + MODES.index(mode))
     for rank_res in res:
         a, b = rank_res["nccl"], rank_res["fused"]
         for la, lb in zip(a["losses"], b["losses"]):
