@@ -35,6 +35,7 @@ typedef struct MdtGemmDesc {
   const void* B_l; const void* B2_l; long long bl_rows, bl_cols, ldb_l, bl_group_stride; int b_mn_l;
   // output
   void* C; void* C2; void* C3;   // dual mode: C = h, optional C2 = gate, C3 = up (all bf16)
+  const void* R;                 // optional (mode 0/1, not dual): bf16 matrix laid out like C, added to the result (residual connection)
   long long ldc, c_group_stride;
   int c_fp32;          // C is fp32 instead of bf16
   int accumulate;      // C += alpha * (A*B) instead of C = alpha * (A*B)
@@ -78,8 +79,11 @@ void mdt_gemm_set_pair_cap(int pairs);
 
 // ---- element-wise / normalisation / loss / optimizer (elementwise.cu) --------------------------
 int mdt_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps, cudaStream_t s);
-int mdt_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx, float* dw_partial,
+// dres (optional, bf16 [rows, cols]): added to dx (the gradient arriving over the residual connection)
+int mdt_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, const void* dres, void* dx, float* dw_partial,
                     int rows, int cols, int n_partial, cudaStream_t s);
+// sums the n_partial rows of dw_partial into dw_bf16 and / or dw_f32 (either may be NULL)
+int mdt_rmsnorm_dw_finalize(const float* dw_partial, int n_partial, int cols, void* dw_bf16, float* dw_f32, cudaStream_t s);
 int mdt_rope(const void* x, void* y, const int* positions, int tokens, int heads, int head_dim, float theta,
              int inverse, cudaStream_t s);
 // dst[0 : rows_used[0]] = src[0 : rows_used[0]] for row buffers of `cols` bf16 elements sized for a capacity (n elements)
@@ -110,8 +114,9 @@ int mdt_make_plan(const int* expert_ids, int num_slots, int num_experts, int blo
                   int* padded_offsets, int* dest_row, int* src_slot, int* scratch, cudaStream_t s);
 int mdt_gather_rows(const void* x, const int* src_slot, const int* padded_offsets, int num_experts, const void* slot_scale,
                     void* out, int capacity, int cols, int top_k, cudaStream_t s);
-int mdt_combine_rows(const void* y, const int* dest_row, const void* weights, void* out, int tokens, int cols, int top_k,
-                     cudaStream_t s);
+// residual (optional, bf16 [tokens, cols]): added to the combined rows
+int mdt_combine_rows(const void* y, const int* dest_row, const void* weights, const void* residual, void* out, int tokens, int cols,
+                     int top_k, cudaStream_t s);
 int mdt_combine_wgrad(const void* y, const int* dest_row, const void* dout, void* dweights, int tokens, int cols, int top_k,
                       cudaStream_t s);
 

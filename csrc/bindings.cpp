@@ -71,7 +71,7 @@ void gemm(int64_t mode, const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, 
           bool a_mn_l, const OptTensor& B_l, const OptTensor& B2_l, bool b_mn_l, int64_t K_l, const OptTensor& C2,
           const OptTensor& C3, bool accumulate, double alpha, const OptTensor& status, const OptTensor& tile_ready,
           const OptTensor& tile_expected, const OptTensor& row_dest_rank, const OptTensor& row_dest_row, const OptTensor& peer_out,
-          const OptTensor& peer_arrive) {
+          const OptTensor& peer_arrive, const OptTensor& residual = std::nullopt) {
   CHECK_BF16(A); CHECK_BF16(B);
   c10::cuda::CUDAGuard guard(A.device());
   MdtGemmDesc d;
@@ -98,6 +98,11 @@ void gemm(int64_t mode, const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, 
   d.c_fp32 = C.scalar_type() == at::kFloat;
   TORCH_CHECK(d.c_fp32 || C.scalar_type() == at::kBFloat16, "C must be bf16 or fp32");
   d.accumulate = accumulate; d.alpha = (float)alpha;
+  if (residual.has_value()) {
+    TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->dim() == 2 && residual->stride(1) == 1 && residual->stride(0) == d.ldc &&
+                residual->size(0) >= M && residual->size(1) == N, "residual must be a bf16 matrix laid out like C");
+    d.R = residual->data_ptr();
+  }
   d.status = status.has_value() ? status->data_ptr<int>() : nullptr;
   if (tile_ready.has_value()) {
     d.tile_ready = (const unsigned*)tile_ready->data_ptr();
@@ -125,7 +130,8 @@ std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
   check(mdt_rmsnorm_fwd(x2.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), (int)x2.size(0), (int)x2.size(1), (float)eps, cur_stream()), "rmsnorm_fwd");
   return {y.view(x.sizes()), rstd};
 }
-std::vector<Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& w, const Tensor& dy, const Tensor& rstd) {
+// dres (optional): gradient that reaches x over the residual connection, added to dx in the same pass
+std::vector<Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& w, const Tensor& dy, const Tensor& rstd, const OptTensor& dres = std::nullopt) {
   c10::cuda::CUDAGuard guard(x.device());
   auto x2 = x.reshape({-1, x.size(-1)}).contiguous();
   auto dy2 = dy.reshape({-1, x.size(-1)}).contiguous();
@@ -134,8 +140,21 @@ std::vector<Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& w, const Tensor& 
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   const int np = rows < sms ? (rows < 1 ? 1 : rows) : sms;
   auto dwp = torch::empty({np, cols}, x.options().dtype(at::kFloat));
-  check(mdt_rmsnorm_bwd(x2.data_ptr(), w.data_ptr(), dy2.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(), dwp.data_ptr<float>(), rows, cols, np, cur_stream()), "rmsnorm_bwd");
+  const void* dr = nullptr;
+  Tensor drc;
+  if (dres.has_value()) { drc = dres->reshape({-1, x.size(-1)}).contiguous(); TORCH_CHECK(drc.scalar_type() == at::kBFloat16); dr = drc.data_ptr(); }
+  check(mdt_rmsnorm_bwd(x2.data_ptr(), w.data_ptr(), dy2.data_ptr(), rstd.data_ptr<float>(), dr, dx.data_ptr(), dwp.data_ptr<float>(), rows, cols, np, cur_stream()), "rmsnorm_bwd");
   return {dx.view(x.sizes()), dwp};
+}
+// weight gradient of RMSNorm from the per-CTA partial sums of rmsnorm_bwd, in w's dtype
+Tensor rmsnorm_dw(const Tensor& dw_partial, const Tensor& like) {
+  c10::cuda::CUDAGuard guard(dw_partial.device());
+  auto out = torch::empty({dw_partial.size(1)}, like.options());
+  const bool f32 = out.scalar_type() == at::kFloat;
+  TORCH_CHECK(f32 || out.scalar_type() == at::kBFloat16);
+  check(mdt_rmsnorm_dw_finalize(dw_partial.data_ptr<float>(), (int)dw_partial.size(0), (int)dw_partial.size(1), f32 ? nullptr : out.data_ptr(),
+                                f32 ? out.data_ptr<float>() : nullptr, cur_stream()), "rmsnorm_dw_finalize");
+  return out;
 }
 Tensor rope(const Tensor& x, const Tensor& positions, double theta, bool inverse) {
   CHECK_BF16(x);
@@ -239,16 +258,18 @@ std::vector<Tensor> router_fwd(const Tensor& x, const Tensor& w, int64_t top_k, 
   check(mdt_router_fwd(x.data_ptr(), w.data_ptr(), scores.data_ptr(), weights.data_ptr(), idx.data_ptr<int>(), T, H, E, (int)top_k, normalize, cur_stream()), "router_fwd");
   return {scores, weights, idx};
 }
+// dx_accum (optional, bf16 [T, H]): the input gradient is added to it instead of written to a new tensor
 std::vector<Tensor> router_bwd(const Tensor& x, const Tensor& w, const Tensor& idx, const Tensor& dweights, const OptTensor& dscores,
-                               bool normalize) {
+                               bool normalize, const OptTensor& dx_accum = std::nullopt) {
   c10::cuda::CUDAGuard guard(x.device());
   const int T = (int)x.size(0), H = (int)x.size(1), E = (int)w.size(0), k = (int)idx.size(1);
-  auto dx = torch::empty_like(x);
+  if (dx_accum.has_value()) TORCH_CHECK(dx_accum->is_contiguous() && dx_accum->scalar_type() == at::kBFloat16 && dx_accum->numel() == x.numel());
+  auto dx = dx_accum.has_value() ? *dx_accum : torch::empty_like(x);
   auto buf = torch::zeros({(int64_t)E * H + (int64_t)T * E}, x.options().dtype(at::kFloat));
   auto dwc = dweights.contiguous();
   OptTensor dsc = dscores.has_value() ? OptTensor(dscores->contiguous()) : std::nullopt;
   check(mdt_router_bwd(x.data_ptr(), w.data_ptr(), nullptr, nullptr, idx.data_ptr<int>(), dwc.data_ptr(), cptr(dsc), dx.data_ptr(),
-                       buf.data_ptr<float>(), T, H, E, k, normalize, 0, cur_stream()), "router_bwd");
+                       buf.data_ptr<float>(), T, H, E, k, normalize, dx_accum.has_value() ? 1 : 0, cur_stream()), "router_bwd");
   return {dx, buf.narrow(0, 0, (int64_t)E * H).view({E, H})};
 }
 // returns counts[E], padded_offsets[E+1], dest_row[n], src_slot[capacity]
@@ -273,13 +294,15 @@ Tensor gather_rows(const Tensor& x, const Tensor& src_slot, const OptTensor& pad
                         cptr(slot_scale), out.data_ptr(), (int)src_slot.numel(), (int)x.size(1), (int)top_k, cur_stream()), "gather_rows");
   return out;
 }
-Tensor combine_rows(const Tensor& y, const Tensor& dest_row, const OptTensor& weights, int64_t top_k) {
+Tensor combine_rows(const Tensor& y, const Tensor& dest_row, const OptTensor& weights, int64_t top_k, const OptTensor& residual = std::nullopt) {
   CHECK_BF16(y);
   c10::cuda::CUDAGuard guard(y.device());
   TORCH_CHECK(y.is_contiguous());
   const int T = (int)(dest_row.numel() / top_k);
   auto out = torch::empty({T, y.size(1)}, y.options());
-  check(mdt_combine_rows(y.data_ptr(), dest_row.data_ptr<int>(), cptr(weights), out.data_ptr(), T, (int)y.size(1), (int)top_k, cur_stream()), "combine_rows");
+  if (residual.has_value())
+    TORCH_CHECK(residual->is_contiguous() && residual->scalar_type() == at::kBFloat16 && residual->numel() == out.numel(), "residual must match the output");
+  check(mdt_combine_rows(y.data_ptr(), dest_row.data_ptr<int>(), cptr(weights), cptr(residual), out.data_ptr(), T, (int)y.size(1), (int)top_k, cur_stream()), "combine_rows");
   return out;
 }
 Tensor combine_wgrad(const Tensor& y, const Tensor& dest_row, const Tensor& dout, int64_t top_k) {
@@ -469,16 +492,17 @@ namespace {
 struct Lin { Tensor W; OptTensor A, B; double s; };   // y = x W^T + s (x A^T) B^T
 
 void gemm_raw(int mode, const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, Tensor& C, int64_t M, int64_t N, int64_t K,
-              const OptTensor& A_l, const OptTensor& B_l, bool b_mn_l, int64_t K_l, bool accumulate, double alpha, const OptTensor& status) {
+              const OptTensor& A_l, const OptTensor& B_l, bool b_mn_l, int64_t K_l, bool accumulate, double alpha, const OptTensor& status,
+              const OptTensor& residual = std::nullopt) {
   gemm(mode, A, a_mn, B, b_mn, C, M, N, K, 1, std::nullopt, 0, std::nullopt, A_l, false, B_l, std::nullopt, b_mn_l, K_l, std::nullopt,
-       std::nullopt, accumulate, alpha, status, std::nullopt, std::nullopt, std::nullopt, std::nullopt, std::nullopt, std::nullopt);
+       std::nullopt, accumulate, alpha, status, std::nullopt, std::nullopt, std::nullopt, std::nullopt, std::nullopt, std::nullopt, residual);
 }
-// y = x W^T (+ LoRA); returns (y, t) with t = s x A^T
-std::pair<Tensor, OptTensor> lin_fwd(const Tensor& x, const Lin& l, const OptTensor& status) {
+// y = x W^T (+ LoRA) (+ residual, added in the GEMM's epilogue); returns (y, t) with t = s x A^T
+std::pair<Tensor, OptTensor> lin_fwd(const Tensor& x, const Lin& l, const OptTensor& status, const OptTensor& residual = std::nullopt) {
   const int64_t M = x.size(0), K = x.size(1), N = l.W.size(0);
   auto y = torch::empty({M, N}, x.options());
   if (!l.A.has_value()) {
-    gemm_raw(0, x, false, l.W, false, y, M, N, K, std::nullopt, std::nullopt, false, 0, false, 1.0, status);
+    gemm_raw(0, x, false, l.W, false, y, M, N, K, std::nullopt, std::nullopt, false, 0, false, 1.0, status, residual);
     return {y, std::nullopt};
   }
   const int64_t r = l.A->size(0);
@@ -489,7 +513,7 @@ std::pair<Tensor, OptTensor> lin_fwd(const Tensor& x, const Lin& l, const OptTen
     t = torch::empty({M, r}, x.options());
     gemm_raw(0, x, false, *l.A, false, t, M, r, K, std::nullopt, std::nullopt, false, 0, false, l.s, status);
   }
-  gemm_raw(0, x, false, l.W, false, y, M, N, K, t, l.B, false, r, false, 1.0, status);
+  gemm_raw(0, x, false, l.W, false, y, M, N, K, t, l.B, false, r, false, 1.0, status, residual);
   return {y, t};
 }
 // dx (+)= dy W (+ LoRA), and the requested parameter gradients
@@ -580,8 +604,7 @@ std::vector<Tensor> attention_block_fwd(const Tensor& x, const std::vector<Tenso
   Tensor v3 = v.view({T, Hkv, d});
   auto at = attention_fwd(qr, kr, v3, cu_seqlens, max_seqlen, 1.0 / std::sqrt((double)d));
   Tensor o = at[0], lse = at[1];
-  auto [out, to] = lin_fwd(o.view({T, Hq * d}), lo, status);
-  out.add_(x);
+  auto [out, to] = lin_fwd(o.view({T, Hq * d}), lo, status, x.is_contiguous() ? OptTensor(x) : OptTensor(x.contiguous()));   // + x in the epilogue
   Tensor none = torch::empty({0}, x.options());
   return {out, rstd, xn, qr, kr, v3, o, lse, tq.value_or(none), tk.value_or(none), tv.value_or(none), to.value_or(none)};
 }
@@ -621,10 +644,9 @@ std::vector<Tensor> attention_block_bwd(const Tensor& dy, const std::vector<Tens
   put(iq, lq, lin_bwd(dq, xn, lq, tq, nd(iq, 0), lq.A.has_value() && nd(iq, 1), lq.A.has_value() && nd(iq, 2), d_xn, false, status));
   put(ik, lk, lin_bwd(dk, xn, lk, tk, nd(ik, 0), lk.A.has_value() && nd(ik, 1), lk.A.has_value() && nd(ik, 2), d_xn, true, status));
   put(iv, lv, lin_bwd(dv, xn, lv, tv, nd(iv, 0), lv.A.has_value() && nd(iv, 1), lv.A.has_value() && nd(iv, 2), d_xn, true, status));
-  auto rb = rmsnorm_bwd(x, params[0], d_xn, rstd);
+  auto rb = rmsnorm_bwd(x, params[0], d_xn, rstd, dyc);     // + dy: the residual connection's gradient
   Tensor dx = rb[0];
-  if (needs[0]) grads[0] = rb[1].sum(0).to(params[0].scalar_type());
-  dx.add_(dyc);
+  if (needs[0]) grads[0] = rmsnorm_dw(rb[1], params[0]);
   std::vector<Tensor> out;
   out.reserve(1 + grads.size());
   out.push_back(dx);
@@ -734,8 +756,7 @@ std::vector<Tensor> moe_block_fwd(const Tensor& x, const Tensor& ln_w, const Ten
     ys = ep[5].narrow(0, 0, n_slots);
     if (keep) ys = ys.clone();
   }
-  out = combine_rows(ys, plan[2], wts, top_k);
-  out.add_(x);
+  out = combine_rows(ys, plan[2], wts, top_k, x.is_contiguous() ? OptTensor(x) : OptTensor(x.contiguous()));   // + x
   if (ckpt == 1 && !grad_mode)
     return {out, plan[0], wts, idx, ys, plan[1], plan[2], plan[3], meta_c, rr, rp, te, xg, expert_sorted, offs};
   if (!grad_mode) return {out, plan[0]};
@@ -747,7 +768,7 @@ std::vector<Tensor> moe_block_fwd(const Tensor& x, const Tensor& ln_w, const Ten
 std::vector<Tensor> moe_block_bwd(const Tensor& dy, const std::vector<Tensor>& state, const Tensor& x, const Tensor& ln_w, const Tensor& Wr,
                                   const Tensor& w1, const Tensor& w2, const Tensor& w3, const std::vector<Tensor>& wg, double wscale,
                                   int64_t top_k, int64_t E, const std::vector<int64_t>& layout, const std::vector<int64_t>& ep_ints,
-                                  const std::vector<Tensor>& ep, const Tensor& status_t) {
+                                  const std::vector<Tensor>& ep, const Tensor& status_t, bool need_ln, bool need_router) {
   c10::cuda::CUDAGuard guard(dy.device());
   OptTensor status = status_t;
   Tensor st = status_t;
@@ -794,18 +815,22 @@ std::vector<Tensor> moe_block_bwd(const Tensor& dy, const std::vector<Tensor>& s
     back = ep[5].narrow(0, 0, n_slots);
   }
   Tensor dxn = combine_rows(back, dest_row, NONE, top_k);
-  auto rb = router_bwd(xn, Wr, idx, dwts, NONE, true);
-  dxn.add_(rb[0]);
-  auto nb = rmsnorm_bwd(x, ln_w, dxn, rstd);
+  auto rb = router_bwd(xn, Wr, idx, dwts, NONE, true, dxn);     // adds the router's input gradient to dxn
+  auto nb = rmsnorm_bwd(x, ln_w, dxn, rstd, dyc);               // + dy: the residual connection's gradient
   Tensor dx = nb[0];
-  dx.add_(dyc);
-  return {dx, nb[1].sum(0).to(ln_w.scalar_type()), rb[1].to(Wr.scalar_type())};
+  Tensor none = torch::empty({0}, x.options());
+  return {dx, need_ln ? rmsnorm_dw(nb[1], ln_w) : none, need_router ? rb[1].to(Wr.scalar_type()) : none};
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  m.def("gemm", &gemm);
+  m.def("gemm", &gemm, py::arg("mode"), py::arg("A"), py::arg("a_mn"), py::arg("B"), py::arg("b_mn"), py::arg("C"), py::arg("M"), py::arg("N"), py::arg("K"),
+        py::arg("G"), py::arg("offsets"), py::arg("capacity_rows"), py::arg("B2"), py::arg("A_l"), py::arg("a_mn_l"), py::arg("B_l"), py::arg("B2_l"),
+        py::arg("b_mn_l"), py::arg("K_l"), py::arg("C2"), py::arg("C3"), py::arg("accumulate"), py::arg("alpha"), py::arg("status"), py::arg("tile_ready"),
+        py::arg("tile_expected"), py::arg("row_dest_rank"), py::arg("row_dest_row"), py::arg("peer_out"), py::arg("peer_arrive"),
+        py::arg("residual") = py::none());
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
-  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("x"), py::arg("w"), py::arg("dy"), py::arg("rstd"), py::arg("dres") = py::none());
+  m.def("rmsnorm_dw", &rmsnorm_dw);
   m.def("rope", &rope);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd, py::arg("g"), py::arg("u"), py::arg("dh"), py::arg("offsets") = py::none());
@@ -830,10 +855,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sumsq", &sumsq);
   m.def("axpby", &axpby);
   m.def("router_fwd", &router_fwd);
-  m.def("router_bwd", &router_bwd);
+  m.def("router_bwd", &router_bwd, py::arg("x"), py::arg("w"), py::arg("idx"), py::arg("dweights"), py::arg("dscores"), py::arg("normalize"),
+        py::arg("dx_accum") = py::none());
   m.def("make_plan", &make_plan);
   m.def("gather_rows", &gather_rows);
-  m.def("combine_rows", &combine_rows);
+  m.def("combine_rows", &combine_rows, py::arg("y"), py::arg("dest_row"), py::arg("weights"), py::arg("top_k"), py::arg("residual") = py::none());
   m.def("combine_wgrad", &combine_wgrad);
   m.def("attention_fwd", &attention_fwd);
   m.def("attention_bwd", &attention_bwd);

@@ -81,10 +81,11 @@ __global__ void rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __res
   }
 }
 
-// dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x));  dw partial sums per CTA (CTA loops over rows)
+// dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x)) (+ dres, the gradient that reaches x past the norm through the
+// residual connection);  dw partial sums per CTA (CTA loops over rows)
 __global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ dy,
-                                   const float* __restrict__ rstd, bf16* __restrict__ dx, float* __restrict__ dw_partial,
-                                   int rows, int cols) {
+                                   const float* __restrict__ rstd, const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                                   float* __restrict__ dw_partial, int rows, int cols) {
   __shared__ float red[32];
   const int nv = cols / 8;
   // each thread owns vectors i = threadIdx.x + k*blockDim.x, k < 8 (cols <= 8*8*blockDim.x)
@@ -98,6 +99,7 @@ __global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __res
     const uint4* xr = reinterpret_cast<const uint4*>(x + (long long)row * cols);
     const uint4* dr = reinterpret_cast<const uint4*>(dy + (long long)row * cols);
     uint4* ox = reinterpret_cast<uint4*>(dx + (long long)row * cols);
+    const uint4* rr = dres != nullptr ? reinterpret_cast<const uint4*>(dres + (long long)row * cols) : nullptr;
     const float r = rstd[row];
     float dot = 0.f;
     for (int i = threadIdx.x; i < nv; i += blockDim.x) {
@@ -115,6 +117,11 @@ __global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __res
         o[j] = r * (df[j] * wf[j] - xf[j] * c);
         if (k < 8) acc[k][j] += df[j] * xf[j] * r;
       }
+      if (rr != nullptr) {
+        float rf[8]; unpack8(rr[i], rf);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += rf[j];
+      }
       ox[i] = pack8(o);
     }
   }
@@ -124,6 +131,17 @@ __global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __res
 #pragma unroll
     for (int j = 0; j < 8; ++j) dst[j] = acc[k][j];
   }
+}
+
+// dw[c] = sum over the partial rows (+ cast): finishes the weight gradient of rmsnorm_bwd_kernel in one launch
+__global__ void rmsnorm_dw_finalize_kernel(const float* __restrict__ partial, int n_partial, int cols, bf16* __restrict__ dw_bf16,
+                                           float* __restrict__ dw_f32) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int r = 0; r < n_partial; ++r) s += partial[(long long)r * cols + c];
+  if (dw_bf16 != nullptr) dw_bf16[c] = __float2bfloat16(s);
+  if (dw_f32 != nullptr) dw_f32[c] = s;
 }
 
 // ------------------------------------------------------------------------------------ RoPE
@@ -400,10 +418,16 @@ extern "C" int mdt_rmsnorm_fwd(const void* x, const void* w, void* y, float* rst
   MDT_CHECK_LAUNCH();
   return 0;
 }
-extern "C" int mdt_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx, float* dw_partial,
-                               int rows, int cols, int n_partial, cudaStream_t s) {
+extern "C" int mdt_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, const void* dres, void* dx,
+                               float* dw_partial, int rows, int cols, int n_partial, cudaStream_t s) {
   if (cols % 8 != 0 || cols > 8 * 8 * 256) return -1;
-  rmsnorm_bwd_kernel<<<n_partial, 256, 0, s>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, (bf16*)dx, dw_partial, rows, cols);
+  rmsnorm_bwd_kernel<<<n_partial, 256, 0, s>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, (const bf16*)dres, (bf16*)dx, dw_partial,
+                                              rows, cols);
+  MDT_CHECK_LAUNCH();
+  return 0;
+}
+extern "C" int mdt_rmsnorm_dw_finalize(const float* dw_partial, int n_partial, int cols, void* dw_bf16, float* dw_f32, cudaStream_t s) {
+  rmsnorm_dw_finalize_kernel<<<(cols + 255) / 256, 256, 0, s>>>(dw_partial, n_partial, cols, (bf16*)dw_bf16, dw_f32);
   MDT_CHECK_LAUNCH();
   return 0;
 }

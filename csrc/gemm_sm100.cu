@@ -47,7 +47,7 @@ struct GemmParams {
   int M, N, K, K_l, G, mode;
   int a_mn, b_mn, a_mn_l, b_mn_l, dual;
   const int* offsets;
-  void* C; void* C2; void* C3;
+  void* C; void* C2; void* C3; const void* R;
   long long ldc, c_group_stride;
   int c_fp32, accumulate;
   float alpha;
@@ -135,7 +135,16 @@ __host__ __device__ __forceinline__ bool get_tile(const GemmParams& p, int t, Ti
   return true;
 }
 
-__device__ __forceinline__ void store8(void* C, long long idx, const float (&v)[8], int c_fp32, int accumulate) {
+__device__ __forceinline__ void store8(void* C, long long idx, const float (&v0)[8], int c_fp32, int accumulate, const void* R = nullptr) {
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = v0[i];
+  if (R != nullptr) {   // residual connection: a bf16 matrix laid out like C
+    const uint4 rv = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(R) + idx);
+    const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(r2[i]); v[2 * i] += f.x; v[2 * i + 1] += f.y; }
+  }
   if (c_fp32) {
     float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(C) + idx);
     float4 a = make_float4(v[0], v[1], v[2], v[3]), b = make_float4(v[4], v[5], v[6], v[7]);
@@ -379,7 +388,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
                 float o[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(r[v * 8 + i]) * p.alpha;
-                store8(Cout, base + col, o, p.c_fp32, p.accumulate);
+                store8(Cout, base + col, o, p.c_fp32, p.accumulate, p.R);
               }
             }
           }
@@ -689,7 +698,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1) gem
                 float o[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(r[v * 8 + i]) * p.alpha;
-                store8(Cout, base + col, o, p.c_fp32, p.accumulate);
+                store8(Cout, base + col, o, p.c_fp32, p.accumulate, p.R);
               }
             }
           }
@@ -947,7 +956,7 @@ __global__ void __launch_bounds__(TALL_THREADS, 1) gemm_sm100_tall_kernel(const 
       const uint32_t taddr = tmem_base + h * BN + ((uint32_t)(q * 32) << 16);
       // bf16 results without accumulation go out through the coalescing stage; the row this lane stores in pass i
       // is row i*8 + lane/4 of the warp's 32, whose address and validity come from the lane that owns it
-      const bool fast = !p.c_fp32 && !p.accumulate;
+      const bool fast = !p.c_fp32 && !p.accumulate && p.R == nullptr;
       uint8_t* stage = store_stage + (warp - 2) * 2048;
       unsigned long long rptr[4] = {0, 0, 0, 0};
       unsigned okm = 0;
@@ -1024,7 +1033,7 @@ __global__ void __launch_bounds__(TALL_THREADS, 1) gemm_sm100_tall_kernel(const 
                 float o[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(r[v * 8 + i]) * p.alpha;
-                store8(Cout, base + col, o, p.c_fp32, p.accumulate);
+                store8(Cout, base + col, o, p.c_fp32, p.accumulate, p.R);
               }
             }
           }
@@ -1277,6 +1286,8 @@ extern "C" int mdt_gemm(const MdtGemmDesc* d, cudaStream_t stream) {
   if (p.mode == 2) { p.rdy_b.ready = nullptr; p.rdy_b2.ready = nullptr; p.rdy_bl.ready = nullptr; }
   p.b_rows = d->b_rows; p.ldb = d->ldb; p.b_group_stride = d->b_group_stride;
   p.bl_rows = d->bl_rows; p.ldb_l = d->ldb_l; p.bl_group_stride = d->bl_group_stride;
+  p.R = d->R;
+  if (p.R != nullptr && (p.dual || p.mode == 2 || p.row_dest_rank != nullptr || (reinterpret_cast<uintptr_t>(p.R) & 15))) return -13;
   if (p.row_dest_rank != nullptr && (p.dual || p.c_fp32 || p.accumulate || p.mode == 2)) return -12;
   if (p.N % 8 != 0 || p.ldc % 8 != 0) return -10;
   if (p.dual && (p.b_mn != 0 || p.c_fp32 || p.accumulate)) return -11;

@@ -320,14 +320,16 @@ __global__ void gather_rows_kernel(const bf16* __restrict__ x, const int* __rest
 }
 
 // out[t, :] = sum_c weights[t, c] * y[dest_row[t*k + c], :]
+// (+ residual[t, :] when given)
 __global__ void combine_rows_kernel(const bf16* __restrict__ y, const int* __restrict__ dest_row, const bf16* __restrict__ weights,
-                                    bf16* __restrict__ out, int cols, int top_k) {
+                                    const bf16* __restrict__ residual, bf16* __restrict__ out, int cols, int top_k) {
   const int t = blockIdx.x;
   uint4* dst = reinterpret_cast<uint4*>(out + (long long)t * cols);
   for (int i = threadIdx.x; i < cols / 8; i += blockDim.x) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    if (residual != nullptr) unpack8r(reinterpret_cast<const uint4*>(residual + (long long)t * cols)[i], acc);
     for (int c = 0; c < top_k; ++c) {
       const int row = dest_row[(long long)t * top_k + c];
       const float wv = weights != nullptr ? __bfloat162float(weights[(long long)t * top_k + c]) : 1.f;
@@ -455,11 +457,11 @@ extern "C" int mdt_gather_rows(const void* x, const int* src_slot, const int* pa
   MDT_RT_CHECK();
   return 0;
 }
-extern "C" int mdt_combine_rows(const void* y, const int* dest_row, const void* weights, void* out, int tokens, int cols, int top_k,
-                                cudaStream_t s) {
+extern "C" int mdt_combine_rows(const void* y, const int* dest_row, const void* weights, const void* residual, void* out, int tokens, int cols,
+                                int top_k, cudaStream_t s) {
   if (cols % 8 != 0) return -1;
   if (tokens == 0) return 0;
-  combine_rows_kernel<<<tokens, 128, 0, s>>>((const bf16*)y, dest_row, (const bf16*)weights, (bf16*)out, cols, top_k);
+  combine_rows_kernel<<<tokens, 128, 0, s>>>((const bf16*)y, dest_row, (const bf16*)weights, (const bf16*)residual, (bf16*)out, cols, top_k);
   MDT_RT_CHECK();
   return 0;
 }

@@ -40,25 +40,26 @@ def launch_count() -> int:
 
 
 def _gemm(mode, A, a_mn, B, b_mn, C, M, N, K, G=1, offsets=None, capacity=0, B2=None, A_l=None, a_mn_l=False,
-          B_l=None, B2_l=None, b_mn_l=False, K_l=0, C2=None, C3=None, accumulate=False, alpha=1.0, wait=None, scatter=None):
+          B_l=None, B2_l=None, b_mn_l=False, K_l=0, C2=None, C3=None, accumulate=False, alpha=1.0, wait=None, scatter=None,
+          residual=None):
     """wait = (tile_ready, tile_expected): A rows arrive from peers, tile by tile.  scatter = (row_rank, row_pos,
     peer_out table, peer_arrive table): result rows are stored into peers' buffers instead of C."""
     w0, w1 = wait if wait is not None else (None, None)
     s0, s1, s2, s3 = scatter if scatter is not None else (None, None, None, None)
     ext.gemm(mode, A, a_mn, B, b_mn, C, M, N, K, G, offsets, capacity, B2, A_l, a_mn_l, B_l, B2_l, b_mn_l, K_l,
-             C2, C3, accumulate, alpha, status_tensor(A.device), w0, w1, s0, s1, s2, s3)
+             C2, C3, accumulate, alpha, status_tensor(A.device), w0, w1, s0, s1, s2, s3, residual)
     return C
 
 
-def mm_nt(x, w, out=None, alpha=1.0, lora=None):
-    """x [M,K] @ w[N,K]^T (+ LoRA segment: (A_l [M,r], B_l [N,r]))."""
+def mm_nt(x, w, out=None, alpha=1.0, lora=None, residual=None):
+    """x [M,K] @ w[N,K]^T (+ LoRA segment: (A_l [M,r], B_l [N,r])) (+ residual [M,N], added in the epilogue)."""
     M, K = x.shape
     N = w.shape[0]
     out = out if out is not None else torch.empty(M, N, dtype=x.dtype, device=x.device)
     if lora is None:
-        return _gemm(0, x, False, w, False, out, M, N, K, alpha=alpha)
+        return _gemm(0, x, False, w, False, out, M, N, K, alpha=alpha, residual=residual)
     t, b = lora
-    return _gemm(0, x, False, w, False, out, M, N, K, A_l=t, B_l=b, b_mn_l=False, K_l=t.shape[1], alpha=alpha)
+    return _gemm(0, x, False, w, False, out, M, N, K, A_l=t, B_l=b, b_mn_l=False, K_l=t.shape[1], alpha=alpha, residual=residual)
 
 
 def mm_nn(x, w, out=None, alpha=1.0, accumulate=False, lora=None):
@@ -416,7 +417,7 @@ class _RMSNorm(torch.autograd.Function):
     def backward(ctx, dy):
         x, w, rstd = ctx.saved_tensors
         dx, dwp = ext.rmsnorm_bwd(x, w, dy.contiguous(), rstd)
-        return dx, dwp.sum(0).to(w.dtype), None
+        return dx, ext.rmsnorm_dw(dwp, w), None
 
 
 def rmsnorm(x, weight, eps):

@@ -19,11 +19,11 @@ ext = C.ext
 GEMM_FUSION = os.environ.get("MDT_EP_GEMM_FUSION", "1") != "0"
 
 
-def _lin_fwd(x2, W, A, B, s):
+def _lin_fwd(x2, W, A, B, s, residual=None):
     if A is None:
-        return C.mm_nt(x2, W), None
+        return C.mm_nt(x2, W, residual=residual), None
     t = C.mm_nt(x2, A, alpha=s)                       # [M, r] = s * x A^T
-    return C.mm_nt(x2, W, lora=(t, B)), t
+    return C.mm_nt(x2, W, lora=(t, B), residual=residual), t
 
 
 def _lin_bwd(dy2, xin, W, A, B, s, t, need_w, need_a, need_b, dx_out=None, accumulate=False):
@@ -87,8 +87,7 @@ class _AttentionBlock(torch.autograd.Function):
         scale = float(d) ** -0.5
         o, lse = ext.attention_fwd(qr, kr, v3, cu, max_seqlen, scale)
         o2 = o.view(T, Hq * d)
-        out, to = _lin_fwd(o2, *lins[3][:4])
-        out.add_(x2)
+        out, to = _lin_fwd(o2, *lins[3][:4], residual=x2)      # + x in the GEMM's epilogue
         if any(ctx.needs_input_grad):
             ctx.meta, ctx.n_params, ctx.lin_index = meta, len(params), [l[4] for l in lins]
             ctx.save_for_backward(x2, rstd, xn, qr, kr, v3, o, lse, tq, tk, tv, to, *params)
@@ -130,10 +129,9 @@ class _AttentionBlock(torch.autograd.Function):
         d_xn = run(0, dq, xn, tq)
         run(1, dk, xn, tk, dx_out=d_xn, accumulate=True)
         run(2, dv.view(T, Hkv * d), xn, tv, dx_out=d_xn, accumulate=True)
-        dx, dwp = ext.rmsnorm_bwd(x2, ln_w, d_xn, rstd)
+        dx, dwp = ext.rmsnorm_bwd(x2, ln_w, d_xn, rstd, dy2)   # + dy: the residual connection's gradient
         if need[2]:
-            grads[0] = dwp.sum(0).to(ln_w.dtype)
-        dx.add_(dy2)
+            grads[0] = ext.rmsnorm_dw(dwp, ln_w)
         return (dx, None) + tuple(grads)
 
 
@@ -210,7 +208,7 @@ class _MoEBlock(torch.autograd.Function):
             xg = ext.gather_rows(xn, plan.src_slot, plan.padded_offsets, E, None, k)
             yg = C._GroupedSwiGLUMLP.forward(mctx, xg, w1, w2, w3, plan, lora, float(ws), wgrad_out, ids, *lora_tensors)
             ys = yg
-            comb = ext.combine_rows(yg, plan.dest_row, wts, k)
+            comb = ext.combine_rows(yg, plan.dest_row, wts, k, x2)      # + x
             eng = meta_c = expert_sorted = None
         else:
             if ex._fused is None:
@@ -244,8 +242,7 @@ class _MoEBlock(torch.autograd.Function):
                 yg = C._GroupedSwiGLUMLP.forward(mctx, xr, w1, w2, w3, rplan, lora, float(ws), wgrad_out, ids, *lora_tensors)
                 ys = eng.combine(yg, meta_c, par, n_slots, clone=grad_mode)
             ext.gemm_rows_hint(0)
-            comb = ext.combine_rows(ys, plan.dest_row, wts, k)
-        comb.add_(x2)
+            comb = ext.combine_rows(ys, plan.dest_row, wts, k, x2)      # + x
         if grad_mode:
             ctx.layer, ctx.plan, ctx.mctx, ctx.eng, ctx.meta_c, ctx.n_params = layer, plan, mctx, eng, meta_c, len(params)
             ctx.save_for_backward(x2, rstd, xn, wts, idx, ys, expert_sorted, ln_w, Wr)
@@ -285,13 +282,12 @@ class _MoEBlock(torch.autograd.Function):
                 back = eng.combine(g[0].contiguous(), meta_c, par, n_slots, clone=False)
             ext.gemm_rows_hint(0)
             dxn = ext.combine_rows(back, plan.dest_row, None, k)
-        dxr, dWr = ext.router_bwd(xn, Wr.contiguous(), idx, dwts, None, True)
-        dxn.add_(dxr)
-        dx, dwp = ext.rmsnorm_bwd(x2, ln_w, dxn, rstd)
-        dx.add_(dy2)
+        dxn = dxn.contiguous()
+        _, dWr = ext.router_bwd(xn, Wr.contiguous(), idx, dwts, None, True, dxn)     # adds the router's input gradient to dxn
+        dx, dwp = ext.rmsnorm_bwd(x2, ln_w, dxn, rstd, dy2)                          # + dy: the residual connection's gradient
         grads = [None] * ctx.n_params
         if need[2]:
-            grads[0] = dwp.sum(0).to(ln_w.dtype)
+            grads[0] = ext.rmsnorm_dw(dwp, ln_w)
         if need[3]:
             grads[1] = dWr.to(Wr.dtype)
         # the MLP works on [E, F, H] views of the [E*F, H] parameters
@@ -366,9 +362,9 @@ class _MoEBlockNative(torch.autograd.Function):
         if eng is not None:
             layout, ints, tens = _MoEBlockNative._ep_args(eng, eng.next_phase(), x2.shape[1])
         wg = list(ctx.wgrad_out) if ctx.wgrad_out is not None else []
-        dx, dln, dWr = ext.moe_block_bwd(dy, state, x2, ln_w, Wr.contiguous(), w1, w2, w3, wg, ctx.ws, a.moe_top_k, a.moe_num_experts,
-                                         layout, ints, tens, C.status_tensor(dy.device))
         need = ctx.needs_input_grad
+        dx, dln, dWr = ext.moe_block_bwd(dy, state, x2, ln_w, Wr.contiguous(), w1, w2, w3, wg, ctx.ws, a.moe_top_k, a.moe_num_experts,
+                                         layout, ints, tens, C.status_tensor(dy.device), bool(need[2]), bool(need[3]))
         return dx, None, (dln if need[2] else None), (dWr if need[3] else None), None, None, None
 
 

@@ -552,3 +552,49 @@ def test_group_bwd_ab_direct_products_match_fp32():
     ids = torch.repeat_interleave(torch.arange(E, device=DEV), torch.tensor(counts, device=DEV))
     pbi, eo = padded_block_indices(ids, E)
     assert pbi.tolist() == [0, 128, 256, 300, 428] and eo.tolist() == [300, 300, 512]
+
+
+def test_residual_connections_fused_into_their_producers(ops):
+    """x + f(x) without a separate add: the GEMM epilogue, the gate-weighted combine and the RMSNorm backward take the
+    residual (or its gradient) as an extra input; the router backward adds into an existing gradient."""
+    torch.manual_seed(31)
+    ext = ops.ext
+    M, K, N = 333, 512, 768
+    x, w, res = _rand(M, K), _rand(N, K, scale=0.05), _rand(M, N)
+    for policy in (0, 4):                                   # 128-row tiles and the tall kernel (coalescing epilogue off)
+        prev = ext.gemm_set_pair_policy(policy)
+        try:
+            got = ops.mm_nt(x, w, residual=res)
+        finally:
+            ext.gemm_set_pair_policy(prev)
+        _close(got, x.float() @ w.float().t() + res.float(), name=f"gemm + residual (policy {policy})")
+    # combine
+    T, k, H = 200, 2, 256
+    y = _rand(T * k + 56, H)
+    dest = torch.randperm(T * k + 56, device=DEV)[:T * k].int()
+    wts = torch.rand(T, k, device=DEV).to(torch.bfloat16)
+    r2 = _rand(T, H)
+    got = ext.combine_rows(y, dest, wts, k, r2)
+    want = (y.float()[dest.long()].view(T, k, H) * wts.float()[:, :, None]).sum(1) + r2.float()
+    _close(got, want, name="combine + residual")
+    # rmsnorm backward + residual gradient, and the weight gradient finished in one launch
+    R, C = 300, 512
+    xx, ww, dy, dres = _rand(R, C), (1 + 0.1 * torch.randn(C, device=DEV)).to(torch.bfloat16), _rand(R, C), _rand(R, C)
+    _, rstd = ext.rmsnorm_fwd(xx, ww, 1e-5)
+    dx, dwp = ext.rmsnorm_bwd(xx, ww, dy, rstd, dres)
+    xf = xx.float().requires_grad_(True)
+    wf = ww.float().requires_grad_(True)
+    yf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
+    yf.backward(dy.float())
+    _close(dx, xf.grad + dres.float(), name="rmsnorm dx + residual gradient")
+    _close(ext.rmsnorm_dw(dwp, ww)[None], wf.grad[None], 3e-2, name="rmsnorm dw")
+    # router backward accumulating into an existing gradient
+    Tk, Hh, E = 150, 256, 8
+    xr, wr = _rand(Tk, Hh), _rand(E, Hh, scale=0.1)
+    _, _, idx = ext.router_fwd(xr, wr, 2, True)
+    dwts = _rand(Tk, 2)
+    dx_plain, _ = ext.router_bwd(xr, wr, idx, dwts, None, True)
+    base = _rand(Tk, Hh)
+    acc = base.clone()
+    ext.router_bwd(xr, wr, idx, dwts, None, True, acc)
+    _close(acc, base.float() + dx_plain.float(), name="router dx accumulate")
