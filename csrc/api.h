@@ -104,8 +104,9 @@ int mdt_sumsq(const void* x, long long n, int fp32, float* out_accum, cudaStream
 int mdt_axpby(void* y, const void* x, long long n, float a, float b, int y_fp32, int x_fp32, cudaStream_t s);
 
 // ---- router and permutation (router.cu) -----------------------------------------------------------
+// stats (optional, fp32 [2 * experts], accumulated into): per-expert slot counts, then per-expert sums of the scores
 int mdt_router_fwd(const void* x, const void* w, void* scores, void* weights, int* idx, int tokens, int hidden,
-                   int experts, int top_k, int normalize, cudaStream_t s);
+                   int experts, int top_k, int normalize, float* stats, cudaStream_t s);
 int mdt_router_bwd(const void* x, const void* w, const void* scores, const void* weights, const int* idx,
                    const void* dweights, const void* dscores, void* dx, float* dw, int tokens, int hidden, int experts,
                    int top_k, int normalize, int accumulate_dx, cudaStream_t s);

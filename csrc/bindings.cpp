@@ -5,6 +5,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include <mutex>
 #include <optional>
 #include <vector>
@@ -19,6 +21,19 @@ extern "C" long long mdt_comm_launch_count();
 
 using torch::Tensor;
 typedef std::optional<Tensor> OptTensor;
+
+// NVTX range around a phase of the C++-issued blocks (router / dispatch / experts / combine ...); on with MDT_NVTX=1
+struct Phase {
+  static bool enabled() { static const bool on = []() { const char* e = getenv("MDT_NVTX"); return e != nullptr && e[0] == '1'; }(); return on; }
+  explicit Phase(const char* name) { if (enabled()) nvtxRangePushA(name); }
+  ~Phase() { if (enabled()) nvtxRangePop(); }
+  // ends the current range of a sequence and begins the next one (nullptr: only ends)
+  static void next(const char* name, bool first = false) {
+    if (!enabled()) return;
+    if (!first) nvtxRangePop();
+    if (name != nullptr) nvtxRangePushA(name);
+  }
+};
 
 static cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 static void check(int rc, const char* what) { TORCH_CHECK(rc == 0, what, " failed with code ", rc); }
@@ -247,7 +262,8 @@ void axpby(Tensor& y, const Tensor& x, double a, double b) {
   check(mdt_axpby(y.data_ptr(), x.data_ptr(), x.numel(), (float)a, (float)b, y.scalar_type() == at::kFloat, x.scalar_type() == at::kFloat, cur_stream()), "axpby");
 }
 
-std::vector<Tensor> router_fwd(const Tensor& x, const Tensor& w, int64_t top_k, bool normalize) {
+// with_stats: a fourth result, fp32 [2 * E]: per-expert slot counts followed by per-expert sums of the scores
+std::vector<Tensor> router_fwd(const Tensor& x, const Tensor& w, int64_t top_k, bool normalize, bool with_stats = false) {
   CHECK_BF16(x); CHECK_BF16(w);
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.is_contiguous() && w.is_contiguous());
@@ -255,7 +271,11 @@ std::vector<Tensor> router_fwd(const Tensor& x, const Tensor& w, int64_t top_k, 
   auto scores = torch::empty({T, E}, x.options());
   auto weights = torch::empty({T, top_k}, x.options());
   auto idx = torch::empty({T, top_k}, x.options().dtype(at::kInt));
-  check(mdt_router_fwd(x.data_ptr(), w.data_ptr(), scores.data_ptr(), weights.data_ptr(), idx.data_ptr<int>(), T, H, E, (int)top_k, normalize, cur_stream()), "router_fwd");
+  Tensor stats;
+  if (with_stats) stats = torch::zeros({2 * (int64_t)E}, x.options().dtype(at::kFloat));
+  check(mdt_router_fwd(x.data_ptr(), w.data_ptr(), scores.data_ptr(), weights.data_ptr(), idx.data_ptr<int>(), T, H, E, (int)top_k, normalize,
+                       with_stats ? stats.data_ptr<float>() : nullptr, cur_stream()), "router_fwd");
+  if (with_stats) return {scores, weights, idx, stats};
   return {scores, weights, idx};
 }
 // dx_accum (optional, bf16 [T, H]): the input gradient is added to it instead of written to a new tensor
@@ -556,6 +576,7 @@ std::vector<Tensor> attention_block_fwd(const Tensor& x, const std::vector<Tenso
                                         const Tensor& positions, const Tensor& cu_seqlens, int64_t max_seqlen, double eps, double theta,
                                         int64_t Hq, int64_t Hkv, int64_t d, const Tensor& status_t) {
   c10::cuda::CUDAGuard guard(x.device());
+  Phase ph("attention.forward");
   OptTensor status = status_t;
   const int64_t T = x.size(0);
   size_t i = 1;
@@ -615,6 +636,7 @@ std::vector<Tensor> attention_block_bwd(const Tensor& dy, const std::vector<Tens
                                         const Tensor& cu_seqlens, int64_t max_seqlen, double theta, int64_t Hq, int64_t Hkv, int64_t d,
                                         const Tensor& status_t) {
   c10::cuda::CUDAGuard guard(dy.device());
+  Phase ph("attention.backward");
   OptTensor status = status_t;
   const Tensor &x = saved[0], &rstd = saved[1], &xn = saved[2], &qr = saved[3], &kr = saved[4], &v3 = saved[5], &o = saved[6], &lse = saved[7];
   auto opt = [](const Tensor& t) -> OptTensor { return t.numel() ? OptTensor(t) : std::nullopt; };
@@ -706,10 +728,14 @@ std::vector<Tensor> moe_block_fwd(const Tensor& x, const Tensor& ln_w, const Ten
   const bool is_ep = !ep.empty();
   const bool keep = grad_mode || ckpt == 1;      // tensors of the exchange outlive this call
   RowsHint rows_hint(is_ep ? T * top_k : 0);   // balanced routing: a rank receives about as many rows as it sends
-  auto nr = rmsnorm_fwd(x, ln_w, eps);
-  Tensor xn = nr[0], rstd = nr[1];
-  auto rt = router_fwd(xn, Wr, top_k, true);
-  Tensor wts = rt[1], idx = rt[2];
+  Tensor xn, rstd, wts, idx;
+  {
+    Phase ph("moe.router");
+    auto nr = rmsnorm_fwd(x, ln_w, eps);
+    xn = nr[0]; rstd = nr[1];
+    auto rt = router_fwd(xn, Wr, top_k, true);
+    wts = rt[1]; idx = rt[2];
+  }
   Tensor none = torch::empty({0}, x.options());
   Tensor nonei = torch::empty({0}, idx.options());
   Tensor xg, offs, meta_c = nonei, rr = nonei, rp = nonei, te = nonei, expert_sorted = nonei, ys, out;
@@ -717,6 +743,7 @@ std::vector<Tensor> moe_block_fwd(const Tensor& x, const Tensor& ln_w, const Ten
   std::vector<Tensor> plan;
   OptTensor w0, w1o, s0, s1, s2, s3;
   const int64_t n_slots = idx.numel();
+  Phase::next("moe.dispatch", true);
   if (!is_ep) {
     const int64_t c = std::max<int64_t>(128, ((n_slots + E * 127) / 128) * 128);
     plan = make_plan(idx.view({-1}), E, 128, c);
@@ -741,6 +768,7 @@ std::vector<Tensor> moe_block_fwd(const Tensor& x, const Tensor& ln_w, const Ten
     cap = L.capacity_rows;
     w0 = ep[3]; w1o = te; s0 = rr; s1 = rp; s2 = ep[1]; s3 = ep[2];
   }
+  Phase::next("moe.experts");
   const int64_t R = xg.size(0);
   Tensor h = torch::empty({R, F}, x.options());
   OptTensor g, u;
@@ -749,6 +777,7 @@ std::vector<Tensor> moe_block_fwd(const Tensor& x, const Tensor& ln_w, const Ten
   if (is_ep && keep) xg = clone_used_rows(xg, offs);   // the receive buffer is reused by the next exchange
   Tensor y = torch::empty({R, H}, x.options());
   ggemm(1, h, false, w2, true, y, R, H, F, El, offs, cap, NONE, NONE, NONE, false, 0, NONE, NONE, false, 1.0, status, NONE, NONE, s0, s1, s2, s3);
+  Phase::next("moe.combine");
   if (!is_ep) {
     ys = y;
   } else {
@@ -757,6 +786,7 @@ std::vector<Tensor> moe_block_fwd(const Tensor& x, const Tensor& ln_w, const Ten
     if (keep) ys = ys.clone();
   }
   out = combine_rows(ys, plan[2], wts, top_k, x.is_contiguous() ? OptTensor(x) : OptTensor(x.contiguous()));   // + x
+  Phase::next(nullptr);
   if (ckpt == 1 && !grad_mode)
     return {out, plan[0], wts, idx, ys, plan[1], plan[2], plan[3], meta_c, rr, rp, te, xg, expert_sorted, offs};
   if (!grad_mode) return {out, plan[0]};
@@ -770,6 +800,7 @@ std::vector<Tensor> moe_block_bwd(const Tensor& dy, const std::vector<Tensor>& s
                                   int64_t top_k, int64_t E, const std::vector<int64_t>& layout, const std::vector<int64_t>& ep_ints,
                                   const std::vector<Tensor>& ep, const Tensor& status_t, bool need_ln, bool need_router) {
   c10::cuda::CUDAGuard guard(dy.device());
+  Phase ph("moe.backward");
   OptTensor status = status_t;
   Tensor st = status_t;
   const bool is_ep = !ep.empty();
@@ -854,7 +885,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw", &adamw);
   m.def("sumsq", &sumsq);
   m.def("axpby", &axpby);
-  m.def("router_fwd", &router_fwd);
+  m.def("router_fwd", &router_fwd, py::arg("x"), py::arg("w"), py::arg("top_k"), py::arg("normalize"), py::arg("with_stats") = false);
   m.def("router_bwd", &router_bwd, py::arg("x"), py::arg("w"), py::arg("idx"), py::arg("dweights"), py::arg("dscores"), py::arg("normalize"),
         py::arg("dx_accum") = py::none());
   m.def("make_plan", &make_plan);

@@ -112,13 +112,25 @@ __device__ __forceinline__ void softmax_topk(const float (&logit)[E_T], int expe
   if (!normalize) denom = 1.f;
 }
 
+// `stats` (optional, fp32 [2 * experts], accumulated into): the per-expert histogram of the selected experts
+// (stats[e] += number of (token, choice) slots routed to e) and the per-expert sums of the softmax scores
+// (stats[experts + e] += sum_t scores[t, e]): the f_e and P_e of the load-balancing loss E * sum_e f_e P_e, and the
+// tokens-per-expert counts, produced in the same pass that routes the tokens.
 template <int E_T>
 __global__ void router_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ scores,
                                   bf16* __restrict__ weights, int* __restrict__ idx, int tokens, int hidden, int experts,
-                                  int top_k, int normalize, int w_staged) {
+                                  int top_k, int normalize, int w_staged, float* __restrict__ stats) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
-  const bf16* wp = stage_router_weights(w, experts, hidden, w_staged);
+  __shared__ float s_stats[2 * MAX_E];
+  if (stats != nullptr) {
+    for (int i = threadIdx.x; i < 2 * experts; i += blockDim.x) s_stats[i] = 0.f;
+  }
+  const bf16* wp = stage_router_weights(w, experts, hidden, w_staged);   // (ends with a barrier when it stages)
+  if (stats != nullptr && !w_staged) __syncthreads();
+  float cnt[E_T], psum[E_T];
+#pragma unroll
+  for (int e = 0; e < E_T; ++e) { cnt[e] = 0.f; psum[e] = 0.f; }
   for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < tokens; t += gridDim.x * warps_per_block) {
     float logit[E_T], prob[E_T], wsel[MAX_K], denom;
     int sel[MAX_K];
@@ -131,7 +143,24 @@ __global__ void router_fwd_kernel(const bf16* __restrict__ x, const bf16* __rest
         weights[(long long)t * top_k + c] = __float2bfloat16(wsel[c] / denom);
         idx[(long long)t * top_k + c] = sel[c];
       }
+      if (stats != nullptr) {
+#pragma unroll
+        for (int e = 0; e < E_T; ++e) {
+          // the rounded score, so that the sum equals what a reader of `scores` would add up
+          if (e < experts) psum[e] += __bfloat162float(__float2bfloat16(prob[e]));
+          for (int c = 0; c < top_k; ++c) cnt[e] += (sel[c] == e) ? 1.f : 0.f;
+        }
+      }
     }
+  }
+  if (stats != nullptr) {
+    if (lane == 0) {
+#pragma unroll
+      for (int e = 0; e < E_T; ++e)
+        if (e < experts) { atomicAdd(&s_stats[e], cnt[e]); atomicAdd(&s_stats[experts + e], psum[e]); }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 2 * experts; i += blockDim.x) atomicAdd(stats + i, s_stats[i]);
   }
 }
 
@@ -389,7 +418,7 @@ static int router_smem_ok(const void* kernel, size_t bytes) {
 }
 
 extern "C" int mdt_router_fwd(const void* x, const void* w, void* scores, void* weights, int* idx, int tokens, int hidden,
-                              int experts, int top_k, int normalize, cudaStream_t s) {
+                              int experts, int top_k, int normalize, float* stats, cudaStream_t s) {
   if (hidden % 8 != 0 || experts > MAX_E || top_k > MAX_K || top_k > experts) return -1;
   if (tokens == 0) return 0;
   const int grid = router_grid(tokens);
@@ -398,7 +427,7 @@ extern "C" int mdt_router_fwd(const void* x, const void* w, void* scores, void* 
   {                                                                                                                            \
     const int staged = router_smem_ok((const void*)router_fwd_kernel<ET>, wbytes);                                             \
     router_fwd_kernel<ET><<<grid, 128, staged ? wbytes : 0, s>>>((const bf16*)x, (const bf16*)w, (bf16*)scores, (bf16*)weights, \
-                                                                 idx, tokens, hidden, experts, top_k, normalize, staged);      \
+                                                                 idx, tokens, hidden, experts, top_k, normalize, staged, stats); \
   }
   if (experts <= 8) RT_FWD(8) else if (experts <= 16) RT_FWD(16) else RT_FWD(MAX_E)
 #undef RT_FWD

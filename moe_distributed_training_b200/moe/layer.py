@@ -193,12 +193,37 @@ class dMoE(nn.Module):
         out = self.experts(x, scores, expert_weights, top_experts)
         return out, None
 
+    def as_dtensors(self) -> dict:
+        """The layer's parameters as `DTensor`s over the mesh `shard_moe` built, under the reference's names:
+        `router.layer.weight` replicated, `experts.mlp.w{1,2,3}` `[E*F, H]` with `Shard(0)` on the expert-parallel
+        mesh dim and `Replicate` on the data-parallel one (megablocks_utils/shard_moe_utils.py:172-201, 240-248).
+        The kernels work on the local tensors (`to_local()` of these); this view is for code that inspects or
+        gathers the sharded model the way it would the reference's.  Without a mesh the plain parameters are returned.
+        """
+        names = {"router.layer.weight": self.router.layer.weight, "experts.mlp.w1": self.experts.mlp.w1,
+                 "experts.mlp.w2": self.experts.mlp.w2, "experts.mlp.w3": self.experts.mlp.w3}
+        mesh, placements = getattr(self, "_ep_mesh", None), getattr(self, "_ep_placements", None)
+        if mesh is None:
+            return names
+        from torch.distributed.tensor import DTensor, Replicate
+        out = {}
+        for name, p in names.items():
+            pl = [Replicate()] * mesh.ndim if name.startswith("router") else list(placements)
+            out[name] = DTensor.from_local(p.detach(), mesh, pl, run_check=False)
+        return out
+
     def aux_loss(self):
         if self.last_scores is None:
             return None
         scores, top = self.last_scores
+        E, k = self.args.moe_num_experts, self.args.moe_top_k
+        stats = getattr(self.router, "last_stats", None)
+        if stats is not None and stats.numel() == 2 * E and not self.args.uniform_expert_assignment:
+            # f_e from the histogram the router kernel made while routing; P_e through `scores`, which carries the gradient
+            f = (stats[:E] / max(scores.shape[0] * k, 1)).to(scores.dtype)
+            return self.args.moe_loss_weight * E * torch.sum(f * scores.mean(dim=0))
         from ..ops.reference import load_balancing_loss
-        return self.args.moe_loss_weight * load_balancing_loss(scores, top, self.args.moe_num_experts, self.args.moe_top_k)
+        return self.args.moe_loss_weight * load_balancing_loss(scores, top, E, k)
 
 
 # The tensor-parallel variant uses the same module; the name is kept for users of the reference,

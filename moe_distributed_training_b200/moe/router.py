@@ -27,10 +27,14 @@ class LearnedRouter(nn.Module):
 
     def forward(self, x: torch.Tensor):
         x2d = x.reshape(-1, x.shape[-1])
-        scores, weights, idx = ops.router(
+        want_stats = self.args.moe_loss_weight > 0
+        out = ops.router(
             x2d, self.layer.weight, self.args.moe_top_k,
             normalize=self.args.moe_normalize_expert_weights,
-            jitter_eps=self.args.moe_jitter_eps, training=self.training)
+            jitter_eps=self.args.moe_jitter_eps, training=self.training, with_stats=want_stats)
+        scores, weights, idx = out[:3]
+        # per-expert slot counts and score sums of this call (only kept when the load-balancing loss is on)
+        self.last_stats = out[3] if want_stats else None
         if self.args.uniform_expert_assignment:
             n = idx.numel()
             idx = (torch.arange(n, device=idx.device, dtype=torch.int32) % self.args.moe_num_experts).view_as(idx)

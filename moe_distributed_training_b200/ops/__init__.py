@@ -40,10 +40,19 @@ def _cuda():
     return cuda_ops
 
 
-def router(x, w_router, top_k, normalize=True, jitter_eps=None, training=False):
+def router(x, w_router, top_k, normalize=True, jitter_eps=None, training=False, with_stats=False):
+    """with_stats: a fourth result, fp32 [2E] = per-expert (token, choice) counts followed by per-expert sums of the
+    scores (from the router kernel's own pass on CUDA; restated with tensor ops elsewhere)."""
     if _native(x) and jitter_eps is None:
-        return _cuda().router(x, w_router, top_k, normalize)
-    return reference.router(x, w_router, top_k, normalize, jitter_eps, training)
+        return _cuda().router(x, w_router, top_k, normalize, with_stats)
+    scores, weights, idx = reference.router(x, w_router, top_k, normalize, jitter_eps, training)
+    if not with_stats:
+        return scores, weights, idx
+    E = w_router.shape[0]
+    with torch.no_grad():
+        counts = torch.bincount(idx.reshape(-1).long(), minlength=E).float()
+        stats = torch.cat([counts, scores.float().sum(0)])
+    return scores, weights, idx, stats
 
 
 def make_plan(top_experts, num_experts, block=BLOCK_ROWS, capacity=None) -> RoutingPlan:

@@ -139,26 +139,31 @@ def linear(x, w, lora=None):
 # ----------------------------------------------------------------------------------------------- router / plan
 class _Router(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, top_k, normalize):
-        scores, weights, idx = ext.router_fwd(x.contiguous(), w.contiguous(), top_k, bool(normalize))
+    def forward(ctx, x, w, top_k, normalize, with_stats=False):
+        res = ext.router_fwd(x.contiguous(), w.contiguous(), top_k, bool(normalize), bool(with_stats))
+        scores, weights, idx = res[:3]
+        stats = res[3] if with_stats else torch.empty(0, dtype=torch.float32, device=x.device)
         ctx.save_for_backward(x, w, idx)
         ctx.normalize = bool(normalize)
-        ctx.mark_non_differentiable(idx)
-        return scores, weights, idx
+        ctx.mark_non_differentiable(idx, stats)
+        return scores, weights, idx, stats
 
     @staticmethod
-    def backward(ctx, dscores, dweights, _didx):
+    def backward(ctx, dscores, dweights, _didx, _dstats=None):
         x, w, idx = ctx.saved_tensors
         if dweights is None:
             dweights = torch.zeros(idx.shape, dtype=x.dtype, device=x.device)
         dx, dw = ext.router_bwd(x.contiguous(), w.contiguous(), idx, dweights.to(x.dtype), dscores, ctx.normalize)
-        return dx, dw.to(w.dtype), None, None
+        return dx, dw.to(w.dtype), None, None, None
 
 
-def router(x, w_router, top_k, normalize=True):
+def router(x, w_router, top_k, normalize=True, with_stats=False):
+    """(scores, weights, indices), plus with `with_stats` the kernel's per-expert statistics (fp32 [2E]: slot counts,
+    then score sums) as a fourth, non-differentiable result."""
     if normalize is not True and normalize not in (None, False, 1):
         raise ValueError("the fused router kernel normalises with the L1 norm only")
-    return _Router.apply(x, w_router, top_k, normalize is True or normalize == 1)
+    out = _Router.apply(x, w_router, top_k, normalize is True or normalize == 1, with_stats)
+    return out if with_stats else out[:3]
 
 
 def make_plan(top_experts, num_experts, block=BLOCK_ROWS, capacity=None) -> RoutingPlan:

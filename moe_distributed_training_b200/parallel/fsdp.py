@@ -34,7 +34,10 @@ import torch.nn as nn
 
 from .. import ops
 from ..models.mixtral import CausalLMOutput, MixtralForCausalLM, PackedBatch
+from ..utils.metrics import nvtx_range
 from . import collectives as coll
+
+NVTX = os.environ.get("MDT_NVTX") == "1"
 
 
 def _round_up(x: int, m: int) -> int:
@@ -398,6 +401,10 @@ class ShardedMixtral:
 
     # ------------------------------------------------------------------ buffers
     def _gather_into(self, unit: FsdpUnit, buffers, flags=None):
+        with nvtx_range("all_gather." + unit.name, NVTX):
+            return self._gather_into_impl(unit, buffers, flags)
+
+    def _gather_into_impl(self, unit: FsdpUnit, buffers, flags=None):
         """`flags` (one entry per group, None or a dict with the progress-flag tensor of the destination buffer): the
         gather publishes its progress there and returns what a consumer needs to wait on the small front part."""
         waits = []
@@ -648,13 +655,19 @@ class ShardedMixtral:
                 continue
             if self.rep > 1 and g.shard.grad is not None:
                 coll.all_reduce_flat(g.shard.grad, self.replicate_group)
-        # router: mean over all ranks; experts (and their LoRA factors): mean over expert replicas
-        router_grads, expert_grads = [], []
+        # router: mean over all ranks; experts (and their LoRA factors): mean over expert replicas; adapter factors that
+        # are whole on every tensor-parallel rank: first the sum of the ranks' partial gradients
+        router_grads, expert_grads, tp_partial = [], [], {}
         for u in self.units:
             for p in u.local_params:
                 if p.grad is None:
                     continue
                 (expert_grads if getattr(p, "_is_expert_param", False) else router_grads).append(p.grad)
+                tpg = getattr(p, "_tp_partial_grad_group", None)
+                if tpg is not None:
+                    tp_partial.setdefault(id(tpg), (tpg, []))[1].append(p.grad)
+        for tpg, grads in tp_partial.values():
+            _all_reduce_list(grads, tpg, 1.0)
         wg = self.world_group
         if router_grads and coll.group_size(wg) > 1:
             _all_reduce_list(router_grads, wg, 1.0 / coll.group_size(wg))

@@ -66,6 +66,11 @@ class ExpertLoraAdapters(nn.Module):
             self.lora_B[name] = nn.Parameter(torch.zeros(E, r, fout, dtype=dt, device=dev))
             self.lora_A[name]._is_expert_param = True
             self.lora_B[name]._is_expert_param = True
+            if args.tensor_parallel_size > 1:
+                # With tensor-parallel experts the factor on the hidden side (A of w1/w3, B of w2) is whole on every
+                # rank and sees only that rank's slice of the FFN dim: its gradient is a partial sum over the group.
+                whole = self.lora_B[name] if name == "w2" else self.lora_A[name]
+                whole._tp_partial_grad_group = args.tensor_parallel_group
             mlp._lora_pointers[name] = (self.lora_A[name], self.lora_B[name], r, alpha, H, F)
 
 

@@ -37,6 +37,10 @@ from ..optim.schedulers import get_scheduler
 from ..parallel.fsdp import ShardedMixtral
 from ..parallel.shard_moe import (KEY_DATA_PARALLEL, KEY_EXPERT_PARALLEL, get_moe_kwargs, shard_moe)
 from ..peft.lora import ATTENTION_TARGETS, get_peft_model
+from ..utils.metrics import nvtx_range
+
+
+NVTX = os.environ.get("MDT_NVTX") == "1"     # NVTX ranges per phase (also inside the C++-issued blocks)
 
 
 def init_distributed(device_type: str = "cuda"):
@@ -118,13 +122,17 @@ class Engine:
         for i, mb in enumerate(microbatches):
             if hasattr(self.runner, "begin_microbatch"):
                 self.runner.begin_microbatch(i == ga - 1)
-            l = self.forward_backward(mb, 1.0 / ga)
+            with nvtx_range(f"microbatch.{i}", NVTX):
+                l = self.forward_backward(mb, 1.0 / ga)
             loss_sum = l if loss_sum is None else loss_sum + l
-        self.runner.reduce_gradients()
+        with nvtx_range("reduce_gradients", NVTX):
+            self.runner.reduce_gradients()
         grad_norm = None
         if self.max_grad_norm is not None and self.max_grad_norm > 0:
-            grad_norm = clip_grad_norm_(self.model, self.max_grad_norm, self.shard_group, self.ep_group, self.optimizer)
-        self.optimizer.step()
+            with nvtx_range("grad_norm", NVTX):
+                grad_norm = clip_grad_norm_(self.model, self.max_grad_norm, self.shard_group, self.ep_group, self.optimizer)
+        with nvtx_range("optimizer", NVTX):
+            self.optimizer.step()
         if hasattr(self.runner, "after_optimizer_step"):
             self.runner.after_optimizer_step()
         self.scheduler.step()

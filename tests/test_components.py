@@ -243,3 +243,24 @@ def test_fsdp1_entry_accepts_the_reference_readme_command(tmp_path):
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=root)
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
     assert "train_runtime" in p.stdout
+
+
+def test_aux_loss_from_router_statistics_matches_the_definition():
+    """With a load-balancing weight the router keeps its per-expert histogram / score sums; the layer's aux loss built
+    from them equals E * sum_e f_e P_e stated directly, and it back-propagates into the router."""
+    from moe_distributed_training_b200.models.mixtral import moe_args_from_config
+    from moe_distributed_training_b200.moe.layer import dMoE
+    from moe_distributed_training_b200.ops.reference import load_balancing_loss
+    from moe_distributed_training_b200 import MixtralConfig
+    cfg = MixtralConfig.tiny()
+    cfg.router_aux_loss_coef = 0.01
+    moe = dMoE(moe_args_from_config(cfg, torch.float32, "cpu"))
+    x = torch.randn(2, 24, cfg.hidden_size)
+    out, _ = moe(x)
+    aux = moe.aux_loss()
+    scores, top = moe.last_scores
+    want = 0.01 * load_balancing_loss(scores, top, cfg.num_local_experts, cfg.num_experts_per_tok)
+    assert torch.allclose(aux, want, rtol=1e-6)
+    assert moe.router.last_stats is not None and int(moe.router.last_stats[:cfg.num_local_experts].sum()) == top.numel()
+    aux.backward()
+    assert moe.router.layer.weight.grad is not None and float(moe.router.layer.weight.grad.abs().sum()) > 0

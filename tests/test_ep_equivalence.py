@@ -50,6 +50,8 @@ def _run(rank, world, mode, steps):
         assert not eng.runner.recompute
     elif mode == "tp":
         eng = build_engine(cfg, ep_size=2, use_tp_sharding=True, **kw)
+    elif mode == "tp-lora":
+        eng = build_engine(cfg, ep_size=2, use_tp_sharding=True, use_lora="all", **kw)
     elif mode == "fsdp":
         eng = build_engine(cfg, ep_size=1, **kw)
     elif mode == "fsdp-lora":
@@ -60,7 +62,7 @@ def _run(rank, world, mode, steps):
         eng = build_engine(cfg, ep_size=world, use_lora="all", **kw)
     else:
         raise ValueError(mode)
-    if mode == "tp":
+    if mode in ("tp", "tp-lora"):
         # tensor-parallel peers see the same batch (train_accelerate_fsdp2.py:346-382)
         dp_rank = rank // 2
         mbs = [_rank_batch(cfg, dp_rank)]
@@ -74,7 +76,7 @@ def _run(rank, world, mode, steps):
         if s < steps - 1:
             eng.optimizer.step(); eng.optimizer.zero_grad(set_to_none=True)
     grads = _collect(eng)
-    ep_rank = rank if mode != "tp" else rank % 2
+    ep_rank = rank if mode not in ("tp", "tp-lora") else rank % 2
     return losses, grads, ep_rank
 
 
@@ -91,6 +93,15 @@ def _reference(n_batches, use_lora="none"):
 def _expert_slice(ref, name, cfg, ep_rank, ep, tp=False):
     g = ref[name]
     E, F, H = cfg.num_local_experts, cfg.intermediate_size, cfg.hidden_size
+    if ("lora_A" in name or "lora_B" in name) and tp:
+        # tensor-parallel experts: the FFN dim of every expert is sliced; the factor on the hidden side is whole
+        Fl = F // ep
+        w = name.rsplit(".", 1)[-1]
+        if "lora_B" in name and w in ("w1", "w3"):
+            return g[:, :, ep_rank * Fl:(ep_rank + 1) * Fl]
+        if "lora_A" in name and w == "w2":
+            return g[:, ep_rank * Fl:(ep_rank + 1) * Fl]
+        return g
     if "lora_A" in name or "lora_B" in name:
         El = E // ep
         return g[ep_rank * El:(ep_rank + 1) * El]
@@ -187,6 +198,17 @@ def test_ep2_lora_all_matches_unsharded():
         _compare(ref_grads, grads, cfg, ep_rank, 2)
 
 
+def test_tp2_dp2_expert_lora_matches_unsharded():
+    """Tensor-parallel experts with per-expert adapters (the reference's `ParallelMLP` LoRA wrapper, peft_utils.py:144-277):
+    factors on the sliced FFN side are sliced with it, the others are whole on every rank and their gradients are summed
+    over the tensor-parallel group (the reference leaves them unreduced, train_accelerate_fsdp2.py:291-298)."""
+    ref_losses, ref_grads, cfg = _reference(2, use_lora="all")
+    res = run_distributed(_run, 4, "tp-lora", 1)
+    for rank, (losses, grads, ep_rank) in enumerate(res):
+        assert abs(losses[0] - ref_losses[rank // 2]) < 1e-5
+        _compare(ref_grads, grads, cfg, ep_rank, 2, tp=True)
+
+
 @pytest.mark.slow
 def test_tp2_dp2_matches_unsharded():
     ref_losses, ref_grads, cfg = _reference(2)
@@ -194,3 +216,27 @@ def test_tp2_dp2_matches_unsharded():
     for rank, (losses, grads, ep_rank) in enumerate(res):
         assert abs(losses[0] - ref_losses[rank // 2]) < 1e-5
         _compare(ref_grads, grads, cfg, ep_rank, 2, tp=True)
+
+
+def _dtensor_views(rank, world):
+    from moe_distributed_training_b200.train.engine import build_engine
+    cfg = MixtralConfig.tiny()
+    eng = build_engine(cfg, dtype=torch.float32, device_type="cpu", ep_size=world, seed=0)
+    moe = eng.model.model.layers[0].block_sparse_moe
+    views = moe.as_dtensors()
+    full = {k: v.full_tensor().clone() for k, v in views.items()}
+    local_ok = all(torch.equal(v.to_local(), dict(moe.named_parameters())[k]) for k, v in views.items())
+    placements = {k: [type(p).__name__ for p in v.placements] for k, v in views.items()}
+    return full, local_ok, placements
+
+
+def test_expert_parameters_as_dtensors_gather_to_the_unsharded_weights():
+    from moe_distributed_training_b200.train.engine import build_engine
+    cfg = MixtralConfig.tiny()
+    ref = build_engine(cfg, dtype=torch.float32, device_type="cpu", seed=0).model.model.layers[0].block_sparse_moe
+    for full, local_ok, placements in run_distributed(_dtensor_views, 2):
+        assert local_ok
+        assert placements["experts.mlp.w1"] == ["Shard"] and placements["router.layer.weight"] == ["Replicate"]
+        assert torch.equal(full["router.layer.weight"].float(), ref.router.layer.weight.detach().float())
+        for w in ("w1", "w2", "w3"):
+            assert torch.equal(full[f"experts.mlp.{w}"].float(), getattr(ref.experts.mlp, w).detach().float()), w

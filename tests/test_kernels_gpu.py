@@ -598,3 +598,50 @@ def test_residual_connections_fused_into_their_producers(ops):
     acc = base.clone()
     ext.router_bwd(xr, wr, idx, dwts, None, True, acc)
     _close(acc, base.float() + dx_plain.float(), name="router dx accumulate")
+
+
+def test_deterministic_kernels_are_bitwise_reproducible(ops):
+    """Routing plan, row gather, the GEMM family (dense, row-grouped with fused SwiGLU, depth-grouped), RMSNorm and
+    the gate-weighted combine use no atomics on their results: two runs on the same inputs agree bit for bit."""
+    torch.manual_seed(41)
+    ext = ops.ext
+    T, k, E, H, F = 900, 2, 4, 512, 1024
+    x = _rand(T, H)
+    top = torch.randn(T, E, device=DEV).topk(k, -1).indices.int()
+    w1, w2, w3 = (_rand(E, F, H, scale=0.05) for _ in range(3))
+    wts = torch.rand(T, k, device=DEV).to(torch.bfloat16)
+
+    def run():
+        plan = ops.make_plan(top, E)
+        xg = ext.gather_rows(x, plan.src_slot, plan.padded_offsets, E, None, k)
+        y = ops.grouped_swiglu_mlp(xg, w1, w2, w3, plan)
+        out = ext.combine_rows(y, plan.dest_row, wts, k, x)
+        dw = torch.empty(E, F, H, dtype=torch.bfloat16, device=DEV)
+        ops._g(2, y.new_zeros(xg.shape[0], F) + 1, True, xg, True, dw, H, 0, plan)
+        dense = ops.mm_nt(x, w1[0])
+        xn, rstd = ext.rmsnorm_fwd(x, torch.ones(H, dtype=torch.bfloat16, device=DEV), 1e-5)
+        return [plan.tokens_per_expert, plan.padded_offsets, plan.dest_row, plan.src_slot, xg, y, out, dw, dense, xn, rstd]
+
+    a, b = run(), run()
+    torch.cuda.synchronize()
+    for i, (p, q) in enumerate(zip(a, b)):
+        assert torch.equal(p, q), f"output {i} differs between two runs"
+    ops.check_status(DEV)
+
+
+def test_router_kernel_histogram_and_score_sums(ops):
+    """The router kernel's optional statistics (per-expert slot counts and score sums, the f_e and P_e of the
+    load-balancing loss) against a count and a sum over its own outputs; the loss built from them equals the plain one."""
+    from moe_distributed_training_b200.ops.reference import load_balancing_loss
+    torch.manual_seed(51)
+    for (T, H, E, k) in [(700, 512, 8, 2), (37, 256, 16, 4)]:
+        x, w = _rand(T, H), _rand(E, H, scale=0.2)
+        scores, weights, idx, stats = ops.ext.router_fwd(x, w, k, True, True)
+        counts = torch.bincount(idx.reshape(-1).long(), minlength=E).float()
+        assert torch.equal(stats[:E], counts)
+        assert torch.allclose(stats[E:], scores.float().sum(0), rtol=1e-4, atol=1e-3)
+        s2, w2, i2 = ops.ext.router_fwd(x, w, k, True)
+        assert torch.equal(s2, scores) and torch.equal(i2, idx) and torch.equal(w2, weights)
+        f = stats[:E] / (T * k)
+        loss = E * torch.sum(f * scores.float().mean(0))
+        assert torch.allclose(loss, load_balancing_loss(scores.float(), idx, E, k), rtol=1e-5)
