@@ -466,11 +466,12 @@ void rs_pull(Tensor& out, const Tensor& peer_full, int64_t ws, int64_t rank, boo
 }
 // announce + wait + reduce-scatter of one group in one kernel (csrc/comm.cu::rs_block_kernel)
 void rs_block(Tensor& out, const Tensor& peer_full, const Tensor& peer_flags, int64_t my_flags, int64_t flag_index, int64_t ws, int64_t rank,
-              bool in_fp32, double scale, bool accumulate, int64_t epoch, Tensor& status, int64_t max_ctas) {
+              bool in_fp32, double scale, bool accumulate, int64_t epoch, Tensor& status, int64_t max_ctas, bool all_reduce) {
   c10::cuda::CUDAGuard guard(out.device());
   TORCH_CHECK(out.is_contiguous());
   check(mdt_rs_block(out.data_ptr(), ptrs(peer_full), ptrs(peer_flags), my_flags, (int)flag_index, (int)ws, (int)rank, out.numel(), in_fp32,
-                     out.scalar_type() == at::kFloat, (float)scale, accumulate, (unsigned)epoch, status.data_ptr<int>(), (int)max_ctas, cur_stream()), "rs_block");
+                     out.scalar_type() == at::kFloat, (float)scale, accumulate, (unsigned)epoch, status.data_ptr<int>(), (int)max_ctas,
+                     all_reduce ? 1 : 0, cur_stream()), "rs_block");
 }
 void barrier_arrive(const Tensor& peer_flags, int64_t ws, int64_t rank, int64_t epoch) {
   c10::cuda::CUDAGuard guard(peer_flags.device());
@@ -911,7 +912,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ag_wait_chunks", &ag_wait_chunks);
   m.def("gather_registry_clear", &gather_registry_clear);
   m.def("rs_block", &rs_block, py::arg("out"), py::arg("peer_full"), py::arg("peer_flags"), py::arg("my_flags"), py::arg("flag_index"), py::arg("ws"),
-        py::arg("rank"), py::arg("in_fp32"), py::arg("scale"), py::arg("accumulate"), py::arg("epoch"), py::arg("status"), py::arg("max_ctas") = 0);
+        py::arg("rank"), py::arg("in_fp32"), py::arg("scale"), py::arg("accumulate"), py::arg("epoch"), py::arg("status"), py::arg("max_ctas") = 0,
+        py::arg("all_reduce") = false);
   m.def("set_peer_wait_limit_ms", [](int64_t ms) { mdt_set_peer_wait_limit_ms((long long)ms); });
   m.def("rs_pull", &rs_pull);
   m.def("barrier_arrive", &barrier_arrive);

@@ -385,9 +385,11 @@ __device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ void from_f(float* p, float v) { *p = v; }
 __device__ __forceinline__ void from_f(bf16* p, float v) { *p = __float2bfloat16(v); }
 template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
+// `src_off`: first element of the range that is read from every peer's buffer (rank * n for a reduce-scatter, 0 for an
+// all-reduce of n elements)
 template <typename TIn, typename TOut>
 __device__ __forceinline__ void rs_pull_body(TOut* __restrict__ out, const long long* __restrict__ peer_full, int ws, int rank, long long n,
-                                             float scale, int accumulate, long long tid, long long nthreads) {
+                                             float scale, int accumulate, long long tid, long long nthreads, long long src_off) {
   constexpr int V = Vec16<TIn>::N;
   const long long nvec = n / V;
   for (long long i = tid; i < nvec; i += nthreads) {
@@ -396,7 +398,7 @@ __device__ __forceinline__ void rs_pull_body(TOut* __restrict__ out, const long 
     for (int j = 0; j < V; ++j) acc[j] = 0.f;
     for (int r = 0; r < ws; ++r) {
       const int rr = (r + rank) % ws;   // start with a different peer on every rank
-      const uint4 v = reinterpret_cast<const uint4*>(reinterpret_cast<const TIn*>(peer_full[rr]) + (long long)rank * n)[i];
+      const uint4 v = reinterpret_cast<const uint4*>(reinterpret_cast<const TIn*>(peer_full[rr]) + src_off)[i];
       const TIn* e = reinterpret_cast<const TIn*>(&v);
 #pragma unroll
       for (int j = 0; j < V; ++j) acc[j] += to_f(e[j]);
@@ -410,7 +412,7 @@ __device__ __forceinline__ void rs_pull_body(TOut* __restrict__ out, const long 
   }
   for (long long i = nvec * V + tid; i < n; i += nthreads) {   // tail (n not a multiple of the vector width)
     float sres = 0.f;
-    for (int r = 0; r < ws; ++r) sres += to_f(reinterpret_cast<const TIn*>(peer_full[(r + rank) % ws])[(long long)rank * n + i]);
+    for (int r = 0; r < ws; ++r) sres += to_f(reinterpret_cast<const TIn*>(peer_full[(r + rank) % ws])[src_off + i]);
     sres *= scale;
     if (accumulate) sres += to_f(out[i]);
     from_f(out + i, sres);
@@ -420,7 +422,7 @@ template <typename TIn, typename TOut>
 __global__ void rs_pull_kernel(TOut* __restrict__ out, const long long* __restrict__ peer_full, int ws, int rank, long long n,
                                float scale, int accumulate) {
   rs_pull_body<TIn, TOut>(out, peer_full, ws, rank, n, scale, accumulate, (long long)blockIdx.x * blockDim.x + threadIdx.x,
-                          (long long)gridDim.x * blockDim.x);
+                          (long long)gridDim.x * blockDim.x, (long long)rank * n);
 }
 // Reduce-scatter of one parameter group in the middle of a backward pass, as one kernel on a side stream:
 //   announce  my contribution (the group's full-size gradient buffer) is complete: store `epoch` into slot
@@ -428,10 +430,12 @@ __global__ void rs_pull_kernel(TOut* __restrict__ out, const long long* __restri
 //   wait      until every peer has announced the same (bounded)
 //   reduce    read my slice of every peer's buffer, scale, cast, write / accumulate the shard gradient
 // The owners of the buffers must not overwrite them before all peers have read: see the caller's barrier.
+// With `all_reduce` every rank reads the whole range [0, n) of every buffer instead of its own slice: the sum of the
+// tensor-parallel ranks' partial expert outputs (the reference's dist.all_reduce, megablocks_utils/config_utils.py:168-184).
 template <typename TIn, typename TOut>
 __global__ void rs_block_kernel(TOut* __restrict__ out, const long long* __restrict__ peer_full, const long long* __restrict__ peer_flags,
                                 long long my_flags, int flag_index, int ws, int rank, long long n, float scale, int accumulate,
-                                unsigned epoch, int* __restrict__ status, unsigned long long limit_ns) {
+                                unsigned epoch, int* __restrict__ status, unsigned long long limit_ns, int all_reduce) {
   __shared__ int ok;
   if (threadIdx.x == 0) ok = status_set(status) ? 0 : 1;
   __syncthreads();
@@ -447,7 +451,7 @@ __global__ void rs_block_kernel(TOut* __restrict__ out, const long long* __restr
   __syncthreads();
   if (!ok) return;
   rs_pull_body<TIn, TOut>(out, peer_full, ws, rank, n, scale, accumulate, (long long)blockIdx.x * blockDim.x + threadIdx.x,
-                          (long long)gridDim.x * blockDim.x);
+                          (long long)gridDim.x * blockDim.x, all_reduce ? 0ll : (long long)rank * n);
 }
 
 // cross-rank barrier on symmetric flags: arrive = write epoch into everyone's slot, then wait for all
@@ -579,11 +583,11 @@ extern "C" int mdt_rs_pull(void* out, const long long* peer_full, int ws, int ra
 }
 extern "C" int mdt_rs_block(void* out, const long long* peer_full, const long long* peer_flags, long long my_flags, int flag_index, int ws, int rank,
                             long long n, int in_fp32, int out_fp32, float scale, int accumulate, unsigned epoch, int* status, int max_ctas,
-                            cudaStream_t s) {
+                            int all_reduce, cudaStream_t s) {
   if (ws > 32 || rank < 0 || rank >= ws) return -1;
   const unsigned blocks = (unsigned)rs_blocks(n, max_ctas > 0 ? max_ctas : sm_count() * 2);
 #define MDT_RS_BLOCK(TI, TO) rs_block_kernel<TI, TO><<<blocks, RS_THREADS, 0, s>>>((TO*)out, peer_full, peer_flags, my_flags, flag_index, ws, rank, n, scale, \
-                                                                              accumulate, epoch, status, g_peer_wait_ns)
+                                                                              accumulate, epoch, status, g_peer_wait_ns, all_reduce)
   if (in_fp32 && !out_fp32) MDT_RS_BLOCK(float, bf16);
   else if (in_fp32 && out_fp32) MDT_RS_BLOCK(float, float);
   else if (!in_fp32 && !out_fp32) MDT_RS_BLOCK(bf16, bf16);

@@ -60,10 +60,11 @@ int mdt_ag_pull(void* out, const long long* peer_shard, int ws, int rank, long l
 int mdt_ag_wait_chunks(const unsigned* ready, int first, int last, unsigned epoch, int* status, cudaStream_t s);
 int mdt_rs_pull(void* out, const long long* peer_full, int ws, int rank, long long n, int in_fp32, int out_fp32, float scale,
                 int accumulate, cudaStream_t s);
-// announce + wait + reduce in one kernel (see rs_block_kernel); flag tables hold u32 [slots][ws]
+// announce + wait + reduce in one kernel (see rs_block_kernel); flag tables hold u32 [slots][ws].  all_reduce = 0: the
+// result is this rank's slice [rank * n, (rank + 1) * n) of the sum; 1: the sum of the whole range [0, n) on every rank.
 int mdt_rs_block(void* out, const long long* peer_full, const long long* peer_flags, long long my_flags, int flag_index, int ws, int rank,
                  long long n, int in_fp32, int out_fp32, float scale, int accumulate, unsigned epoch, int* status, int max_ctas,
-                 cudaStream_t s);
+                 int all_reduce, cudaStream_t s);
 int mdt_barrier_arrive(const long long* peer_flags, int ws, int rank, unsigned epoch, cudaStream_t s);
 int mdt_barrier_wait(const void* my_flags, int ws, unsigned epoch, int* status, long long limit_ms, cudaStream_t s);  // limit_ms <= 0: default
 // limit of every wait for a peer (also the GEMM's waits for operands that other GPUs or streams deliver); ms <= 0 restores 10 s

@@ -21,6 +21,7 @@ The EP token exchange has two implementations: "nccl" issues
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -57,14 +58,28 @@ class _AllToAll(torch.autograd.Function):
         return out, None, None, None
 
 
+def _tp_all_reduce(x: torch.Tensor, group) -> torch.Tensor:
+    """Sum over the tensor-parallel group: the peer-memory kernel on CUDA (native backend), else the library call."""
+    x = x.contiguous()
+    if x.is_cuda and ops.get_backend() == "native" and x.dtype in (torch.bfloat16, torch.float32) \
+            and os.environ.get("MDT_PEER_COLLECTIVES", "1") != "0":
+        from ..parallel import fused_ep, symm
+        if fused_ep.available():
+            nbytes = x.numel() * x.element_size()
+            ar = symm.PeerAllReduce.for_group(group, max(nbytes, 64 << 20), x.device)
+            if nbytes <= ar.half:
+                return ar(x)
+    x = x.clone()
+    dist.all_reduce(x, group=group)
+    return x
+
+
 class _ReduceFromTP(torch.autograd.Function):
     """Forward: sum over the tensor-parallel group.  Backward: identity."""
 
     @staticmethod
     def forward(ctx, x, group):
-        x = x.contiguous().clone()
-        dist.all_reduce(x, group=group)
-        return x
+        return _tp_all_reduce(x, group)
 
     @staticmethod
     def backward(ctx, grad):
@@ -81,9 +96,7 @@ class _CopyToTP(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad):
-        grad = grad.contiguous().clone()
-        dist.all_reduce(grad, group=ctx.group)
-        return grad, None
+        return _tp_all_reduce(grad, ctx.group), None
 
 
 # ----------------------------------------------------------------------------

@@ -125,3 +125,57 @@ class FlatPeers:
 
     def table(self, byte_offset: int) -> torch.Tensor:
         return torch.tensor([b + byte_offset for b in self.bases], dtype=torch.int64, device=self.device)
+
+
+class PeerAllReduce:
+    """Sum of bf16 / fp32 tensors over a group through peer memory: one kernel per call.
+
+    Every rank copies its contribution into its half-buffer of the current parity, and one kernel announces that to
+    the peers, waits for their announcements and adds up all ranks' buffers (`csrc/comm.cu::rs_block_kernel` with
+    `all_reduce`).  Two parities make a second barrier unnecessary: a rank reaches call c + 2, which overwrites the
+    buffer of call c, only after its kernel of call c + 1 has seen every peer announce call c + 1, and a peer
+    announces call c + 1 after its own kernel of call c (which did all its reads) has finished, in stream order.
+    Used for the partial sums of tensor-parallel experts (the reference's `dist.all_reduce`,
+    megablocks_utils/config_utils.py:168-184).
+    """
+
+    _instances = {}
+
+    def __init__(self, group, max_bytes: int, device):
+        import torch.distributed._symmetric_memory as symm_mem
+        from ..ops import cuda_ops
+        self.ext, self.cuda_ops = cuda_ops.ext, cuda_ops
+        self.ws, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.half = _align(max_bytes)
+        self.flag_bytes = _align(2 * self.ws * 4)
+        self.nbytes = 2 * self.half + self.flag_bytes
+        self.buffer = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.buffer.zero_()
+        self.handle = symm_mem.rendezvous(self.buffer, group.group_name)
+        self.bases = [int(p) for p in self.handle.buffer_ptrs]
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+        self.device = device
+        self.calls = 0
+        self.tables = [torch.tensor([b + par * self.half for b in self.bases], dtype=torch.int64, device=device) for par in (0, 1)]
+        self.flag_table = torch.tensor([b + 2 * self.half for b in self.bases], dtype=torch.int64, device=device)
+
+    @classmethod
+    def for_group(cls, group, max_bytes: int, device):
+        key = (group.group_name, torch.device(device).index)
+        inst = cls._instances.get(key)
+        if inst is None or inst.half < max_bytes:
+            inst = cls._instances[key] = cls(group, max_bytes, device)
+        return inst
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        nbytes = x.numel() * x.element_size()
+        assert nbytes <= self.half and x.dtype in (torch.bfloat16, torch.float32)
+        self.calls += 1
+        par = self.calls & 1
+        mine = self.buffer[par * self.half: par * self.half + nbytes].view(x.dtype).view(x.shape)
+        mine.copy_(x)
+        out = torch.empty_like(x, memory_format=torch.contiguous_format)
+        self.ext.rs_block(out.view(-1), self.tables[par], self.flag_table, self.bases[self.rank] + 2 * self.half, par, self.ws, self.rank,
+                          x.dtype == torch.float32, 1.0, False, self.calls, self.cuda_ops.status_tensor(self.device), 0, True)
+        return out

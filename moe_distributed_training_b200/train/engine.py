@@ -78,6 +78,7 @@ class Engine:
     ep_group: object = None
     max_grad_norm: Optional[float] = None
     sort_microbatches: bool = True
+    balance_microbatches: bool = True
     manage_gc: bool = True
     gc_every: int = 50
     step_count: int = 0
@@ -111,12 +112,84 @@ class Engine:
                 gc.enable()
                 gc.collect(2 if self.step_count % self.gc_every == 0 else 0)
 
+    def _balance_across_ranks(self, microbatches: List[dict]) -> Optional[List[dict]]:
+        """Re-deal the step's sequences over the ranks so that micro-batch i has nearly the same length on every rank.
+
+        Expert-parallel ranks meet at every MoE layer, so micro-batch i costs all of them the time of the longest
+        sequence any of them holds at position i; sorting each rank's own micro-batches leaves a spread of the order
+        of +-20 % between the ranks' i-th longest.  Here the lengths of all ranks are gathered, the world x GA
+        sequences are ranked by length, and position i of every rank is filled from ranks i*world ... (i+1)*world - 1
+        of that list (in alternating rank order, which also evens out the ranks' token totals).  The sequences then
+        change owners with one small all-to-all.  The set of sequences in the global batch, and therefore the
+        averaged gradient, is unchanged.  Only for micro-batches of one sequence each (the reference's
+        per_device_train_batch_size=1); returns None when that does not hold.
+        """
+        world, rank, ga = self.world_size, self.rank, len(microbatches)
+        single = all(mb["input_ids"].dim() == 1 and mb.get("cu_seqlens") is not None and mb["cu_seqlens"].numel() == 2
+                     and mb.get("labels") is not None for mb in microbatches)
+        lens = torch.tensor([int(mb["input_ids"].numel()) for mb in microbatches], dtype=torch.int64, device=self.device)
+        # every rank must take the same decision: it is taken on what all of them report
+        mine = torch.tensor([ga, 1 if single else 0], dtype=torch.int64, device=self.device)
+        everyone = torch.empty(2 * world, dtype=torch.int64, device=self.device)
+        dist.all_gather_into_tensor(everyone, mine)
+        everyone = everyone.view(world, 2).tolist()
+        if any(g != ga or ok != 1 for g, ok in everyone):
+            return None
+        gathered = torch.empty(world * ga, dtype=torch.int64, device=self.device)
+        dist.all_gather_into_tensor(gathered, lens)
+        all_lens = gathered.view(world, ga).tolist()
+        order = sorted(((all_lens[r][i], r, i) for r in range(world) for i in range(ga)), key=lambda t: (-t[0], t[1], t[2]))
+        # owner[(src rank, src index)] = (dst rank, slot)
+        plan = {}
+        for slot in range(ga):
+            chunk = order[slot * world:(slot + 1) * world]
+            ranks = range(world) if slot % 2 == 0 else range(world - 1, -1, -1)
+            for (n, r, i), dst in zip(chunk, ranks):
+                plan[(r, i)] = (dst, slot, n)
+        send = [[] for _ in range(world)]              # my sequences by destination, in slot order
+        for i in range(ga):
+            dst, slot, n = plan[(rank, i)]
+            send[dst].append((slot, i))
+        recv = [[] for _ in range(world)]              # (slot, length) of what each source sends me, in its send order
+        for (r, i), (dst, slot, n) in plan.items():
+            if dst == rank:
+                recv[r].append((slot, n))
+        for lst in send + recv:
+            lst.sort()
+        parts, in_splits = [], []
+        for dst in range(world):
+            n_dst = 0
+            for slot, i in send[dst]:
+                mb = microbatches[i]
+                ids = mb["input_ids"].to(self.device, non_blocking=True).reshape(-1).long()
+                lab = mb["labels"].to(self.device, non_blocking=True).reshape(-1).long()
+                parts += [ids, lab]
+                n_dst += 2 * ids.numel()
+            in_splits.append(n_dst)
+        out_splits = [2 * sum(n for _, n in recv[r]) for r in range(world)]
+        flat_in = torch.cat(parts) if parts else torch.empty(0, dtype=torch.int64, device=self.device)
+        flat_out = torch.empty(sum(out_splits), dtype=torch.int64, device=self.device)
+        dist.all_to_all_single(flat_out, flat_in, output_split_sizes=out_splits, input_split_sizes=in_splits)
+        result = [None] * ga
+        off = 0
+        for r in range(world):
+            for slot, n in recv[r]:
+                ids, lab = flat_out[off:off + n], flat_out[off + n:off + 2 * n]
+                off += 2 * n
+                result[slot] = {"input_ids": ids, "labels": lab,
+                                "cu_seqlens": torch.tensor([0, n], dtype=torch.int32, device=self.device), "max_seqlen": n}
+        return result if all(mb is not None for mb in result) else None
+
     def _train_step(self, microbatches: List[dict]) -> dict:
         ga = len(microbatches)
-        if self.world_size > 1 and self.sort_microbatches:
-            # Expert-parallel ranks meet at every MoE layer, so a micro-batch costs every rank the time of the
-            # longest sequence among them.  Gradient accumulation does not depend on the order, so each rank runs
-            # its micro-batches longest first: ranks then work on sequences of similar length at the same time.
+        balanced = None
+        if self.world_size > 1 and self.sort_microbatches and self.balance_microbatches:
+            balanced = self._balance_across_ranks(microbatches)
+        if balanced is not None:
+            microbatches = balanced              # position i: nearly the same length on every rank, longest first
+        elif self.world_size > 1 and self.sort_microbatches:
+            # Gradient accumulation does not depend on the order, so each rank at least runs its own micro-batches
+            # longest first: ranks then work on sequences of similar length at the same time.
             microbatches = sorted(microbatches, key=lambda mb: -int(mb["input_ids"].numel()))
         loss_sum = None
         for i, mb in enumerate(microbatches):
@@ -239,4 +312,7 @@ def build_engine(cfg: MixtralConfig, *, dtype: torch.dtype = torch.bfloat16, dev
     params = [p for p in model.parameters() if p.requires_grad]
     opt = FusedAdamW(params, lr=learning_rate, weight_decay=weight_decay, state_dtype=optimizer_state_dtype)
     sched = get_scheduler(lr_scheduler_type, opt, num_warmup_steps, num_training_steps)
-    return Engine(model, runner, opt, sched, mesh, device, rank, world, ep_size, shard_group, ep_group, max_grad_norm)
+    eng = Engine(model, runner, opt, sched, mesh, device, rank, world, ep_size, shard_group, ep_group, max_grad_norm)
+    # tensor-parallel peers share their batches, so sequences cannot change owners there
+    eng.balance_microbatches = not use_tp_sharding and os.environ.get("MDT_BALANCE_MICROBATCHES", "1") != "0"
+    return eng

@@ -35,7 +35,15 @@ def main():
         os.environ["MDT_GEMM_ONLY_MIN_NUMEL"] = str(1 << 16)
         mode = mode[:-len("-pool")]
     for impl in ("nccl", "fused"):
-        if mode.startswith("fsdp"):
+        if mode == "tp":
+            # tensor-parallel experts on a (dp, tp) mesh: the partial sums of the down projection are added up by the
+            # library all-reduce or by the peer-memory all-reduce kernel; tensor-parallel peers share a batch
+            os.environ["MDT_PEER_COLLECTIVES"] = "0" if impl == "nccl" else "1"
+            eng = build_engine(cfg, dtype=torch.bfloat16, device_type="cuda", ep_size=2, use_tp_sharding=True, learning_rate=1e-3,
+                               seed=0, lr_scheduler_type="constant")
+            ds_tp = SyntheticInstructionDataset(cfg.vocab_size, 6, 100, 400, seed=3, rank=rank // 2)
+            mbs = [collate_packed([ex]) for ex in ds_tp.examples]
+        elif mode.startswith("fsdp"):
             # no expert parallelism: everything, experts included, is sharded; compare NCCL collectives with the
             # peer-memory all-gather / reduce-scatter kernels
             os.environ["MDT_PEER_COLLECTIVES"] = "0" if impl == "nccl" else "1"

@@ -272,6 +272,16 @@ def test_reduce_scatter_block_kernel_emulated(cops):
         want = 1.0 + 0.25 * sum(f[rank * n:(rank + 1) * n] for f in fulls)
         assert torch.allclose(acc.float(), want, atol=2e-2, rtol=2e-2)
     assert int(status.item()) == 0
+    # the all-reduce form: every rank gets the sum of the whole buffers (bf16 in, bf16 out)
+    parts = [torch.randn(n, device=DEV).to(torch.bfloat16) for _ in range(ws)]
+    ptable = torch.tensor([p_.data_ptr() for p_ in parts], dtype=torch.int64, device=DEV)
+    for f in flags:
+        f.view(8, ws)[5].fill_(2)
+    for rank in range(ws):
+        out = torch.empty(n, dtype=torch.bfloat16, device=DEV)
+        ext.rs_block(out, ptable, flag_table, flags[rank].data_ptr(), 5, ws, rank, False, 1.0, False, 2, status, 0, True)
+        assert torch.allclose(out.float(), sum(p_.float() for p_ in parts), atol=3e-2, rtol=2e-2)
+    assert int(status.item()) == 0
     ext.set_peer_wait_limit_ms(100)
     try:
         acc = torch.ones(n, dtype=torch.bfloat16, device=DEV)

@@ -240,3 +240,37 @@ def test_expert_parameters_as_dtensors_gather_to_the_unsharded_weights():
         assert torch.equal(full["router.layer.weight"].float(), ref.router.layer.weight.detach().float())
         for w in ("w1", "w2", "w3"):
             assert torch.equal(full[f"experts.mlp.{w}"].float(), getattr(ref.experts.mlp, w).detach().float()), w
+
+
+def _step_with_balancing(rank, world, balance):
+    from moe_distributed_training_b200.train.engine import build_engine
+    cfg = MixtralConfig.tiny()
+    eng = build_engine(cfg, dtype=torch.float32, device_type="cpu", ep_size=world, learning_rate=1e-2, max_grad_norm=None, seed=0,
+                       lr_scheduler_type="constant")
+    eng.balance_microbatches = balance
+    ds = SyntheticInstructionDataset(cfg.vocab_size, 4, 16, 96, seed=11, rank=rank)
+    mbs = [collate_packed([ex]) for ex in ds.examples]
+    eng.train_step(mbs)
+    dense = {}
+    for u in eng.runner.all_units():
+        dense.update(eng.runner.full_state(u))
+    lens = None
+    if balance:
+        lens = [int(mb["input_ids"].numel()) for mb in eng._balance_across_ranks(mbs)]
+    return {k: v.double() for k, v in dense.items()}, lens, [int(mb["input_ids"].numel()) for mb in mbs]
+
+
+def test_dealing_sequences_over_ranks_by_length_leaves_the_update_unchanged():
+    """Sequences change owners so that micro-batch i has nearly the same length on every rank; the global batch is the
+    same set of sequences, so one optimizer step gives the same parameters as without the exchange."""
+    plain = run_distributed(_step_with_balancing, 2, False)
+    dealt = run_distributed(_step_with_balancing, 2, True)
+    for (pa, _, _), (pb, _, _) in zip(plain, dealt):
+        assert pa.keys() == pb.keys()
+        for k in pa:
+            assert (pa[k] - pb[k]).abs().max().item() <= 1e-5 + 1e-4 * pa[k].abs().max().item(), k
+    all_lens = sorted((n for _, _, own in dealt for n in own), reverse=True)
+    l0, l1 = dealt[0][1], dealt[1][1]
+    assert sorted(l0 + l1, reverse=True) == all_lens                     # nothing lost, nothing duplicated
+    for i in range(4):                                                    # position i holds ranks 2i and 2i+1 of the global order
+        assert sorted([l0[i], l1[i]], reverse=True) == all_lens[2 * i:2 * i + 2]

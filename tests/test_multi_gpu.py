@@ -42,6 +42,18 @@ def test_fused_exchange_matches_nccl_exchange(tmp_path, mode):
         assert abs(a["checksum"] - b["checksum"]) < 1e-3 * abs(a["checksum"]), (a, b)
 
 
+def test_tensor_parallel_experts_peer_all_reduce_matches_nccl(tmp_path):
+    """Tensor-parallel experts need a 2-D (dp, tp) mesh, i.e. four GPUs."""
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs at least four GPUs")
+    res = _run(4, "tp", tmp_path, 29630)
+    for rank_res in res:
+        a, b = rank_res["nccl"], rank_res["fused"]
+        for la, lb in zip(a["losses"], b["losses"]):
+            assert abs(la - lb) < 2e-2 * abs(la), (a, b)
+        assert abs(a["checksum"] - b["checksum"]) < 1e-3 * abs(a["checksum"]), (a, b)
+
+
 def test_rank_that_leaves_between_steps_is_detected_on_the_host(tmp_path):
     """A rank exits between two steps (nothing of its in flight); the others see it in the store before their next
     launch, raise RankFailure on the host, and their CUDA contexts stay usable (status word clean)."""
