@@ -40,6 +40,8 @@ def main():
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--ffn", type=int, default=14336)
     ap.add_argument("--out", default="")
+    ap.add_argument("--split", action="store_true",
+                    help="only compare products with and without sharing the last round of tiles along the depth")
     ap.add_argument("--tilings", action="store_true",
                     help="only compare the three GEMM tilings (128-row, CTA pair, tall) on a few shapes")
     args = ap.parse_args()
@@ -64,6 +66,26 @@ def main():
             r["gbs"] = round(bytes_ / ms / 1e6, 1); r["frac_of_copy_peak"] = round(bytes_ / ms / 1e6 / peak_bw, 3)
         res[name] = r
         print(name, r, flush=True)
+
+    if args.split:
+        for (M, N, K) in [(576, 4096, 4096), (576, 1024, 4096), (1152, 4096, 4096), (1152, 4096, 14336), (1280, 4096, 14336),
+                          (1408, 4096, 14336), (1280, 4096, 28672), (1152, 14336, 4096), (576, 4096, 1024)]:
+            x, w = torch.randn(M, K, device=dev, dtype=bf) * 0.1, torch.randn(N, K, device=dev, dtype=bf) * 0.1
+            out = torch.empty(M, N, device=dev, dtype=bf)
+            prev_policy = ops.ext.gemm_set_pair_policy(0)
+            for name, on in (("shared_last_round", 1), ("whole_tiles_only", 0)):
+                old = ops.ext.gemm_set_split(on)
+                report(f"gemm_nt_{M}x{N}x{K}_{name}", timeit(lambda: ops.mm_nt(x, w, out=out), flush=flush), flops=2.0 * M * N * K)
+                ops.ext.gemm_set_split(old)
+            ops.ext.gemm_set_pair_policy(prev_policy)
+            report(f"gemm_nt_{M}x{N}x{K}_default_choice", timeit(lambda: ops.mm_nt(x, w, out=out), flush=flush), flops=2.0 * M * N * K)
+            report(f"cublas_nt_{M}x{N}x{K}", timeit(lambda: torch.matmul(x, w.t(), out=out), flush=flush), flops=2.0 * M * N * K)
+            del x, w, out
+        ops.check_status(dev)
+        if args.out:
+            os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
+            json.dump(res, open(args.out, "w"), indent=1)
+        return
 
     if args.tilings:
         for (M, N, K) in [(8192, 8192, 8192), (8192, 8192, 512), (1152, 4096, 4096), (1280, 14336, 4096), (1280, 4096, 14336),
@@ -111,6 +133,19 @@ def main():
         y.backward(y)
         w1.grad = w2.grad = w3.grad = None
     report("expert_mlp_fwd_bwd_full", timeit(fwd_bwd, iters=5, flush=flush), flops=18.0 * padded * H * F)
+
+    # causal GQA attention, one sequence of T tokens and one of 1024 (32 query heads, 8 key/value heads, head_dim 128);
+    # FLOPs = the causal half of 4 * T^2 * 128 per head (forward), 2.5x that for the backward pass
+    for Ta in sorted({T, 1024}):
+        q = torch.randn(Ta, 32, 128, device=dev, dtype=bf)
+        k = torch.randn(Ta, 8, 128, device=dev, dtype=bf)
+        v = torch.randn(Ta, 8, 128, device=dev, dtype=bf)
+        cu = torch.tensor([0, Ta], device=dev, dtype=torch.int32)
+        fl = 4.0 * Ta * Ta * 128 * 32 / 2
+        o, lse = ops.ext.attention_fwd(q, k, v, cu, Ta, 128 ** -0.5)
+        report(f"attention_fwd_T{Ta}", timeit(lambda: ops.ext.attention_fwd(q, k, v, cu, Ta, 128 ** -0.5), flush=flush), flops=fl)
+        do = torch.randn_like(o)
+        report(f"attention_bwd_T{Ta}", timeit(lambda: ops.ext.attention_bwd(q, k, v, o, do, lse, cu, Ta, 128 ** -0.5), flush=flush), flops=2.5 * fl)
 
     # memory-bound kernels
     xx = torch.randn(T, H, device=dev, dtype=bf)

@@ -1,6 +1,6 @@
 """Small single-GPU cases for profiler captures: one kernel family per case, a handful of launches.
 
-    python benchmarks/ncu_cases.py gemm|gemm_pair|expert_mlp|attention|dispatch|gemm_exchange
+    python benchmarks/ncu_cases.py gemm|gemm_pair|gemm_split|gather_gemm|expert_mlp|attention|dispatch|gemm_exchange
 
 Sizes keep the working set above the 126 MB L2 where DRAM figures matter, but far below a GB of launches.
 """
@@ -24,6 +24,35 @@ def main():
         C.ext.gemm_set_pair_policy(2 if case == "gemm_pair" else 0)   # CTA-pair kernel or single-CTA kernel
         for _ in range(4):
             C.mm_nt(x, w, out=out)
+    elif case == "gemm_split":
+        # down-projection shape of one micro-batch: 10 x 16 = 160 tiles on 148 SMs, the last round shared along the depth
+        x = torch.randn(1280, 14336, device=dev, dtype=bf)
+        w = torch.randn(4096, 14336, device=dev, dtype=bf) * 0.02
+        out = torch.empty(1280, 4096, device=dev, dtype=bf)
+        C.ext.gemm_set_pair_policy(0)
+        for _ in range(4):
+            C.mm_nt(x, w, out=out)
+    elif case == "gather_gemm":
+        # The all-gather of one decoder block's attention weights (8 emulated shards, 84 MB) runs on a side stream and
+        # publishes its progress; the q projection on the main stream finds its weight in the registry of gathered
+        # buffers and waits, tile by tile, for the chunks it needs.
+        ws_, H, T = 8, 4096, 1152
+        n_el = (4096 + 1024 + 1024 + 4096) * H
+        shard = n_el // ws_
+        full = torch.randn(n_el, device=dev, dtype=bf) * 0.02
+        shards = [full[r * shard:(r + 1) * shard].clone() for r in range(ws_)]
+        table = torch.tensor([t.data_ptr() for t in shards], dtype=torch.int64, device=dev)
+        nflags, _ = C.ext.ag_chunks(ws_, shard * 2)
+        ready = torch.zeros(nflags, dtype=torch.int32, device=dev)
+        out = torch.zeros(n_el, device=dev, dtype=bf)
+        x = torch.randn(T, H, device=dev, dtype=bf)
+        side = torch.cuda.Stream()
+        for epoch in range(1, 4):
+            torch.cuda.synchronize()
+            with torch.cuda.stream(side):
+                C.ext.ag_pull_flagged(out, table, ws_, 0, shard * 2, ready, epoch, 1)
+            C.mm_nt(x, out[:H * H].view(H, H))
+        C.ext.gather_registry_clear()
     elif case == "expert_mlp":
         E, F, H, rows = 1, 14336, 4096, 1152
         top = torch.zeros(rows, 1, dtype=torch.int32, device=dev)

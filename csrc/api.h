@@ -74,6 +74,10 @@ void mdt_gemm_rows_hint(long long rows);
 // `num_sms` SMs: 0 = 128-row tiles, 1 = CTA pair, 2 = tall.  Reads only M, N, K, K_l, G, mode, dual, c_fp32, accumulate,
 // capacity_rows and whether offsets is set; needs no GPU.
 int mdt_gemm_choose_tiling(const MdtGemmDesc* d, int policy, long long rows_hint, int num_sms);
+// Sharing of the last, partly filled round of 128-row tiles by all SMs along the depth (partial sums through an fp32
+// workspace, finished by the last contributor): 1 on (default; MDT_GEMM_SPLIT=0 turns it off), 0 off; returns the
+// previous setting (other values only read it).  Results of shared tiles depend on the order of fp32 additions.
+int mdt_gemm_set_split(int on);
 // upper bound on the pair kernel's grid, in pairs (0 = the resident maximum); for scaling measurements
 void mdt_gemm_set_pair_cap(int pairs);
 

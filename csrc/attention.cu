@@ -16,6 +16,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "api.h"
@@ -33,6 +35,7 @@ constexpr int ATOM_BYTES = AB * 128;      // 16 KB: [128 rows x 64 bf16]
 
 struct AttnParams {
   CUtensorMap tmQ, tmK, tmV, tmdO;
+  CUtensorMap tmK64, tmV64;                  // key / value maps with 64-row boxes (pipelined forward)
   const int* cu_seqlens;
   int num_seqs, heads_q, heads_kv;
   float scale_log2e, scale;
@@ -219,6 +222,228 @@ __global__ void __launch_bounds__(128, 1) attn_fwd_kernel(const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 256); }
+}
+
+// ------------------------------------------------------------------------------------------- forward, pipelined
+// Warp-specialised forward: warps 0-3 do the softmax (one query row per thread), warp 4 loads (TMA) and issues the
+// MMAs.  Keys / values come in blocks of 64 rows; S = Q K^T lives in two 64-column TMEM buffers, so the tensor core
+// computes S of block j+1 while the softmax warps work on block j; O is accumulated in TMEM by the P V products
+// themselves.  The running row maximum used for the exponentials is only raised when the true maximum has grown
+// by more than 2^8 (the sum and O are rescaled then, rarely after the first blocks; the final division by the row
+// sum makes the result independent of the reference point).  96 KB of shared memory and 256 TMEM columns per CTA:
+// two CTAs share an SM, so that one's softmax also overlaps the other's products.
+//   TMEM columns: [0,64) S buffer 0, [64,128) S buffer 1, [128,256) O
+//   barriers: Q, K (one K tile, reloaded as soon as S of the previous block is done), V[2], S[2] (S ready),
+//             Sfree[2] (softmax has read S), P (probabilities stored), O (P V done: O updated, P and V tile free)
+constexpr int FB = 64;                        // key rows per block
+constexpr int KV_TILE = FB * HD * 2;          // 16 KB: two atoms of [64 rows x 128 B]
+constexpr int KV_ATOM = FB * 128;             // 8 KB
+constexpr int P_TILE = AB * FB * 2;           // 16 KB: one atom of [128 rows x 128 B]
+constexpr int FWD2_THREADS = 160;
+constexpr int FWD2_SMEM = TILE_BYTES + KV_TILE + 2 * KV_TILE + P_TILE + 1024 + 128;
+static_assert(2 * (FWD2_SMEM + 1024) <= 228 * 1024, "two CTAs of the pipelined forward must fit one SM");
+constexpr float RESCALE_THRESHOLD = 8.0f;     // log2 units
+
+__device__ __forceinline__ void load_kv_tile(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int col0, int row0) {
+  tma_load_2d(dst, map, bar, col0, row0);               // box {64 columns, 64 rows}
+  tma_load_2d(dst + KV_ATOM, map, bar, col0 + 64, row0);
+}
+
+__global__ void __launch_bounds__(FWD2_THREADS, 2) attn_fwd_pipelined_kernel(const __grid_constant__ AttnParams p) {
+  int seq_start, seq_end, qb;
+  if (!find_block(p.cu_seqlens, p.num_seqs, blockIdx.x, seq_start, seq_end, qb)) return;
+  const int h = blockIdx.y, kvh = h / (p.heads_q / p.heads_kv);
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + TILE_BYTES;
+  uint8_t* sV = sK + KV_TILE;                 // two stages
+  uint8_t* sP = sV + 2 * KV_TILE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_TILE);
+  uint64_t* barQ = bars; uint64_t* barK = bars + 1; uint64_t* barV = bars + 2; uint64_t* barS = bars + 4;
+  uint64_t* barSfree = bars + 6; uint64_t* barP = bars + 8; uint64_t* barO = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    mbar_init(barQ, 1); mbar_init(barK, 1); mbar_init(&barV[0], 1); mbar_init(&barV[1], 1);
+    mbar_init(&barS[0], 1); mbar_init(&barS[1], 1); mbar_init(&barSfree[0], 4); mbar_init(&barSfree[1], 4);
+    mbar_init(barP, 4); mbar_init(barO, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 4) { tmem_alloc(tmem_slot, 256); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const int q0 = seq_start + qb * AB;
+  // key blocks up to the diagonal, and not past the end of the sequence
+  const int len = seq_end - seq_start;
+  int n_kv = 2 * qb + 2;
+  const int n_seq = (len + FB - 1) / FB;
+  if (n_kv > n_seq) n_kv = n_seq;
+  auto fail = [&](int code) {
+    *abort_flag = 1;
+    if (p.status != nullptr) atomicCAS(p.status, 0, code);
+  };
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- loads and MMA issue
+      const uint32_t idesc_s = make_idesc_bf16(128, FB, 0, 0);       // Q (K-major) x K^T (K-major)
+      const uint32_t idesc_pv = make_idesc_bf16(128, HD, 0, 1);      // P (K-major) x V (MN-major)
+      const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aP = smem_u32(sP);
+      mbar_expect_tx(barQ, TILE_BYTES);
+      load_tile(sQ, &p.tmQ, barQ, h * HD, q0);
+      mbar_expect_tx(barK, KV_TILE);
+      load_kv_tile(sK, &p.tmK64, barK, kvh * HD, seq_start);
+      mbar_expect_tx(&barV[0], KV_TILE);
+      load_kv_tile(sV, &p.tmV64, &barV[0], kvh * HD, seq_start);
+      bool ok = wait_parity(barQ, 0, abort_flag) && wait_parity(barK, 0, abort_flag);
+      if (!ok) fail(ST_TIMEOUT_FULL);
+      auto issue_s = [&](int j) {     // S_j = Q K_j^T into S buffer j & 1
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_bf16(tmem + (j & 1) * FB, desc_kmajor(aQ, k), make_smem_desc(aK + (k >> 2) * KV_ATOM + (k & 3) * 32, 16, 1024), idesc_s, k > 0);
+        umma_commit(&barS[j & 1]);
+      };
+      if (ok) issue_s(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) {
+          // K tile free once S_j is done; S buffer (j+1)&1 free once the softmax of block j-1 has read it
+          ok = wait_parity(&barS[j & 1], (j >> 1) & 1, abort_flag);
+          if (!ok) { fail(ST_TIMEOUT_TMEM_FULL); break; }
+          mbar_expect_tx(barK, KV_TILE);
+          load_kv_tile(sK, &p.tmK64, barK, kvh * HD, seq_start + (j + 1) * FB);
+          ok = wait_parity(barK, (j + 1) & 1, abort_flag);
+          if (ok && j >= 1) ok = wait_parity(&barSfree[(j + 1) & 1], ((j - 1) >> 1) & 1, abort_flag);
+          if (!ok) { fail(ST_TIMEOUT_FULL); break; }
+          issue_s(j + 1);
+        }
+        // P_j stored (which also means P V of block j-1 is complete: the softmax warps waited for it)
+        ok = wait_parity(barP, j & 1, abort_flag);
+        if (!ok) { fail(ST_TIMEOUT_EMPTY); break; }
+        if (j + 1 < n_kv) {
+          mbar_expect_tx(&barV[(j + 1) & 1], KV_TILE);
+          load_kv_tile(sV + ((j + 1) & 1) * KV_TILE, &p.tmV64, &barV[(j + 1) & 1], kvh * HD, seq_start + (j + 1) * FB);
+        }
+        ok = wait_parity(&barV[j & 1], (j >> 1) & 1, abort_flag);
+        if (!ok) { fail(ST_TIMEOUT_FULL); break; }
+        tc_fence_after();
+        const uint32_t aV = smem_u32(sV + (j & 1) * KV_TILE);
+#pragma unroll
+        for (int k = 0; k < FB / 16; ++k)
+          umma_bf16(tmem + 128, make_smem_desc(aP + k * 32, 16, 1024), make_smem_desc(aV + k * 2048, KV_ATOM, 1024), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+        umma_commit(barO);
+      }
+      if (!ok) {   // give copies in flight a bounded time to land before the CTA leaves
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 20000ull) {}
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warps: thread = query row
+    const int r = tid;
+    const uint32_t t_row = tmem + ((uint32_t)(warp * 32) << 16);
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      if (!wait_parity(&barS[j & 1], (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      __syncwarp();
+      tc_fence_after();
+      uint32_t s0[32], s1[32];
+      tmem_ld_32x32(t_row + (j & 1) * FB, s0);
+      tmem_ld_32x32(t_row + (j & 1) * FB + 32, s1);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&barSfree[j & 1]);
+      // causal mask: key column 64j + c is visible to query row 128qb + r iff it is not to the right of it
+      const int visible = qb * AB + r - j * FB;         // columns c <= visible are kept
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const float a = __uint_as_float(s0[c]) * p.scale_log2e, b = __uint_as_float(s1[c]) * p.scale_log2e;
+        s0[c] = __float_as_uint(c <= visible ? a : -INFINITY);
+        s1[c] = __float_as_uint(c + 32 <= visible ? b : -INFINITY);
+        mx = fmaxf(mx, fmaxf(__uint_as_float(s0[c]), __uint_as_float(s1[c])));
+      }
+      // raise the reference point only when the maximum has outgrown it by more than the threshold
+      float alpha = 1.f;
+      const bool raise = mx > m_ref + RESCALE_THRESHOLD;    // (also true for the first visible block: m_ref = -inf)
+      if (raise) { alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - mx); m_ref = mx; l *= alpha; }
+      if (j > 0) {
+        if (!wait_parity(barO, (j - 1) & 1, abort_flag)) { ok = false; break; }   // O of the blocks so far is complete, P free
+        __syncwarp();
+        if (__any_sync(0xffffffffu, raise)) {
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32(t_row + 128 + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(t_row + 128 + c * 32, o);
+          }
+          tmem_st_wait();
+        }
+      }
+      float rs = 0.f;
+#pragma unroll
+      for (int c = 0; c < 64; c += 8) {
+        float e[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          const float v = __uint_as_float(c < 32 ? s0[c + t] : s1[c - 32 + t]);
+          e[t] = fast_exp2(v - m_ref);      // -inf -> 0; a row with nothing visible yet has m_ref = -inf: (-inf) - (-inf) = nan, guarded below
+          if (m_ref == -INFINITY) e[t] = 0.f;
+          rs += e[t];
+        }
+        *reinterpret_cast<uint4*>(sP + r * 128 + (((c >> 3) ^ (r & 7)) << 4)) =
+            make_uint4(pack2(e[0], e[1]), pack2(e[2], e[3]), pack2(e[4], e[5]), pack2(e[6], e[7]));
+      }
+      l += rs;
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(barP);
+    }
+    if (ok && n_kv > 0 && !wait_parity(barO, (n_kv - 1) & 1, abort_flag)) ok = false;
+    __syncwarp();
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok && lane == 0) fail(ST_TIMEOUT_TMEM_FULL);
+    if (ok) {
+      tc_fence_after();
+      const int row = q0 + r;
+      const bool valid = row < seq_end;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      bf16* dst = p.o + ((long long)row * p.heads_q + h) * HD;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32(t_row + 128 + c * 32, o);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 u = make_uint4(pack2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv),
+                                 pack2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv),
+                                 pack2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv),
+                                 pack2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv));
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = u;
+          }
+        }
+        __syncwarp();
+      }
+      if (valid) p.lse[(long long)row * p.heads_q + h] = (m_ref + log2f(l)) * 0.6931471805599453f;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) { tc_fence_after(); tmem_dealloc(tmem, 256); }
 }
 
 // ------------------------------------------------------------------------------------------- backward
@@ -424,14 +649,14 @@ static EncodeTiledFnA att_encode_fn() {
   });
   return fn;
 }
-// [tokens, heads*128] bf16, box 64 columns x 128 rows
-static int att_map(CUtensorMap* m, const void* ptr, long long tokens, int heads) {
+// [tokens, heads*128] bf16, box 64 columns x `box_rows` rows
+static int att_map(CUtensorMap* m, const void* ptr, long long tokens, int heads, int box_rows = AB) {
   EncodeTiledFnA fn = att_encode_fn();
   if (fn == nullptr) return -1;
   if (reinterpret_cast<uintptr_t>(ptr) & 15) return -2;
   cuuint64_t dims[2] = {(cuuint64_t)heads * HD, (cuuint64_t)tokens};
   cuuint64_t strides[1] = {(cuuint64_t)heads * HD * 2};
-  cuuint32_t box[2] = {64, AB};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   cuuint32_t es[2] = {1, 1};
   return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -3;
@@ -453,7 +678,10 @@ extern "C" int mdt_attention_fwd(const void* q, const void* k, const void* v, vo
   if (!bound) { cudaFree(nullptr); bound = true; }
   AttnParams p;
   memset(&p, 0, sizeof(p));
+  // MDT_ATTN_FWD=serial selects the one-block-at-a-time kernel (for comparisons); default: the pipelined kernel
+  static const bool serial = []() { const char* e = getenv("MDT_ATTN_FWD"); return e != nullptr && e[0] == 's'; }();
   int rc = att_map(&p.tmQ, q, total_tokens, heads_q) | att_map(&p.tmK, k, total_tokens, heads_kv) | att_map(&p.tmV, v, total_tokens, heads_kv);
+  if (!serial) rc |= att_map(&p.tmK64, k, total_tokens, heads_kv, FB) | att_map(&p.tmV64, v, total_tokens, heads_kv, FB);
   if (rc) return rc;
   p.cu_seqlens = cu_seqlens; p.num_seqs = num_seqs; p.heads_q = heads_q; p.heads_kv = heads_kv;
   p.scale = scale; p.scale_log2e = scale * 1.4426950408889634f;
@@ -461,11 +689,13 @@ extern "C" int mdt_attention_fwd(const void* q, const void* k, const void* v, vo
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) != cudaSuccess) return -4;
+    if (cudaFuncSetAttribute(attn_fwd_pipelined_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD2_SMEM) != cudaSuccess) return -4;
     if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) != cudaSuccess) return -4;
     configured = true;
   }
   dim3 grid((total_tokens + AB - 1) / AB + num_seqs, heads_q);
-  attn_fwd_kernel<<<grid, 128, ATT_SMEM, s>>>(p);
+  if (serial) attn_fwd_kernel<<<grid, 128, ATT_SMEM, s>>>(p);
+  else attn_fwd_pipelined_kernel<<<grid, FWD2_THREADS, FWD2_SMEM, s>>>(p);
   ++g_att_launches;
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -100 - (int)e;

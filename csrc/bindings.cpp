@@ -871,6 +871,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cross_entropy", &cross_entropy);
   m.def("gemm_set_pair_policy", [](int64_t policy) { return (int64_t)mdt_gemm_set_pair_policy((int)policy); });
   m.def("gemm_set_pair_cap", [](int64_t n) { mdt_gemm_set_pair_cap((int)n); });
+  m.def("gemm_set_split", [](int64_t on) { return (int64_t)mdt_gemm_set_split((int)on); });
   m.def("gemm_choose_tiling", [](int64_t mode, int64_t M, int64_t N, int64_t K, int64_t K_l, int64_t G, int64_t capacity_rows, bool dual,
                                  bool c_fp32, bool accumulate, bool has_offsets, int64_t policy, int64_t rows_hint, int64_t num_sms) {
     MdtGemmDesc d;

@@ -59,6 +59,8 @@ struct GemmParams {
   // B (and B2) may be part of a buffer that an all-gather is still filling: see MdtGemmDesc::b_ready
   MdtOperandReady rdy_b, rdy_b2, rdy_bl;
   long long b_rows, ldb, b_group_stride, bl_rows, ldb_l, bl_group_stride;
+  // split of the last, partly filled wave of tiles along the depth (128-row kernel; see get_work)
+  float* sk_ws; unsigned* sk_ctr;
 };
 
 // Bounded wait until the chunks of the gathered buffer that hold bytes [off, off + len) of an operand have landed.
@@ -132,6 +134,64 @@ __host__ __device__ __forceinline__ bool get_tile(const GemmParams& p, int t, Ti
   }
   o.krow0 = 0;
   o.num_kb = (p.K + BK - 1) / BK;
+  return true;
+}
+
+// One unit of work of a CTA: a whole output tile, or a piece [kb0, kb1) of the depth of a tile that several CTAs share.
+struct Work {
+  Tile t;
+  int kb0, kb1;        // k blocks of the tile this CTA computes (main segment first, then the LoRA segment)
+  int split;           // -1: whole tile.  Otherwise the index of the shared tile (its slot in the fp32 workspace)
+  int contributors;    // CTAs that share the tile
+};
+
+// Tiles are dealt to the CTAs round robin; when the last round would leave most SMs idle (fewer than 7/8 of them
+// get a tile), the tiles of that round are not handed out whole: their k blocks, taken together, are cut into one
+// contiguous piece per CTA (a piece spans at most two tiles).  Every CTA adds its piece's partial sums into an fp32
+// workspace tile and counts itself in (per 32-row quarter of the tile, i.e. per epilogue warp); the warp that arrives
+// last at a quarter reads the sums back and runs the normal epilogue for it.  Nobody waits for anybody.  With 160 tiles of depth 224 on 148 SMs that is 1 round + 18 k blocks per CTA instead of
+// 2 rounds; with 80 tiles of depth 64 it is 35 k blocks per CTA on all SMs instead of 64 on 80 of them.
+// it = 0, 1, ... enumerates the CTA's work in order; returns false when there is no more.
+template <int BN_OUT>
+__device__ __forceinline__ bool get_work(const GemmParams& p, int cta, int num_ctas, int it, Work& w) {
+  const int n_blocks = (p.N + BN_OUT - 1) / BN_OUT;
+  int total_tiles;
+  if (p.mode == 2) {
+    total_tiles = ((p.M + BM - 1) / BM) * n_blocks * p.G;
+  } else {
+    const int rows = (p.mode == 1) ? p.offsets[p.G] : p.M;
+    total_tiles = ((rows + BM - 1) / BM) * n_blocks;
+  }
+  const int kbt = (p.K + BK - 1) / BK + (p.K_l + BK - 1) / BK;        // k blocks per tile (modes 0 and 1)
+  int whole = total_tiles;
+  if (p.sk_ws != nullptr && p.mode != 2 && !p.dual && kbt >= 8) {
+    const int rem = total_tiles % num_ctas;
+    // (pieces shorter than 8 k blocks are not worth their partial-sum traffic)
+    if (rem != 0 && rem * 8 < num_ctas * 7 && (long long)rem * kbt >= 8ll * num_ctas) whole = total_tiles - rem;
+  }
+  const int n_whole = whole > cta ? (whole - cta + num_ctas - 1) / num_ctas : 0;
+  w.split = -1; w.contributors = 1;
+  if (it < n_whole) {
+    if (!get_tile<BN_OUT>(p, cta + it * num_ctas, w.t)) return false;
+    w.kb0 = 0;
+    w.kb1 = w.t.num_kb + (w.t.num_kb > 0 || p.mode != 2 ? w.t.num_kb_l : 0);
+    return true;
+  }
+  const int rem = total_tiles - whole;
+  if (rem == 0) return false;
+  const long long units = (long long)rem * kbt;
+  const long long per = (units + num_ctas - 1) / num_ctas;
+  const long long u0 = (long long)cta * per, u1 = (u0 + per < units) ? u0 + per : units;
+  if (u0 >= u1) return false;
+  const int t_first = (int)(u0 / kbt), t_last = (int)((u1 - 1) / kbt);
+  const int tt = t_first + (it - n_whole);
+  if (tt > t_last) return false;
+  if (!get_tile<BN_OUT>(p, whole + tt, w.t)) return false;
+  const long long lo = (long long)tt * kbt, hi = lo + kbt;
+  w.kb0 = (int)((u0 > lo ? u0 : lo) - lo);
+  w.kb1 = (int)((u1 < hi ? u1 : hi) - lo);
+  w.contributors = (int)((hi - 1) / per) - (int)(lo / per) + 1;
+  w.split = w.contributors > 1 ? tt : -1;
   return true;
 }
 
@@ -215,10 +275,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     // ------------------------------------------------------------------ TMA producer
     prefetch_tensormap(&p.tmA); prefetch_tensormap(&p.tmB);
     uint32_t it = 0;
-    Tile t;
+    Work w;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && (p.dual ? get_tile<BN / 2>(p, tile, t) : get_tile<BN>(p, tile, t)); tile += gridDim.x) {
-      const int total_kb = t.num_kb + (t.num_kb > 0 || p.mode != 2 ? t.num_kb_l : 0);
+    for (int wi = 0; ok && (p.dual ? get_work<BN / 2>(p, blockIdx.x, gridDim.x, wi, w) : get_work<BN>(p, blockIdx.x, gridDim.x, wi, w)); ++wi) {
+      const Tile& t = w.t;
+      const int total_kb = w.kb1 - w.kb0;
       if (p.tile_ready != nullptr) {
         // rows of this tile are stored by peer GPUs: wait for them, then order the TMA reads after the acquire
         const int ti = t.m0 / BM;
@@ -230,7 +291,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         if (!wait_b_tile(p, t.g, t.n0, BN_OUT)) { fail(ST_TIMEOUT_PEER); ok = false; break; }
         fence_proxy_async_all();
       }
-      for (int kb = 0; kb < total_kb; ++kb, ++it) {
+      for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
         if (!wait_parity(&empty_bar[s], ph ^ 1, abort_flag)) { fail(ST_TIMEOUT_EMPTY); ok = false; break; }
@@ -281,17 +342,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
   } else if (warp == 1 && lane == 0) {
     // ------------------------------------------------------------------ MMA issuer
     uint32_t it = 0, acc_it = 0;
-    Tile t;
+    Work w;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && (p.dual ? get_tile<BN / 2>(p, tile, t) : get_tile<BN>(p, tile, t)); tile += gridDim.x) {
-      const int total_kb = t.num_kb + (t.num_kb > 0 || p.mode != 2 ? t.num_kb_l : 0);
+    for (int wi = 0; ok && (p.dual ? get_work<BN / 2>(p, blockIdx.x, gridDim.x, wi, w) : get_work<BN>(p, blockIdx.x, gridDim.x, wi, w)); ++wi) {
+      const Tile& t = w.t;
+      const int total_kb = w.kb1 - w.kb0;
       if (total_kb == 0) continue;
       const int buf = acc_it & 1;
       const uint32_t aph = (acc_it >> 1) & 1;
       if (!wait_parity(&tempty_bar[buf], aph ^ 1, abort_flag)) { fail(ST_TIMEOUT_TMEM_EMPTY); break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + buf * BN;
-      for (int kb = 0; kb < total_kb; ++kb, ++it) {
+      for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
         if (!wait_parity(&full_bar[s], ph, abort_flag)) { fail(ST_TIMEOUT_FULL); ok = false; break; }
@@ -305,7 +367,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
         for (int k = 0; k < BK / 16; ++k) {
           const uint64_t da = a_mn ? make_smem_desc(sA + k * 2048, 8192, 1024) : make_smem_desc(sA + k * 32, 16, 1024);
           const uint64_t db = b_mn ? make_smem_desc(sB + k * 2048, 8192, 1024) : make_smem_desc(sB + k * 32, 16, 1024);
-          umma_bf16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_bf16(d_tmem, da, db, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
         }
         umma_commit(&empty_bar[s]);   // frees the stage when these MMAs have read it
       }
@@ -317,9 +379,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;
     uint32_t acc_it = 0;
-    Tile t;
-    for (int tile = blockIdx.x; (p.dual ? get_tile<BN / 2>(p, tile, t) : get_tile<BN>(p, tile, t)); tile += gridDim.x) {
-      const int total_kb = t.num_kb + (t.num_kb > 0 || p.mode != 2 ? t.num_kb_l : 0);
+    Work w;
+    for (int wi = 0; (p.dual ? get_work<BN / 2>(p, blockIdx.x, gridDim.x, wi, w) : get_work<BN>(p, blockIdx.x, gridDim.x, wi, w)); ++wi) {
+      const Tile& t = w.t;
+      const int total_kb = w.kb1 - w.kb0;
       const int row = t.m0 + q * 32 + lane;
       const int row_limit = (p.mode == 1) ? p.offsets[p.G] : p.M;
       const bool row_ok = row < row_limit;
@@ -374,6 +437,63 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_sm100_kernel(const __gri
           }
           __syncwarp();   // the next TMEM load is warp-aligned
         }
+      } else if (w.split >= 0) {
+        // A piece of a shared tile: add the partial sums into the tile's fp32 workspace (column-major inside the tile,
+        // so that the 32 rows of a warp are 128 contiguous bytes), release the accumulator, count this CTA in, and
+        // if it is the last one of the tile's contributors, read the sums back and finish the tile.
+        float* ws = p.sk_ws + (long long)w.split * (BM * BN) + (q * 32 + lane);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) atomicAdd(ws + (c + i) * BM, __uint_as_float(r[i]));
+          __syncwarp();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+        ++acc_it;
+        // Each 32-row quarter of the tile has its own counter, so a warp never has to meet the other warps of its CTA:
+        // the warp that arrives last at its quarter finishes that quarter.
+        __threadfence();
+        __syncwarp();
+        unsigned before = 0;
+        if (lane == 0) before = atomicAdd(p.sk_ctr + w.split * 4 + q, 1u);
+        before = __shfl_sync(0xffffffffu, before, 0);
+        const bool last = before == (unsigned)w.contributors - 1u;
+        if (!last) continue;
+        __threadfence();
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          float acc[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { acc[i] = __ldcg(ws + (c + i) * BM); __stcg(ws + (c + i) * BM, 0.f); }   // leave the workspace clean
+          if (store_ok) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = t.n0 + c + v * 8;
+              if (col < p.N) {
+                float o[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = acc[v * 8 + i] * p.alpha;
+                store8(Cout, base + col, o, p.c_fp32, p.accumulate, p.R);
+              }
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) p.sk_ctr[w.split * 4 + q] = 0;
+        if (p.row_dest_rank != nullptr) {
+          __threadfence_system();
+          __syncwarp();
+          for (int d = 0; d < p.num_peers; ++d) {
+            const unsigned m = __ballot_sync(0xffffffffu, dest == d);
+            if (lane == 0 && m != 0) red_add_release_sys(reinterpret_cast<unsigned*>(p.peer_arrive[d]), __popc(m));
+          }
+        }
+        continue;
       } else {
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
@@ -1129,6 +1249,40 @@ static int make_map_uncached(CUtensorMap* m, const void* ptr, uint64_t d0, uint6
 static int g_num_sms = 0;
 static long long g_launches = 0;
 
+// Workspace of the split last wave: one fp32 tile per SM plus four counters per tile, zero between launches (the warp
+// that finishes a shared tile clears what it read).  One workspace per stream, since launches on different streams may
+// overlap on the GPU; created on the stream's first product that can use it.  MDT_GEMM_SPLIT=0 switches the split off.
+struct SplitWorkspace { float* ws; unsigned* ctr; };
+static std::mutex g_split_mutex;
+static std::map<std::pair<int, cudaStream_t>, SplitWorkspace> g_split_ws;
+static int g_split_enabled = -1;
+static bool split_enabled() {
+  if (g_split_enabled < 0) {
+    const char* e = getenv("MDT_GEMM_SPLIT");
+    g_split_enabled = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return g_split_enabled == 1;
+}
+static bool split_workspace(cudaStream_t stream, SplitWorkspace* out) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(g_split_mutex);
+  auto key = std::make_pair(dev, stream);
+  auto it = g_split_ws.find(key);
+  if (it == g_split_ws.end()) {
+    if (g_split_ws.size() >= 64) return false;          // more streams than expected: those products run unsplit
+    SplitWorkspace w{nullptr, nullptr};
+    const size_t ws_bytes = (size_t)g_num_sms * BM * 256 * sizeof(float), ctr_bytes = (size_t)g_num_sms * 4 * sizeof(unsigned);
+    if (cudaMalloc(&w.ws, ws_bytes) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (cudaMalloc(&w.ctr, ctr_bytes) != cudaSuccess) { cudaGetLastError(); cudaFree(w.ws); return false; }
+    cudaMemset(w.ws, 0, ws_bytes);
+    cudaMemset(w.ctr, 0, ctr_bytes);
+    it = g_split_ws.emplace(key, w).first;
+  }
+  *out = it->second;
+  return true;
+}
+
 template <int BN, int STAGES>
 static cudaError_t launch(const GemmParams& p, int grid, cudaStream_t stream) {
   constexpr int smem = STAGES * (A_BYTES + BN * BK * 2) + 1024 + 256;
@@ -1236,7 +1390,14 @@ static int choose_tiling(const MdtGemmDesc* d, int policy, long long thread_rows
   if (d->mode != 1 || hinted) {
     const double sms = num_sms;
     const double slow_epilogue = (!d->c_fp32 && !d->accumulate) ? 0.0 : 6.0;   // the uncoalesced epilogue costs more
-    const double t1 = ceil(ceil(blocks) * nb / sms) * (fmax(kb * 0.47, 2.0) + 1.0);
+    // rounds of 128-row tiles: whole rounds, except that a last round that fills less than 7/8 of the SMs is shared
+    // by all of them along the depth (get_work), which costs about its share plus the partial-sum traffic
+    double rounds = ceil(ceil(blocks) * nb / sms);
+    if (split_enabled() && d->mode != 2 && !d->dual) {
+      const double exact = ceil(blocks) * nb / sms, frac = exact - floor(exact);
+      if (frac > 0.0 && frac < 0.875 && kb >= 8.0) rounds = exact + 0.08;
+    }
+    const double t1 = rounds * (fmax(kb * 0.47, 2.0) + 1.0);
     const double t2 = ceil(ceil(blocks / 2 + (d->mode == 1 ? 0.25 * G : 0.0)) * nb / sms) * (kb * 0.70 + 5.0 + (d->dual ? 9.0 : 0.0) + slow_epilogue);
     tall = r >= 2 * BM && kb >= 32.0 && t2 < 0.9 * t1;
   } else {
@@ -1254,6 +1415,11 @@ extern "C" int mdt_gemm_choose_tiling(const MdtGemmDesc* d, int policy, long lon
   return mdt::choose_tiling(d, policy, rows_hint, num_sms);
 }
 extern "C" void mdt_gemm_set_pair_cap(int pairs) { mdt::g_pair_cap = pairs; }
+extern "C" int mdt_gemm_set_split(int on) {
+  const int old = mdt::split_enabled() ? 1 : 0;
+  if (on == 0 || on == 1) mdt::g_split_enabled = on;
+  return old;
+}
 extern "C" int mdt_gemm_set_pair_policy(int policy) {
   const int old = mdt::pair_policy();
   if (policy >= 0 && policy <= 4) mdt::g_pair_policy = policy;
@@ -1325,6 +1491,15 @@ extern "C" int mdt_gemm(const MdtGemmDesc* d, cudaStream_t stream) {
     const int np = (int)(pairs < 1 ? 1 : (pairs > g_num_sms ? g_num_sms : pairs));
     cudaError_t e2 = launch_pair(p, np, stream);
     return e2 == cudaSuccess ? 0 : -100 - (int)e2;
+  }
+  if (split_enabled() && p.mode != 2 && !p.dual) {
+    // the last, partly filled round of tiles may be cut along the depth and shared by all SMs (get_work)
+    const long long kbt = (p.K + BK - 1) / BK + (p.K_l + BK - 1) / BK;
+    SplitWorkspace w;
+    if (kbt >= 8 && tiles * kbt >= 8ll * g_num_sms && split_workspace(stream, &w)) {
+      p.sk_ws = w.ws; p.sk_ctr = w.ctr;
+      grid = g_num_sms;
+    }
   }
   cudaError_t e = (BN == 256) ? launch<256, 4>(p, grid, stream) : launch<128, 6>(p, grid, stream);
   return e == cudaSuccess ? 0 : -100 - (int)e;

@@ -645,3 +645,50 @@ def test_router_kernel_histogram_and_score_sums(ops):
         f = stats[:E] / (T * k)
         loss = E * torch.sum(f * scores.float().mean(0))
         assert torch.allclose(loss, load_balancing_loss(scores.float(), idx, E, k), rtol=1e-5)
+
+
+def test_gemm_last_round_shared_along_the_depth(ops):
+    """Products whose last round of 128-row tiles would leave most SMs idle: the k blocks of that round are cut into one
+    piece per SM, partial sums meet in an fp32 workspace, the last contributor of each tile quarter finishes it.  Checked
+    against fp32 and against the same product with the sharing switched off, for the epilogue variants that can meet it
+    (plain, LoRA segment, residual, fp32 accumulation, MN-major weights, row groups), twice in a row (the workspace
+    must come back clean)."""
+    ext = ops.ext
+    torch.manual_seed(61)
+    prev_policy = ext.gemm_set_pair_policy(0)          # the 128-row kernel
+    try:
+        for (M, N, K) in [(1280, 4096, 2048), (576, 4096, 1024), (576, 1024, 4096), (200, 2048, 8192)]:
+            x, w = _rand(M, K), _rand(N, K, scale=0.05)
+            want = x.float() @ w.float().t()
+            for rep in range(2):
+                _close(ops.mm_nt(x, w), want, name=f"split nt {M}x{N}x{K} run {rep}")
+            old = ext.gemm_set_split(0)
+            try:
+                unsplit = ops.mm_nt(x, w)
+            finally:
+                ext.gemm_set_split(old)
+            _close(ops.mm_nt(x, w), unsplit.float(), 1e-2, name=f"split vs unsplit {M}x{N}x{K}")
+        M, N, K, r = 576, 4096, 1024, 16
+        x, w, res = _rand(M, K), _rand(N, K, scale=0.05), _rand(M, N)
+        t, b = _rand(M, r), _rand(N, r, scale=0.1)
+        _close(ops.mm_nt(x, w, lora=(t, b), residual=res), x.float() @ w.float().t() + t.float() @ b.float().t() + res.float(),
+               name="split + lora + residual")
+        w2 = _rand(K, N, scale=0.05)
+        out32 = torch.ones(M, N, device=DEV)
+        ops._gemm(0, x, False, w2, True, out32, M, N, K, accumulate=True, alpha=0.5)
+        _close(out32, 1.0 + 0.5 * (x.float() @ w2.float()), name="split + fp32 accumulate, MN-major weights")
+        # row groups (expert down projection): 3 experts
+        E, F, H = 3, 2048, 4096
+        top = (torch.arange(700, device=DEV) % E).int()[:, None]
+        plan = ops.make_plan(top, E)
+        hg = _rand(int(plan.src_slot.numel()), F)
+        w2g = _rand(E, F, H, scale=0.03)
+        y = torch.empty(hg.shape[0], H, dtype=torch.bfloat16, device=DEV)
+        ops._g(1, hg, False, w2g, True, y, H, F, plan)
+        offs = plan.padded_offsets.tolist()
+        for e in range(E):
+            a, bnd = offs[e], offs[e + 1]
+            _close(y[a:bnd], hg[a:bnd].float() @ w2g[e].float(), name=f"split grouped rows, expert {e}")
+    finally:
+        ext.gemm_set_pair_policy(prev_policy)
+    ops.check_status(DEV)
