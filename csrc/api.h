@@ -105,6 +105,11 @@ typedef struct MdtAdamTensor { void* p; const void* g; void* m; void* v; long lo
 int mdt_adamw(const MdtAdamTensor* tensors_device, int num_tensors, long long max_n, float lr, float beta1, float beta2,
               float eps, float weight_decay, float bc1, float bc2, float grad_scale, cudaStream_t s);
 int mdt_sumsq(const void* x, long long n, int fp32, float* out_accum, cudaStream_t s);
+// dst_i (fp32) += src_i (bf16 or fp32), i < count <= MDT_MULTI_ADD_MAX, one launch
+#define MDT_MULTI_ADD_MAX 16
+typedef struct MdtMultiAdd { float* dst[MDT_MULTI_ADD_MAX]; const void* src[MDT_MULTI_ADD_MAX]; long long n[MDT_MULTI_ADD_MAX];
+                             int src_fp32[MDT_MULTI_ADD_MAX]; int count; } MdtMultiAdd;
+int mdt_multi_add(const MdtMultiAdd* a, cudaStream_t s);
 int mdt_axpby(void* y, const void* x, long long n, float a, float b, int y_fp32, int x_fp32, cudaStream_t s);
 
 // ---- router and permutation (router.cu) -----------------------------------------------------------

@@ -542,7 +542,7 @@ __global__ void __launch_bounds__(128, 1) attn_bwd_kernel(const __grid_constant_
 #pragma unroll
         for (int t = 0; t < 8; ++t) {
           const int col = c * 32 + x + t;
-          float pr = exp2f(__uint_as_float(rs[x + t]) * p.scale_log2e - lse2);
+          float pr = fast_exp2(__uint_as_float(rs[x + t]) * p.scale_log2e - lse2);
           if (!qvalid || (diag && col > r) || (k0 + col >= seq_end)) pr = 0.f;
           pv[t] = pr;
           ds[t] = pr * (__uint_as_float(rp[x + t]) - dl) * p.scale;
@@ -579,7 +579,9 @@ __global__ void __launch_bounds__(128, 1) attn_bwd_kernel(const __grid_constant_
       tmem_ld_wait();
       if (qvalid) {
 #pragma unroll
-        for (int x = 0; x < 32; ++x) atomicAdd(dqrow + c * 32 + x, __uint_as_float(raw[x]));
+        for (int x = 0; x < 32; x += 4)
+          red_add_v4_f32(dqrow + c * 32 + x, __uint_as_float(raw[x]), __uint_as_float(raw[x + 1]), __uint_as_float(raw[x + 2]),
+                         __uint_as_float(raw[x + 3]));
       }
       __syncwarp();
     }

@@ -251,6 +251,29 @@ void adamw(std::vector<Tensor> ps, std::vector<Tensor> gs, std::vector<Tensor> m
   const float bc1 = 1.0f - (float)std::pow(b1, (double)step), bc2 = 1.0f - (float)std::pow(b2, (double)step);
   check(mdt_adamw((const MdtAdamTensor*)dev.data_ptr(), (int)host.size(), max_n, (float)lr, (float)b1, (float)b2, (float)eps, (float)wd, bc1, bc2, (float)grad_scale, cur_stream()), "adamw");
 }
+// dst[i] (fp32, contiguous) += src[i] (bf16 or fp32, same number of elements): the gradient accumulators of one unit
+// in one launch per 16 tensors
+void multi_add(std::vector<Tensor> dst, std::vector<Tensor> src) {
+  TORCH_CHECK(dst.size() == src.size());
+  if (dst.empty()) return;
+  c10::cuda::CUDAGuard guard(dst[0].device());
+  for (size_t base = 0; base < dst.size(); base += MDT_MULTI_ADD_MAX) {
+    MdtMultiAdd a;
+    memset(&a, 0, sizeof(a));
+    const size_t n = std::min<size_t>(MDT_MULTI_ADD_MAX, dst.size() - base);
+    std::vector<Tensor> keep;
+    for (size_t i = 0; i < n; ++i) {
+      const Tensor& d = dst[base + i];
+      Tensor sx = src[base + i].contiguous();
+      TORCH_CHECK(d.scalar_type() == at::kFloat && d.is_contiguous() && d.numel() == sx.numel(), "multi_add: fp32 contiguous destinations of matching size");
+      TORCH_CHECK(sx.scalar_type() == at::kFloat || sx.scalar_type() == at::kBFloat16, "multi_add: bf16 or fp32 sources");
+      a.dst[i] = d.data_ptr<float>(); a.src[i] = sx.data_ptr(); a.n[i] = d.numel(); a.src_fp32[i] = sx.scalar_type() == at::kFloat;
+      keep.push_back(sx);
+    }
+    a.count = (int)n;
+    check(mdt_multi_add(&a, cur_stream()), "multi_add");
+  }
+}
 void sumsq(const Tensor& x, Tensor& out) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.is_contiguous() && out.scalar_type() == at::kFloat);
@@ -885,6 +908,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_max_pairs", []() { return (int64_t)mdt_gemm_max_pairs(); });
   m.def("skinny_mm", &skinny_mm);
   m.def("adamw", &adamw);
+  m.def("multi_add", &multi_add);
   m.def("sumsq", &sumsq);
   m.def("axpby", &axpby);
   m.def("router_fwd", &router_fwd, py::arg("x"), py::arg("w"), py::arg("top_k"), py::arg("normalize"), py::arg("with_stats") = false);

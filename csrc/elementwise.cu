@@ -398,6 +398,22 @@ __global__ void __launch_bounds__(256) axpby_kernel(void* __restrict__ y, const 
 }
 
 // cap: upper bound on the grid in CTAs; <= 0 means -cap CTAs per SM of the current device (default 16 per SM)
+// dst_i (fp32) += src_i (bf16 or fp32) for up to MDT_MULTI_ADD_MAX tensors in one launch (pointers passed by value)
+__global__ void multi_add_kernel(const MdtMultiAdd a) {
+  const int t = blockIdx.y;
+  if (t >= a.count) return;
+  float* __restrict__ dst = a.dst[t];
+  const long long n = a.n[t];
+  if (a.src_fp32[t]) {
+    const float* __restrict__ src = reinterpret_cast<const float*>(a.src[t]);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) dst[i] += src[i];
+  } else {
+    const bf16* __restrict__ src = reinterpret_cast<const bf16*>(a.src[t]);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+      dst[i] += __bfloat162float(src[i]);
+  }
+}
+
 static inline int grid_for(long long work_items, int block, int cap = -16) {
   if (cap <= 0) cap = sm_count_of_current_device() * -cap;
   long long g = (work_items + block - 1) / block;
@@ -494,6 +510,17 @@ extern "C" int mdt_adamw(const MdtAdamTensor* tensors_device, int num_tensors, l
   if (num_tensors == 0) return 0;
   dim3 grid(grid_for((max_n + 7) / 8, 256, -16), num_tensors);
   adamw_kernel<<<grid, 256, 0, s>>>(tensors_device, lr, beta1, beta2, eps, weight_decay, 1.0f / bc1, 1.0f / bc2, grad_scale);
+  MDT_CHECK_LAUNCH();
+  return 0;
+}
+extern "C" int mdt_multi_add(const MdtMultiAdd* a, cudaStream_t s) {
+  if (a->count < 1) return 0;
+  if (a->count > MDT_MULTI_ADD_MAX) return -1;
+  long long max_n = 0;
+  for (int i = 0; i < a->count; ++i) max_n = a->n[i] > max_n ? a->n[i] : max_n;
+  if (max_n == 0) return 0;
+  dim3 grid(grid_for(max_n, 256, -4), a->count);
+  multi_add_kernel<<<grid, 256, 0, s>>>(*a);
   MDT_CHECK_LAUNCH();
   return 0;
 }

@@ -40,6 +40,11 @@ def _cuda():
     return cuda_ops
 
 
+def cuda_ops_ext():
+    """The built extension module (raises if it is missing)."""
+    return _cuda().ext
+
+
 def router(x, w_router, top_k, normalize=True, jitter_eps=None, training=False, with_stats=False):
     """with_stats: a fourth result, fp32 [2E] = per-expert (token, choice) counts followed by per-expert sums of the
     scores (from the router kernel's own pass on CUDA; restated with tensor ops elsewhere)."""

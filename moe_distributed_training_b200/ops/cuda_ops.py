@@ -17,6 +17,13 @@ from .reference import BLOCK_ROWS, RoutingPlan, plan_capacity
 
 ext = _build.load()
 
+# Limit of every device-side wait for a peer (counts, rows, chunks of a gather, announcements of a reduction): 10 s by
+# default, which covers start-up skew; MDT_PEER_WAIT_MS sets another one for the process.  After the limit a kernel sets
+# the status word and returns, and every later kernel of that exchange does nothing (see check_status).
+import os as _os
+if _os.environ.get("MDT_PEER_WAIT_MS"):
+    ext.set_peer_wait_limit_ms(int(_os.environ["MDT_PEER_WAIT_MS"]))
+
 _status = {}
 
 

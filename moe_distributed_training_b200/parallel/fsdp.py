@@ -594,7 +594,10 @@ class ShardedMixtral:
             dst = [v for v, gr in zip(views, grads) if gr is not None]
             src = [gr for gr in grads if gr is not None]
             if dst:
-                torch._foreach_add_(dst, src)
+                if self.is_cuda and ops.get_backend() == "native":
+                    ops.cuda_ops_ext().multi_add(dst, src)      # one launch for the unit's gradients (fp32 += bf16)
+                else:
+                    torch._foreach_add_(dst, src)
             g._acc_dirty = True
             if self.peers is not None and self.overlap_rs and self._last_microbatch:
                 self._reduce_block_now(unit, g, scale)

@@ -242,7 +242,7 @@ def build_engine(cfg: MixtralConfig, *, dtype: torch.dtype = torch.bfloat16, dev
                  checkpoint: Optional[str] = None, seed: int = 0, mlp_impl: str = "sparse",
                  dispatch_impl: str = "auto", sync_each_batch: bool = False,
                  optimizer_state_dtype: Optional[torch.dtype] = None, ep_max_tokens: int = 4096,
-                 activation_checkpointing: bool = True) -> Engine:
+                 activation_checkpointing: bool = True, resident_params: Optional[bool] = None) -> Engine:
     rank, world, device = init_distributed(device_type)
     ep_size = ep_size or 1
     if ep_size > 1 and world % ep_size != 0:
@@ -307,7 +307,7 @@ def build_engine(cfg: MixtralConfig, *, dtype: torch.dtype = torch.bfloat16, dev
         sync_each_batch = True
     runner = ShardedMixtral(model, shard_group, replicate_group, expert_dp_group, world_group,
                             shard_experts=shard_experts, sync_each_batch=sync_each_batch,
-                            recompute=activation_checkpointing,
+                            recompute=activation_checkpointing, resident_params=resident_params,
                             lazy_init=(device, seed, cfg.initializer_range) if lazy_blocks else None)
     params = [p for p in model.parameters() if p.requires_grad]
     opt = FusedAdamW(params, lr=learning_rate, weight_decay=weight_decay, state_dtype=optimizer_state_dtype)

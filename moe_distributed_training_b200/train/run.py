@@ -170,7 +170,10 @@ def run_training(
         learning_rate=learning_rate, lr_scheduler_type=lr_scheduler_type, num_warmup_steps=num_warmup_steps,
         num_training_steps=max(total_steps, 1), max_grad_norm=max_grad_norm, checkpoint=ckpt, seed=seed,
         mlp_impl="scattermoe" if use_scattermoe else "sparse", dispatch_impl=dispatch_impl,
-        sync_each_batch=_sync_each_batch(sync_each_batch), activation_checkpointing=activation_checkpointing)
+        sync_each_batch=_sync_each_batch(sync_each_batch), activation_checkpointing=activation_checkpointing,
+        # the FSDP1 entry re-gathers every unit's flat parameters per use (accelerate.yaml: FULL_SHARD, re-shard after
+        # forward); the FSDP2 entry may keep the gathered dense parameters resident when they fit
+        resident_params=False if sharding_strategy == "fsdp1" else None)
     start_step = 0
     if resume_from:
         from ..checkpoint.state import load_training_state

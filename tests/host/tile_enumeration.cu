@@ -9,6 +9,9 @@
 
 using namespace mdt;
 
+// (defined in csrc/comm.cu, which this host program does not link)
+extern "C" unsigned long long mdt_peer_wait_limit_ns(void) { return 0; }
+
 static unsigned long long rng_state = 88172645463325252ull;
 static int rnd(int n) {
   rng_state ^= rng_state << 13; rng_state ^= rng_state >> 7; rng_state ^= rng_state << 17;
@@ -56,8 +59,71 @@ static int check(const GemmParams& p, bool pair, const std::vector<int>& offs) {
   return bad;
 }
 
+// The work lists of all CTAs together (get_work, 128-row kernel): every k block of every tile exactly once; whole
+// tiles in one piece; a shared tile's pieces come from exactly `contributors` CTAs; at most two pieces per CTA.
+template <int BN_OUT>
+static int check_work(const GemmParams& p, int num_ctas, const std::vector<int>& offs) {
+  const int rows = p.mode == 1 ? offs[p.G] : p.M;
+  const int mb = (rows + BM - 1) / BM, nb = (p.N + BN_OUT - 1) / BN_OUT;
+  const int kbt = (p.K + BK - 1) / BK + (p.K_l + BK - 1) / BK;
+  std::vector<int> covered((size_t)mb * nb * kbt, 0), pieces_of_tile((size_t)mb * nb, 0), claimed((size_t)mb * nb, 0);
+  int bad = 0;
+  for (int cta = 0; cta < num_ctas; ++cta) {
+    int pieces = 0;
+    for (int it = 0;; ++it) {
+      Work w;
+      if (!get_work<BN_OUT>(p, cta, num_ctas, it, w)) break;
+      if (it > mb * nb + 4) { printf("work list does not end\n"); return 1; }
+      const size_t tile = (size_t)(w.t.m0 / BM) * nb + w.t.n0 / BN_OUT;
+      if (w.kb0 < 0 || w.kb1 > kbt || w.kb0 >= w.kb1) { ++bad; continue; }
+      for (int kb = w.kb0; kb < w.kb1; ++kb) covered[tile * kbt + kb] += 1;
+      if (w.split >= 0) {
+        ++pieces;
+        pieces_of_tile[tile] += 1;
+        if (claimed[tile] != 0 && claimed[tile] != w.contributors) ++bad;
+        claimed[tile] = w.contributors;
+        if (w.split >= num_ctas) ++bad;                 // the workspace has one tile per CTA
+      } else if (w.kb0 != 0 || w.kb1 != kbt) {
+        ++bad;                                          // a tile that is not shared is computed whole
+      }
+    }
+    if (pieces > 2) ++bad;
+  }
+  for (size_t i = 0; i < covered.size(); ++i) if (covered[i] != 1) ++bad;
+  for (size_t i = 0; i < claimed.size(); ++i) if (claimed[i] != 0 && claimed[i] != pieces_of_tile[i]) ++bad;
+  return bad;
+}
+
 int main() {
   int failures = 0, cases = 0;
+  for (int it = 0; it < 300; ++it) {
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.mode = it % 2;
+    p.N = 8 * (1 + rnd(600));
+    p.K = 8 * (1 + rnd(2000));
+    p.K_l = (rnd(3) == 0) ? 16 : 0;
+    p.sk_ws = reinterpret_cast<float*>(0x10);           // any non-null value: only tested against NULL
+    std::vector<int> offs;
+    if (p.mode == 0) {
+      p.M = 1 + rnd(3000); p.G = 1;
+    } else {
+      p.G = 1 + rnd(8);
+      offs.push_back(0);
+      for (int g = 0; g < p.G; ++g) offs.push_back(offs.back() + BM * rnd(6));
+      p.M = offs[p.G];
+      p.offsets = offs.data();
+    }
+    const int ctas[3] = {148, 132, 7};
+    for (int c = 0; c < 3; ++c) {
+      const int b1 = check_work<256>(p, ctas[c], offs), b2 = check_work<128>(p, ctas[c], offs);
+      ++cases;
+      if (b1 || b2) {
+        ++failures;
+        printf("work lists: mode %d M %d N %d K %d K_l %d G %d ctas %d: %d / %d errors\n", p.mode, p.M, p.N, p.K, p.K_l, p.G, ctas[c], b1, b2);
+      }
+    }
+  }
   for (int it = 0; it < 400; ++it) {
     GemmParams p;
     memset(&p, 0, sizeof(p));

@@ -211,7 +211,14 @@ def test_gemm_tiling_choice_without_a_gpu():
     assert choose(0, 576, 16, 4096) == TILE128                       # narrow outputs never use 256-wide tiles
     assert choose(0, 1152, 32000, 4096) == TILE128                   # lm_head: 4.5 tall tiles per column block, no gain
     # expert GEMMs inside the exchange: buffers sized for 16 384 rows, ~1 300 expected
-    assert choose(1, 0, 4096, 14336, cap=16384, offs=True, hint=1300) == TALL     # 11 x 16 tiles would need 2 waves
+    # 11 x 16 = 176 tiles on 148 SMs: the 128-row kernel shares the 28 tiles of its second round among all SMs along the
+    # depth; without that sharing two rounds would be needed and the tall tiling wins
+    assert choose(1, 0, 4096, 14336, cap=16384, offs=True, hint=1300) == TILE128
+    old = ext.gemm_set_split(0)
+    try:
+        assert choose(1, 0, 4096, 14336, cap=16384, offs=True, hint=1300) == TALL
+    finally:
+        ext.gemm_set_split(old)
     assert choose(1, 0, 4096, 14336, cap=16384, offs=True, hint=500) == TILE128   # one wave either way
     assert choose(2, 14336, 4096, 0, cap=16384, acc=True, offs=True, hint=1152) == TILE128   # weight gradient: short depth
     assert choose(0, 8192, 8192, 8192, policy=0) == TILE128

@@ -620,7 +620,8 @@ def test_deterministic_kernels_are_bitwise_reproducible(ops):
         ops._g(2, y.new_zeros(xg.shape[0], F) + 1, True, xg, True, dw, H, 0, plan)
         dense = ops.mm_nt(x, w1[0])
         xn, rstd = ext.rmsnorm_fwd(x, torch.ones(H, dtype=torch.bfloat16, device=DEV), 1e-5)
-        return [plan.tokens_per_expert, plan.padded_offsets, plan.dest_row, plan.src_slot, xg, y, out, dw, dense, xn, rstd]
+        used = int(plan.padded_offsets[-1])      # rows past the padded groups are never written
+        return [plan.tokens_per_expert, plan.padded_offsets, plan.dest_row, plan.src_slot, xg[:used], y[:used], out, dw, dense, xn, rstd]
 
     a, b = run(), run()
     torch.cuda.synchronize()
@@ -692,3 +693,15 @@ def test_gemm_last_round_shared_along_the_depth(ops):
     finally:
         ext.gemm_set_pair_policy(prev_policy)
     ops.check_status(DEV)
+
+
+def test_multi_tensor_gradient_accumulate(ops):
+    """fp32 accumulators += bf16 / fp32 gradients of many tensors in one launch per 16."""
+    torch.manual_seed(71)
+    shapes = [(16, 4096), (4096, 16), (1024, 16), (16, 1024), (7,), (3, 5, 11)] * 4      # 24 tensors: two launches
+    dst = [torch.randn(*s_, device=DEV) for s_ in shapes]
+    src = [(torch.randn(*s_, device=DEV).to(torch.bfloat16) if i % 3 else torch.randn(*s_, device=DEV)) for i, s_ in enumerate(shapes)]
+    want = [d + s_.float() for d, s_ in zip(dst, src)]
+    ops.ext.multi_add(dst, src)
+    for got, w in zip(dst, want):
+        assert torch.equal(got, w)
