@@ -37,6 +37,7 @@ def main():
         # publishes its progress; the q projection on the main stream finds its weight in the registry of gathered
         # buffers and waits, tile by tile, for the chunks it needs.
         ws_, H, T = 8, 4096, 1152
+        C.ext.set_peer_wait_limit_ms(500)       # a wait that could not be satisfied would end quickly, also under a profiler
         n_el = (4096 + 1024 + 1024 + 4096) * H
         shard = n_el // ws_
         full = torch.randn(n_el, device=dev, dtype=bf) * 0.02
