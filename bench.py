@@ -39,6 +39,7 @@ import threading
 import time
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+T_START = time.time()
 sys.path.insert(0, HERE)
 
 DATA = "synthetic (uniform token ids, lengths uniform in [128,1024], first 40% label-masked), random-init N(0,0.02) weights"
@@ -64,7 +65,9 @@ def parse():
                          "the result is labelled gradient_checkpointing=false)")
     ap.add_argument("--configs", default="auto", choices=["auto", "none"],
                     help="auto: after the series measurement run the other named configurations as child jobs")
-    ap.add_argument("--extras-budget-s", type=float, default=620.0, help="time limit for all child jobs together")
+    ap.add_argument("--extras-budget-s", type=float, default=700.0, help="time limit for all child jobs together")
+    ap.add_argument("--total-budget-s", type=float, default=790.0,
+                    help="the child jobs also end this long after this process started, whatever the series measurement took")
     ap.add_argument("--extra-steps", type=int, default=2)
     ap.add_argument("--extra-warmup", type=int, default=3)
     ap.add_argument("--sub", default="", help="internal: this process is a child job (run | pair | check)")
@@ -408,7 +411,7 @@ def brief(res):
 
 def run_extras(args, world, line):
     """Child jobs after the series measurement (rank 0 only, the process group is closed, the other ranks are gone)."""
-    deadline = time.time() + args.extras_budget_s
+    deadline = min(time.time() + args.extras_budget_s, T_START + args.total_budget_s)
     port0 = int(os.environ.get("MASTER_PORT", "29500")) + 101
     common = ["--steps", str(args.extra_steps), "--warmup", str(args.extra_warmup), "--configs", "none", "--no-e2e",
               "--min-len", str(args.min_len), "--max-len", str(args.max_len), "--grad-accum", str(args.grad_accum)]
@@ -471,7 +474,8 @@ def run_extras(args, world, line):
         configs["ep_over_no_ep"] = ratios
     line["configs"] = configs
     line["configs_note"] = (f"child jobs on the same GPUs after the series measurement, {args.extra_warmup} warm-up + {args.extra_steps} timed "
-                            f"optimizer steps per arm, same data recipe, device-input timing; together limited to {int(args.extras_budget_s)} s")
+                            f"optimizer steps per arm, same data recipe, device-input timing; together limited to {int(args.extras_budget_s)} s and to {int(args.total_budget_s)} s "
+                            f"after the start of the whole run")
 
 
 def main():
