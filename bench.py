@@ -72,6 +72,8 @@ def parse():
     ap.add_argument("--extra-warmup", type=int, default=3)
     ap.add_argument("--sub", default="", help="internal: this process is a child job (run | pair | check)")
     ap.add_argument("--sub-out", default="")
+    ap.add_argument("--abs-deadline", type=float, default=0.0,
+                    help="internal: wall-clock time (epoch seconds) by which a child job should have ended by itself")
     return ap.parse_args()
 
 
@@ -285,13 +287,47 @@ def run_measurement(args):
     return line
 
 
+def second_arm_fits(first_arm_s, now, abs_deadline):
+    """Whether the library arm of a pair job can still finish by `abs_deadline`: it builds the same model and runs the
+    same steps 1.5-2x as slowly as the native arm, which took `first_arm_s`."""
+    return now + 2.2 * first_arm_s + 10.0 < abs_deadline
+
+
+def share_decision(path, rank, decision=None, wait_s=60.0):
+    """Rank 0 publishes a yes/no decision in `path`; every rank returns it (no: also when nothing appears in time)."""
+    if rank == 0:
+        with open(path + ".tmp", "w") as f:
+            f.write("go" if decision else "skip")
+        os.replace(path + ".tmp", path)
+    t0 = time.time()
+    while not os.path.exists(path) and time.time() - t0 < wait_s:
+        time.sleep(0.05)
+    try:
+        with open(path) as f:
+            return f.read().strip() == "go"
+    except OSError:
+        return False
+
+
 def run_pair(args):
     """One configuration on both arms in one job: native first, then library.  The result file is rewritten after
     each arm, so that the first arm's numbers survive if the second one fails or runs out of time."""
     rank = int(os.environ.get("RANK", 0))
     out = {}
+    t_arm = time.time()
     for impl in ("native", "library"):
         args.impl = impl
+        if impl == "library" and args.abs_deadline > 0:
+            # Rather end here than be stopped in the middle of a collective: rank 0 decides from the first arm's duration
+            # and tells the other ranks through a file.
+            go = share_decision(args.sub_out + ".decision", rank,
+                                second_arm_fits(time.time() - t_arm, time.time(), args.abs_deadline) if rank == 0 else None)
+            if not go:
+                out[impl] = {"skipped": "not enough of the run's time limit left for this arm"}
+                if rank == 0:
+                    with open(args.sub_out, "w") as f:
+                        json.dump(out, f)
+                break
         try:
             out[impl] = brief(run_measurement(args)) if rank == 0 else run_measurement(args)
         except Exception as exc:  # noqa: BLE001
@@ -357,7 +393,10 @@ def _clean_env():
 def run_child(n, extra_args, timeout_s, port):
     """Runs `bench.py --sub ...` on n GPUs as a job of its own; returns its result dict or {"error": ...}."""
     out_path = os.path.join("/tmp", f"mdt_bench_child_{os.getpid()}_{port}.json")
-    base = [os.path.join(HERE, "bench.py"), "--gpus", str(n), "--sub-out", out_path] + extra_args
+    for stale in (out_path, out_path + ".decision"):
+        if os.path.exists(stale):
+            os.remove(stale)
+    base = [os.path.join(HERE, "bench.py"), "--gpus", str(n), "--sub-out", out_path, "--abs-deadline", f"{time.time() + timeout_s - 8.0:.1f}"] + extra_args
     if n > 1:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
                "--master-port", str(port)] + base
@@ -389,6 +428,8 @@ def run_child(n, extra_args, timeout_s, port):
 
 def _read_partial(path):
     try:
+        if os.path.exists(path + ".decision"):
+            os.remove(path + ".decision")
         with open(path) as f:
             res = json.load(f)
         os.remove(path)
