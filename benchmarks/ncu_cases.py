@@ -1,6 +1,6 @@
 """Small single-GPU cases for profiler captures: one kernel family per case, a handful of launches.
 
-    python benchmarks/ncu_cases.py gemm|gemm_pair|gemm_split|gather_gemm|expert_mlp|attention|dispatch|gemm_exchange
+    python benchmarks/ncu_cases.py gemm|gemm_pair|gemm_split|gather_gemm|rs_block|expert_mlp|attention|dispatch|gemm_exchange
 
 Sizes keep the working set above the 126 MB L2 where DRAM figures matter, but far below a GB of launches.
 """
@@ -135,6 +135,36 @@ def main():
                      wait=(wi.tile_counters(par), te), scatter=(rr, rp, peer_out, peer_arr))
             for r, wo in enumerate(spaces_out):
                 C.ext.ep_wait_rows(wo.my_base, wo.layout, metas[r], par, status, (N + 255) // 256)
+    elif case == "rs_block":
+        # Gradient reduce-scatter of one decoder block's attention parameters (full fine-tune: 42 M fp32 accumulator
+        # elements per rank) as one kernel: announce, wait for the peers' announcements, read this rank's slice of
+        # every rank's accumulator with 16-byte loads, scale, cast to bf16, add to the shard gradient.  Eight ranks
+        # emulated on one GPU: their kernels run one after another, so all announcements are written beforehand and
+        # no launch waits for a later one.
+        ws_ = 8
+        n = (4096 + 1024 + 1024 + 4096) * 4096 // ws_
+        C.ext.set_peer_wait_limit_ms(500)
+        fulls = [torch.randn(ws_ * n, device=dev) for _ in range(ws_)]
+        ftable = torch.tensor([f.data_ptr() for f in fulls], dtype=torch.int64, device=dev)
+        flags = [torch.zeros(8 * ws_, dtype=torch.int32, device=dev) for _ in range(ws_)]
+        flag_table = torch.tensor([f.data_ptr() for f in flags], dtype=torch.int64, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        shard = torch.zeros(n, dtype=bf, device=dev)
+        flush = torch.zeros(96 * 1024 * 1024, device=dev)
+        times = []
+        for epoch in range(1, 6):
+            for f in flags:
+                f.view(8, ws_)[3].fill_(epoch)
+            flush.add_(1.0)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            C.ext.rs_block(shard, ftable, flag_table, flags[0].data_ptr(), 3, ws_, 0, True, 1.0 / ws_, True, epoch, status)
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        ms = sorted(times)[len(times) // 2]
+        print(f"rs_block: {ws_} x {n * 4 / 1e6:.1f} MB read, {n * 2 / 1e6:.1f} MB written in {ms:.4f} ms = {(ws_ * n * 4 + 2 * n * 2) / ms / 1e6:.0f} GB/s")
+        assert int(status.item()) == 0
     else:
         raise SystemExit("unknown case")
     torch.cuda.synchronize()

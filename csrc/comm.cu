@@ -387,27 +387,90 @@ __device__ __forceinline__ void from_f(bf16* p, float v) { *p = __float2bfloat16
 template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
 // `src_off`: first element of the range that is read from every peer's buffer (rank * n for a reduce-scatter, 0 for an
 // all-reduce of n elements)
+// V consecutive outputs as one 8-, 16- or 2 x 16-byte access (the caller has checked the alignment)
+template <int V> __device__ __forceinline__ void load_out_vec(const bf16* p, float (&o)[V]) {
+  if constexpr (V == 4) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    for (int j = 0; j < 2; ++j) { const float2 f = __bfloat1622float2(h[j]); o[2 * j] = f.x; o[2 * j + 1] = f.y; }
+  } else {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h[j]); o[2 * j] = f.x; o[2 * j + 1] = f.y; }
+  }
+}
+template <int V> __device__ __forceinline__ void load_out_vec(const float* p, float (&o)[V]) {
+#pragma unroll
+  for (int c = 0; c < V / 4; ++c) {
+    const float4 v = reinterpret_cast<const float4*>(p)[c];
+    o[4 * c] = v.x; o[4 * c + 1] = v.y; o[4 * c + 2] = v.z; o[4 * c + 3] = v.w;
+  }
+}
+template <int V> __device__ __forceinline__ void store_out_vec(bf16* p, const float (&o)[V]) {
+  if constexpr (V == 4) {
+    uint2 v;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+    for (int j = 0; j < 2; ++j) h[j] = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]);
+    *reinterpret_cast<uint2*>(p) = v;
+  } else {
+    uint4 v;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]);
+    *reinterpret_cast<uint4*>(p) = v;
+  }
+}
+template <int V> __device__ __forceinline__ void store_out_vec(float* p, const float (&o)[V]) {
+#pragma unroll
+  for (int c = 0; c < V / 4; ++c) reinterpret_cast<float4*>(p)[c] = make_float4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+}
+
 template <typename TIn, typename TOut>
 __device__ __forceinline__ void rs_pull_body(TOut* __restrict__ out, const long long* __restrict__ peer_full, int ws, int rank, long long n,
                                              float scale, int accumulate, long long tid, long long nthreads, long long src_off) {
   constexpr int V = Vec16<TIn>::N;
+  constexpr int BATCH = 8;            // peers whose vectors are in flight together (the latency of a peer load is ~2 us)
   const long long nvec = n / V;
+  const bool out_vec = (reinterpret_cast<unsigned long long>(out) % (V * sizeof(TOut))) == 0;
   for (long long i = tid; i < nvec; i += nthreads) {
     float acc[V];
 #pragma unroll
     for (int j = 0; j < V; ++j) acc[j] = 0.f;
-    for (int r = 0; r < ws; ++r) {
-      const int rr = (r + rank) % ws;   // start with a different peer on every rank
-      const uint4 v = reinterpret_cast<const uint4*>(reinterpret_cast<const TIn*>(peer_full[rr]) + src_off)[i];
-      const TIn* e = reinterpret_cast<const TIn*>(&v);
+    for (int r0 = 0; r0 < ws; r0 += BATCH) {
+      uint4 v[BATCH];
 #pragma unroll
-      for (int j = 0; j < V; ++j) acc[j] += to_f(e[j]);
+      for (int u = 0; u < BATCH; ++u) {
+        if (r0 + u < ws) {
+          const int rr = (r0 + u + rank) % ws;   // start with a different peer on every rank
+          v[u] = reinterpret_cast<const uint4*>(reinterpret_cast<const TIn*>(peer_full[rr]) + src_off)[i];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        if (r0 + u < ws) {
+          const TIn* e = reinterpret_cast<const TIn*>(&v[u]);
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[j] += to_f(e[j]);
+        }
+      }
     }
+    if (out_vec) {
+      float o[V];
+      if (accumulate) {
+        load_out_vec<V>(out + i * V, o);
 #pragma unroll
-    for (int j = 0; j < V; ++j) {
-      float sres = acc[j] * scale;
-      if (accumulate) sres += to_f(out[i * V + j]);
-      from_f(out + i * V + j, sres);
+        for (int j = 0; j < V; ++j) o[j] += acc[j] * scale;
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) o[j] = acc[j] * scale;
+      }
+      store_out_vec<V>(out + i * V, o);
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        float sres = acc[j] * scale;
+        if (accumulate) sres += to_f(out[i * V + j]);
+        from_f(out + i * V + j, sres);
+      }
     }
   }
   for (long long i = nvec * V + tid; i < n; i += nthreads) {   // tail (n not a multiple of the vector width)
