@@ -35,3 +35,17 @@ def test_ranks_share_the_decision_of_rank_zero(tmp_path):
 
 def test_a_decision_that_never_arrives_means_no(tmp_path):
     assert bench.share_decision(str(tmp_path / "never"), 1, None, wait_s=0.2) is False
+
+
+def test_reference_arm_reports_unavailable_and_exits_zero():
+    """`bench.py --impl reference` must print one JSON line with `impl` and `unavailable` and exit 0 when the
+    reference's entry points cannot run (their third-party imports are missing in this environment)."""
+    import json
+    import subprocess
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, os.path.join(here, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "3"],
+                       capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    line = json.loads(p.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference"
+    assert "unavailable" in line and isinstance(line["unavailable"], str) and "\n" not in line["unavailable"]
